@@ -1,0 +1,327 @@
+// Python bindings of the extension `_C`: one function per kernel family.  Every function
+// validates device, dtype, shape and contiguity of what it is given and raises a Python
+// error that names the argument; nothing is allocated here (callers pass outputs and
+// workspaces), so every call can be captured into a CUDA graph.  The reference's extension
+// has the same split between checked entry points and launchers (csrc/bindings.cpp:43-73,
+// csrc/paged_decode.cu:567-632), but guards indices with device asserts; here a bad index
+// sets a code in the `status` tensor instead and the access is skipped.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "launchers.h"
+
+namespace {
+
+using at::Tensor;
+using OptTensor = c10::optional<at::Tensor>;
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+int dtype_code(const Tensor& t, const char* name) {
+  if (t.scalar_type() == at::kFloat) return 0;
+  if (t.scalar_type() == at::kBFloat16) return 1;
+  TORCH_CHECK(false, name, " must be float32 or bfloat16, got ", t.scalar_type());
+  return -1;
+}
+
+void check_same(const Tensor& a, const Tensor& b, const char* an, const char* bn) {
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), an, " and ", bn, " must have the same dtype");
+  TORCH_CHECK(a.device() == b.device(), an, " and ", bn, " must be on the same device");
+}
+
+void check_i32(const Tensor& t, const char* name, int64_t numel = -1) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kInt, name, " must be int32");
+  if (numel >= 0) TORCH_CHECK(t.numel() >= numel, name, " must hold at least ", numel, " entries, has ", t.numel());
+}
+
+void check_f32(const Tensor& t, const char* name, int64_t numel = -1) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
+  if (numel >= 0) TORCH_CHECK(t.numel() == numel, name, " must hold ", numel, " entries, has ", t.numel());
+}
+
+int* status_ptr(const OptTensor& status) {
+  if (!status.has_value()) return nullptr;
+  check_i32(*status, "status", 1);
+  return status->data_ptr<int>();
+}
+
+void check_launch(int err, const char* what) {
+  TORCH_CHECK(err == 0, what, ": launch failed: ", cudaGetErrorString((cudaError_t)err));
+}
+
+cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+Tensor smoke_add(const Tensor& a, const Tensor& b) {
+  check_f32(a, "a");
+  check_f32(b, "b", a.numel());
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = at::empty_like(a);
+  check_launch(akv::launch_smoke_add(a.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr<float>(), a.numel(),
+                                     stream_of(a)),
+               "smoke_add");
+  return out;
+}
+
+void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const OptTensor& status) {
+  check_cuda(table, "table");
+  TORCH_CHECK(table.dim() == 2, "table must be [vocab, hidden]");
+  const int64_t n = ids.numel(), h = table.size(1);
+  check_i32(ids, "ids");
+  check_f32(hidden, "hidden", n * h);
+  c10::cuda::CUDAGuard guard(table.device());
+  check_launch(akv::launch_embedding(ids.data_ptr<int>(), table.data_ptr(), hidden.data_ptr<float>(), n, h,
+                                     table.size(0), dtype_code(table, "table"), status_ptr(status),
+                                     stream_of(table)),
+               "embedding");
+}
+
+void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, Tensor& out, const OptTensor& rows,
+                 double eps, const OptTensor& status) {
+  check_cuda(hidden, "hidden");
+  TORCH_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2, "hidden must be float32 [tokens, hidden]");
+  const int64_t n = hidden.size(0), h = hidden.size(1);
+  check_f32(weight, "weight", h);
+  check_cuda(out, "out");
+  const int code = dtype_code(out, "out");
+  TORCH_CHECK(h * 4 <= 200 * 1024, "add_rmsnorm: hidden size ", h, " exceeds the kernel's limit of 51200");
+  const void* delta_ptr = nullptr;
+  if (delta.has_value()) {
+    check_cuda(*delta, "delta");
+    check_same(*delta, out, "delta", "out");
+    TORCH_CHECK(delta->numel() == n * h, "delta must be [tokens, hidden]");
+    delta_ptr = delta->data_ptr();
+  }
+  const int* rows_ptr = nullptr;
+  int64_t num_rows = 0;
+  if (rows.has_value()) {
+    check_i32(*rows, "rows");
+    rows_ptr = rows->data_ptr<int>();
+    num_rows = rows->numel();
+    TORCH_CHECK(out.numel() == num_rows * h, "out must be [rows, hidden]");
+  } else {
+    TORCH_CHECK(out.numel() == n * h, "out must be [tokens, hidden]");
+  }
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_add_rmsnorm(hidden.data_ptr<float>(), delta_ptr, weight.data_ptr<float>(), out.data_ptr(),
+                                       rows_ptr, num_rows, n, h, (float)eps, code, status_ptr(status),
+                                       stream_of(hidden)),
+               "add_rmsnorm");
+}
+
+void silu_mul(const Tensor& gate_up, Tensor& out) {
+  check_cuda(gate_up, "gate_up");
+  check_cuda(out, "out");
+  check_same(gate_up, out, "gate_up", "out");
+  TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
+  const int64_t n = gate_up.size(0), inter = gate_up.size(1) / 2;
+  TORCH_CHECK(out.numel() == n * inter, "out must be [tokens, intermediate]");
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  check_launch(akv::launch_silu_mul(gate_up.data_ptr(), out.data_ptr(), n, inter, dtype_code(out, "out"),
+                                    stream_of(out)),
+               "silu_mul");
+}
+
+struct CacheGeometry {
+  int64_t num_pages;
+  int num_kv_heads, page_size, head_dim;
+};
+
+CacheGeometry check_cache(const Tensor& k_cache, const Tensor& v_cache, int num_kv_heads, int head_dim,
+                          const Tensor& like) {
+  check_cuda(k_cache, "k_cache");
+  check_cuda(v_cache, "v_cache");
+  check_same(k_cache, v_cache, "k_cache", "v_cache");
+  check_same(k_cache, like, "k_cache", "activations");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.sizes() == v_cache.sizes(),
+              "k_cache and v_cache must both be [pages, kv_heads, page_size, head_dim]");
+  TORCH_CHECK(k_cache.size(1) == num_kv_heads && k_cache.size(3) == head_dim, "cache pages are [",
+              k_cache.size(1), " kv heads, ", k_cache.size(3), " dims], the call says [", num_kv_heads, ", ",
+              head_dim, "]");
+  return {k_cache.size(0), num_kv_heads, (int)k_cache.size(2), head_dim};
+}
+
+void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTensor& slots,
+                        const OptTensor& q_weight, const OptTensor& k_weight, const OptTensor& inv_freq,
+                        Tensor& q_out, const OptTensor& k_out, const OptTensor& v_out, const OptTensor& k_cache,
+                        const OptTensor& v_cache, int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                        int64_t rotary_dim, double eps, const OptTensor& status) {
+  check_cuda(qkv, "qkv");
+  check_cuda(q_out, "q_out");
+  check_same(qkv, q_out, "qkv", "q_out");
+  TORCH_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0, "head counts and head_dim must be positive");
+  TORCH_CHECK(head_dim % 2 == 0 && head_dim <= 512, "qk_norm_rope_write: head_dim must be even and <= 512, got ",
+              head_dim);
+  const int64_t width = (num_heads + 2 * num_kv_heads) * head_dim;
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == width, "qkv must be [tokens, (heads + 2 kv_heads) * head_dim = ",
+              width, "]");
+  const int64_t n = qkv.size(0);
+  check_i32(positions, "positions", n);
+  TORCH_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
+  akv::QkRopeWriteParams p{};
+  p.qkv = qkv.data_ptr();
+  p.positions = positions.data_ptr<int>();
+  p.q_out = q_out.data_ptr();
+  if (slots.has_value()) {
+    check_i32(*slots, "slots", n);
+    p.slots = slots->data_ptr<int>();
+  }
+  if (q_weight.has_value()) { check_f32(*q_weight, "q_weight", head_dim); p.q_weight = q_weight->data_ptr<float>(); }
+  if (k_weight.has_value()) { check_f32(*k_weight, "k_weight", head_dim); p.k_weight = k_weight->data_ptr<float>(); }
+  if (inv_freq.has_value()) {
+    TORCH_CHECK(rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
+                "rotary_dim must be even and in (0, head_dim], got ", rotary_dim);
+    check_f32(*inv_freq, "inv_freq", rotary_dim / 2);
+    p.inv_freq = inv_freq->data_ptr<float>();
+  }
+  if (k_out.has_value()) {
+    check_cuda(*k_out, "k_out"); check_same(*k_out, qkv, "k_out", "qkv");
+    TORCH_CHECK(k_out->numel() == n * num_kv_heads * head_dim, "k_out must be [tokens, kv_heads * head_dim]");
+    p.k_out = k_out->data_ptr();
+  }
+  if (v_out.has_value()) {
+    check_cuda(*v_out, "v_out"); check_same(*v_out, qkv, "v_out", "qkv");
+    TORCH_CHECK(v_out->numel() == n * num_kv_heads * head_dim, "v_out must be [tokens, kv_heads * head_dim]");
+    p.v_out = v_out->data_ptr();
+  }
+  TORCH_CHECK(k_cache.has_value() == v_cache.has_value(), "k_cache and v_cache come together");
+  if (k_cache.has_value()) {
+    TORCH_CHECK(slots.has_value(), "a cache to write needs slots");
+    const CacheGeometry g = check_cache(*k_cache, *v_cache, (int)num_kv_heads, (int)head_dim, qkv);
+    p.k_cache = k_cache->data_ptr();
+    p.v_cache = v_cache->data_ptr();
+    p.num_pages = g.num_pages;
+    p.page_size = g.page_size;
+  }
+  p.num_tokens = n;
+  p.num_heads = (int)num_heads;
+  p.num_kv_heads = (int)num_kv_heads;
+  p.head_dim = (int)head_dim;
+  p.rotary_dim = (int)rotary_dim;
+  p.eps = (float)eps;
+  p.dtype = dtype_code(qkv, "qkv");
+  p.status = status_ptr(status);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  check_launch(akv::launch_qk_norm_rope_write(p, stream_of(qkv)), "qk_norm_rope_write");
+}
+
+void kv_write(const Tensor& k, const Tensor& v, const Tensor& slots, Tensor& k_cache, Tensor& v_cache,
+              const OptTensor& status) {
+  check_cuda(k, "k");
+  check_cuda(v, "v");
+  check_same(k, v, "k", "v");
+  TORCH_CHECK(k.dim() == 2 && k.sizes() == v.sizes(), "k and v must both be [tokens, kv_heads * head_dim]");
+  TORCH_CHECK(k_cache.dim() == 4, "k_cache must be [pages, kv_heads, page_size, head_dim]");
+  const int nkv = (int)k_cache.size(1), d = (int)k_cache.size(3);
+  const CacheGeometry g = check_cache(k_cache, v_cache, nkv, d, k);
+  TORCH_CHECK(k.size(1) == (int64_t)nkv * d, "k is ", k.size(1), " wide, the cache wants ", (int64_t)nkv * d);
+  check_i32(slots, "slots", k.size(0));
+  c10::cuda::CUDAGuard guard(k.device());
+  check_launch(akv::launch_kv_write(k.data_ptr(), v.data_ptr(), slots.data_ptr<int>(), k_cache.data_ptr(),
+                                    v_cache.data_ptr(), k.size(0), nkv, d, g.page_size, g.num_pages,
+                                    dtype_code(k, "k"), status_ptr(status), stream_of(k)),
+               "kv_write");
+}
+
+void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, Tensor& out,
+                     const Tensor& block_table, const Tensor& cu_q, const Tensor& ctx_lens, const Tensor& tile_seq,
+                     const Tensor& tile_q0, const Tensor& tile_nq, const OptTensor& partials, int64_t num_tiles,
+                     int64_t q_tile, int64_t num_splits, int64_t num_heads, int64_t num_kv_heads, int64_t window,
+                     double scale, const OptTensor& status) {
+  check_cuda(q, "q");
+  check_cuda(out, "out");
+  check_same(q, out, "q", "out");
+  TORCH_CHECK(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0,
+              "paged_attention: heads (", num_heads, ") must be a positive multiple of kv heads (", num_kv_heads, ")");
+  TORCH_CHECK(q.dim() == 2 && q.size(1) % num_heads == 0, "q must be [tokens, heads * head_dim]");
+  const int64_t n = q.size(0), d = q.size(1) / num_heads;
+  TORCH_CHECK(d % 16 == 0 && d <= 256, "paged_attention: head_dim must be a multiple of 16 up to 256, got ", d);
+  TORCH_CHECK(out.numel() == q.numel(), "out must have q's shape");
+  const CacheGeometry g = check_cache(k_cache, v_cache, (int)num_kv_heads, (int)d, q);
+  check_i32(block_table, "block_table");
+  TORCH_CHECK(block_table.dim() == 2, "block_table must be [sequences, width]");
+  const int64_t s = block_table.size(0);
+  check_i32(cu_q, "cu_q", s + 1);
+  check_i32(ctx_lens, "ctx_lens", s);
+  TORCH_CHECK(num_tiles >= 0 && q_tile >= 1 && num_splits >= 1 && window >= 0, "bad tile / split / window counts");
+  check_i32(tile_seq, "tile_seq", num_tiles);
+  check_i32(tile_q0, "tile_q0", num_tiles);
+  check_i32(tile_nq, "tile_nq", num_tiles);
+  akv::PagedAttentionParams p{};
+  if (num_splits > 1) {
+    TORCH_CHECK(partials.has_value(), "num_splits > 1 needs a partials workspace");
+    check_cuda(*partials, "partials");
+    TORCH_CHECK(partials->scalar_type() == at::kFloat && partials->numel() >= n * num_heads * num_splits * (d + 2),
+                "partials must be float32 with at least tokens * heads * splits * (head_dim + 2) entries");
+    p.partials = partials->data_ptr<float>();
+  }
+  p.q = q.data_ptr();
+  p.k_cache = k_cache.data_ptr();
+  p.v_cache = v_cache.data_ptr();
+  p.out = out.data_ptr();
+  p.block_table = block_table.data_ptr<int>();
+  p.cu_q = cu_q.data_ptr<int>();
+  p.ctx_lens = ctx_lens.data_ptr<int>();
+  p.tile_seq = tile_seq.data_ptr<int>();
+  p.tile_q0 = tile_q0.data_ptr<int>();
+  p.tile_nq = tile_nq.data_ptr<int>();
+  p.num_tokens = n;
+  p.num_tiles = (int)num_tiles;
+  p.q_tile = (int)q_tile;
+  p.num_splits = (int)num_splits;
+  p.num_seqs = (int)s;
+  p.table_width = (int)block_table.size(1);
+  p.num_heads = (int)num_heads;
+  p.num_kv_heads = (int)num_kv_heads;
+  p.head_dim = (int)d;
+  p.page_size = g.page_size;
+  p.num_pages = g.num_pages;
+  p.window = (int)window;
+  p.scale = (float)scale;
+  p.dtype = dtype_code(q, "q");
+  p.status = status_ptr(status);
+  c10::cuda::CUDAGuard guard(q.device());
+  check_launch(akv::launch_paged_attention(p, stream_of(q)), "paged_attention");
+}
+
+void sample(const Tensor& logits, const Tensor& temperature, const Tensor& uniform, Tensor& tokens) {
+  check_cuda(logits, "logits");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2, "logits must be float32 [rows, vocab]");
+  const int64_t rows = logits.size(0);
+  check_f32(temperature, "temperature", rows);
+  check_f32(uniform, "uniform", rows);
+  check_i32(tokens, "tokens", rows);
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_launch(akv::launch_sample(logits.data_ptr<float>(), temperature.data_ptr<float>(), uniform.data_ptr<float>(),
+                                  tokens.data_ptr<int>(), rows, logits.size(1), stream_of(logits)),
+               "sample");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "sm_100a kernels of the engine";
+  namespace py = pybind11;
+  m.def("smoke_add", &smoke_add, "a + b on the device (toolchain check)");
+  m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("hidden"), py::arg("status") = py::none());
+  m.def("add_rmsnorm", &add_rmsnorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
+        py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
+  m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"));
+  m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),
+        py::arg("q_weight"), py::arg("k_weight"), py::arg("inv_freq"), py::arg("q_out"), py::arg("k_out"),
+        py::arg("v_out"), py::arg("k_cache"), py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"),
+        py::arg("head_dim"), py::arg("rotary_dim"), py::arg("eps"), py::arg("status") = py::none());
+  m.def("kv_write", &kv_write, py::arg("k"), py::arg("v"), py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"),
+        py::arg("status") = py::none());
+  m.def("paged_attention", &paged_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
+        py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),
+        py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),
+        py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("window"), py::arg("scale"),
+        py::arg("status") = py::none());
+  m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("uniform"), py::arg("tokens"));
+}

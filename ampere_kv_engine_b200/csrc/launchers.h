@@ -1,0 +1,86 @@
+// Host launchers of the hand-written kernels.  Plain C++ signatures over raw device
+// pointers so that the .cu files compile without any tensor-library header; bindings.cpp
+// checks shapes, dtypes, devices and contiguity before it calls these.
+//
+// `dtype` is akv::DType (0 = float32, 1 = bfloat16) and names the storage type of
+// activations / matrices / cache pages; norm weights, rotary tables and logits are float32.
+// Every launcher enqueues on `stream` and returns the launch's cudaError_t as int.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace akv {
+
+int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream);
+
+// hidden[n, :] = float(table[ids[n], :])
+int launch_embedding(const int32_t* ids, const void* table, float* hidden, int64_t num_tokens,
+                     int64_t hidden_size, int64_t vocab, int dtype, int* status, cudaStream_t stream);
+
+// hidden += delta (if delta); out = rmsnorm(hidden) * weight.  With `rows` (num_rows entries)
+// only those rows are read, hidden is left untouched and out is [num_rows, hidden_size].
+int launch_add_rmsnorm(float* hidden, const void* delta, const float* weight, void* out,
+                       const int32_t* rows, int64_t num_rows, int64_t num_tokens, int64_t hidden_size,
+                       float eps, int dtype, int* status, cudaStream_t stream);
+
+// out[n, i] = silu(gate_up[n, i]) * gate_up[n, inter + i]
+int launch_silu_mul(const void* gate_up, void* out, int64_t num_tokens, int64_t inter, int dtype,
+                    cudaStream_t stream);
+
+struct QkRopeWriteParams {
+  const void* qkv;          // [N, (NH + 2 NKV) * D]
+  const int32_t* positions; // [N]
+  const int32_t* slots;     // [N] page * page_size + offset, or -1: do not write; may be null
+  const float* q_weight;    // [D] or null: no norm
+  const float* k_weight;    // [D] or null
+  const float* inv_freq;    // [rotary_dim / 2] or null: no rotation
+  void* q_out;              // [N, NH * D]
+  void* k_out;              // [N, NKV * D] or null
+  void* v_out;              // [N, NKV * D] or null
+  void* k_cache;            // [num_pages, NKV, page_size, D] or null
+  void* v_cache;
+  int64_t num_tokens;
+  int num_heads, num_kv_heads, head_dim, rotary_dim, page_size;
+  int64_t num_pages;
+  float eps;
+  int dtype;
+  int* status;
+};
+int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream);
+
+// Copy k, v [N, NKV * D] into their cache slots.
+int launch_kv_write(const void* k, const void* v, const int32_t* slots, void* k_cache, void* v_cache,
+                    int64_t num_tokens, int num_kv_heads, int head_dim, int page_size, int64_t num_pages,
+                    int dtype, int* status, cudaStream_t stream);
+
+struct PagedAttentionParams {
+  const void* q;               // [N, NH * D]
+  const void* k_cache;         // [num_pages, NKV, page_size, D]
+  const void* v_cache;
+  void* out;                   // [N, NH * D]
+  const int32_t* block_table;  // [S, table_width]
+  const int32_t* cu_q;         // [S + 1] first batch row of each sequence
+  const int32_t* ctx_lens;     // [S] keys of each sequence once this step's tokens are in
+  const int32_t* tile_seq;     // [tiles] sequence of each query tile
+  const int32_t* tile_q0;      // [tiles] first batch row of the tile
+  const int32_t* tile_nq;      // [tiles] rows in the tile (<= q_tile)
+  float* partials;             // [N * NH, num_splits, D + 2] when num_splits > 1
+  int64_t num_tokens;
+  int num_tiles, q_tile, num_splits;
+  int num_seqs, table_width;
+  int num_heads, num_kv_heads, head_dim, page_size;
+  int64_t num_pages;
+  int window;                  // 0 = all keys
+  float scale;
+  int dtype;
+  int* status;
+};
+int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream);
+
+// tokens[r] = argmax(logits[r]) where temperature[r] == 0, else the inverse-CDF draw of
+// softmax(logits[r] / temperature[r]) at uniform[r].
+int launch_sample(const float* logits, const float* temperature, const float* uniform, int32_t* tokens,
+                  int64_t num_rows, int64_t vocab, cudaStream_t stream);
+
+}  // namespace akv

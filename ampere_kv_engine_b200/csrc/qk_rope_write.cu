@@ -1,0 +1,190 @@
+// Fused per-head QK RMSNorm + rotate-half RoPE + KV page write, and the page write alone.
+//
+// Replaces, in one pass over the fused projection output: the per-head norms of
+// ampere_kv/runner.py:73-75, apply_rope (runner.py:80-98: angle = position * inv_freq in
+// float32, both halves share the angle, x*cos + rotate_half(x)*sin) and the page-write
+// kernels csrc/paged_decode.cu:90-111 and :500-525 (post-rotation K and un-rotated V go to
+// slot (page, offset) of a [page, kv_head, offset, dim] pool).
+//
+// One warp per (token, head).  Lane l owns the rotation pairs (j, j + D/2) for
+// j = l, l + 32, ... so any even head size works.  rotary_dim <= D may rotate only the first
+// rotary_dim dims of a head (pairs (j, j + rotary_dim/2)); the rest pass through.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace akv {
+
+constexpr int kMaxPairsPerLane = 8;  // head_dim <= 512
+
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(QkRopeWriteParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_heads = p.num_heads + 2 * p.num_kv_heads;
+  const int head = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int64_t token = blockIdx.y + (int64_t)blockIdx.z * 65535;
+  if (head >= total_heads || token >= p.num_tokens) return;
+  const int D = p.head_dim, half = D / 2;
+  const T* src = (const T*)p.qkv + (token * total_heads + head) * (int64_t)D;
+
+  // which kind of head, and where its results go
+  const bool is_q = head < p.num_heads;
+  const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
+  const int local = is_q ? head : (is_k ? head - p.num_heads : head - p.num_heads - p.num_kv_heads);
+  T* dense_out = nullptr;
+  if (is_q) dense_out = (T*)p.q_out + (token * p.num_heads + local) * (int64_t)D;
+  else if (is_k && p.k_out) dense_out = (T*)p.k_out + (token * p.num_kv_heads + local) * (int64_t)D;
+  else if (!is_k && p.v_out) dense_out = (T*)p.v_out + (token * p.num_kv_heads + local) * (int64_t)D;
+  T* cache_out = nullptr;
+  if (!is_q && p.slots != nullptr && p.k_cache != nullptr) {
+    const int64_t slot = p.slots[token];
+    if (slot >= 0) {
+      if (slot >= p.num_pages * p.page_size) {
+        if (lane == 0) set_status(p.status, kBadSlot);
+      } else {
+        const int64_t page = slot / p.page_size, off = slot % p.page_size;
+        T* base = (T*)(is_k ? p.k_cache : p.v_cache);
+        cache_out = base + ((page * p.num_kv_heads + local) * p.page_size + off) * (int64_t)D;
+      }
+    }
+  }
+
+  // load the head: lane owns elements j and j + half
+  float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxPairsPerLane; ++c) {
+    const int j = c * 32 + lane;
+    if (j < half) {
+      lo[c] = to_float<T>(src[j]);
+      hi[c] = to_float<T>(src[j + half]);
+      ss += lo[c] * lo[c] + hi[c] * hi[c];
+    } else {
+      lo[c] = hi[c] = 0.f;
+    }
+  }
+  const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+    for (int c = 0; c < kMaxPairsPerLane; ++c) {
+      const int j = c * 32 + lane;
+      if (j < half) {
+        lo[c] = lo[c] * inv * w[j];
+        hi[c] = hi[c] * inv * w[j + half];
+      }
+    }
+  }
+  const bool rotate = !(!is_q && !is_k) && p.inv_freq != nullptr && p.rotary_dim > 0;
+  if (rotate && p.rotary_dim == D) {
+    const float pos = (float)p.positions[token];
+#pragma unroll
+    for (int c = 0; c < kMaxPairsPerLane; ++c) {
+      const int j = c * 32 + lane;
+      if (j < half) {
+        const float angle = pos * p.inv_freq[j];
+        float s, co;
+        sincosf(angle, &s, &co);
+        const float a = lo[c], b = hi[c];
+        lo[c] = a * co - b * s;  // x*cos + (-x[j+half])*sin
+        hi[c] = b * co + a * s;  // x*cos + ( x[j])*sin
+      }
+    }
+  }
+  // store (a partial rotary_dim is handled below, after the values are in memory order)
+  if (rotate && p.rotary_dim != D) {
+    // general case: rotation pairs are (j, j + rotary_dim/2) inside the first rotary_dim dims,
+    // which does not match the (j, j + D/2) ownership; go through shared memory per warp.
+    extern __shared__ float head_buf[];
+    float* buf = head_buf + warp * D;
+#pragma unroll
+    for (int c = 0; c < kMaxPairsPerLane; ++c) {
+      const int j = c * 32 + lane;
+      if (j < half) { buf[j] = lo[c]; buf[j + half] = hi[c]; }
+    }
+    __syncwarp();
+    const int rh = p.rotary_dim / 2;
+    const float pos = (float)p.positions[token];
+    for (int j = lane; j < rh; j += 32) {
+      const float angle = pos * p.inv_freq[j];
+      float s, co;
+      sincosf(angle, &s, &co);
+      const float a = buf[j], b = buf[j + rh];
+      buf[j] = a * co - b * s;
+      buf[j + rh] = b * co + a * s;
+    }
+    __syncwarp();
+    for (int d = lane; d < D; d += 32) {
+      const T v = from_float<T>(buf[d]);
+      if (dense_out) dense_out[d] = v;
+      if (cache_out) cache_out[d] = v;
+    }
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < kMaxPairsPerLane; ++c) {
+    const int j = c * 32 + lane;
+    if (j < half) {
+      const T a = from_float<T>(lo[c]), b = from_float<T>(hi[c]);
+      if (dense_out) { dense_out[j] = a; dense_out[j + half] = b; }
+      if (cache_out) { cache_out[j] = a; cache_out[j + half] = b; }
+    }
+  }
+}
+
+int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
+  if (p.num_tokens == 0) return 0;
+  if (p.head_dim % 2 || p.head_dim / 2 > 32 * kMaxPairsPerLane) return (int)cudaErrorInvalidValue;
+  const int warps = 4;
+  const int total_heads = p.num_heads + 2 * p.num_kv_heads;
+  const int64_t ny = p.num_tokens < 65535 ? p.num_tokens : 65535;
+  const int64_t nz = (p.num_tokens + 65534) / 65535;
+  if (nz > 65535) return (int)cudaErrorInvalidValue;
+  dim3 grid((unsigned)((total_heads + warps - 1) / warps), (unsigned)ny, (unsigned)nz);
+  const size_t smem = (p.rotary_dim != p.head_dim && p.inv_freq) ? (size_t)warps * p.head_dim * sizeof(float) : 0;
+  if (p.dtype == kBFloat16)
+    qk_norm_rope_write_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(p);
+  else
+    qk_norm_rope_write_kernel<float><<<grid, warps * 32, smem, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v,
+                                const int32_t* __restrict__ slots, T* __restrict__ k_cache,
+                                T* __restrict__ v_cache, int64_t num_tokens, int num_kv_heads, int head_dim,
+                                int page_size, int64_t num_pages, int* status) {
+  const int64_t token = blockIdx.x;
+  const int64_t slot = slots[token];
+  if (slot < 0) return;
+  if (slot >= num_pages * page_size) {
+    if (threadIdx.x == 0) set_status(status, kBadSlot);
+    return;
+  }
+  const int64_t page = slot / page_size, off = slot % page_size;
+  const int width = num_kv_heads * head_dim;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const int head = i / head_dim, d = i % head_dim;
+    const int64_t dst = ((page * num_kv_heads + head) * page_size + off) * (int64_t)head_dim + d;
+    k_cache[dst] = k[token * width + i];
+    v_cache[dst] = v[token * width + i];
+  }
+}
+
+int launch_kv_write(const void* k, const void* v, const int32_t* slots, void* k_cache, void* v_cache,
+                    int64_t num_tokens, int num_kv_heads, int head_dim, int page_size, int64_t num_pages,
+                    int dtype, int* status, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const int threads = 128;
+  if (dtype == kBFloat16)
+    kv_write_kernel<__nv_bfloat16><<<(unsigned)num_tokens, threads, 0, stream>>>(
+        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, slots, (__nv_bfloat16*)k_cache,
+        (__nv_bfloat16*)v_cache, num_tokens, num_kv_heads, head_dim, page_size, num_pages, status);
+  else
+    kv_write_kernel<float><<<(unsigned)num_tokens, threads, 0, stream>>>(
+        (const float*)k, (const float*)v, slots, (float*)k_cache, (float*)v_cache, num_tokens, num_kv_heads,
+        head_dim, page_size, num_pages, status);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace akv
