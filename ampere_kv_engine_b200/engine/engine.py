@@ -1,0 +1,128 @@
+"""The Python entry point: a model folder (or a configuration and a seed) to generated tokens.
+
+``Engine.generate`` is the multi-request form of the reference's ``generate_tokens``
+(ampere_kv/runner.py:301-406) driven through its scheduler loop
+(``while any unfinished: scheduler.step()``, ampere_kv/bench_external.py:109-114): host token
+ids in, host token ids out, greedy by default, stop at EOS unless ``ignore_eos``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.model_config import ConfigError
+from ..models.decoder import DecoderModel
+from ..models.registry import ARCHITECTURES, config_from_dict, load_config
+from ..sampling.sampler import Sampler, SamplingParams
+from ..weights.loader import load_weights
+from ..weights.random_init import init_random
+from .batch import SeqStep
+from .scheduler import Request, Scheduler
+from .step import ModelRunner
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype must be bfloat16 or float32, got {name}")
+        return name
+    if name not in _DTYPES:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {name!r}")
+    return _DTYPES[name]
+
+
+def set_exact_matmul() -> None:
+    """No reduced-precision matrix mode anywhere: float32 products stay float32 (no TF32), and
+    bfloat16 products accumulate and reduce in float32."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    try:
+        torch.set_float32_matmul_precision("highest")
+    except Exception:  # pragma: no cover
+        pass
+
+
+class Engine:
+    """Model + cache + scheduler + sampler on one device."""
+
+    def __init__(self, model: DecoderModel, *, page_size: int = 16, num_pages: int | None = None,
+                 max_tokens: int | None = None, max_seqs: int = 256, max_batch_tokens: int = 2048,
+                 admission: str = "budget"):
+        set_exact_matmul()
+        self.model = model
+        self.device = model.device
+        if num_pages is None:
+            if max_tokens is None:
+                max_tokens = min(model.spec.max_position, 8192) * 4
+            num_pages = (max_tokens + page_size - 1) // page_size + max_seqs
+        self.runner = ModelRunner(model, page_size=page_size, num_pages=num_pages, max_seqs=max_seqs)
+        self.manager = self.runner.manager
+        self.sampler = Sampler(self.device)
+        self.vocab_size = model.spec.vocab_size
+        self.max_batch_tokens = max_batch_tokens
+        self.max_seqs = max_seqs
+        self.admission = admission
+        self.eos_token_ids = tuple(model.spec.eos_token_ids)
+        self._stream_counter = 0
+
+    # ------------------------------------------------------------------ construction
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str, *, dtype="bfloat16", device="cuda", **engine_options) -> "Engine":
+        arch, config = load_config(model_dir)
+        model = DecoderModel(arch.build_spec(config), dtype=parse_dtype(dtype), device=device)
+        load_weights(model, model_dir)
+        return cls(model, **engine_options)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, *, dtype="bfloat16", device="cuda", **engine_options) -> "Engine":
+        """``config``: a typed configuration, or a dict of config.json keys (with ``architectures``)."""
+        if isinstance(config, dict):
+            arch, config = config_from_dict(config)
+        else:
+            arch = ARCHITECTURES[config.architectures[0]]
+        model = DecoderModel(arch.build_spec(config), dtype=parse_dtype(dtype), device=device)
+        init_random(model, seed)
+        return cls(model, **engine_options)
+
+    # ------------------------------------------------------------------ executor interface (for the scheduler)
+
+    def execute(self, entries: list[SeqStep], wanted: list[Request]) -> list[int]:
+        logits = self.runner.step(entries)
+        if logits is None:
+            self.runner.raise_on_status()
+            return []
+        tokens = self.sampler.sample(logits, [r.sampling for r in wanted], [len(r.output_ids) for r in wanted])
+        packed = torch.cat((tokens, self.runner.status))     # one read-back: the tokens and the kernels' status word
+        host = packed.tolist()
+        if host[-1]:
+            self.runner.raise_on_status()
+        return host[:-1]
+
+    def new_scheduler(self, **overrides) -> Scheduler:
+        options = dict(max_batch_tokens=self.max_batch_tokens, max_seqs=self.max_seqs,
+                       eos_token_ids=self.eos_token_ids, admission=self.admission,
+                       max_context=None)
+        options.update(overrides)
+        return Scheduler(self, **options)
+
+    # ------------------------------------------------------------------ generation
+
+    def generate(self, prompts: list[list[int]], max_new_tokens: int = 32, *, temperature: float = 0.0,
+                 seed: int = 0, ignore_eos: bool = False) -> list[list[int]]:
+        """New token ids for every prompt (host lists in, host lists out)."""
+        if prompts and isinstance(prompts[0], int):
+            raise TypeError("generate() takes a list of prompts, each a list of token ids")
+        scheduler = self.new_scheduler()
+        requests = []
+        for index, prompt in enumerate(prompts):
+            sampling = SamplingParams(temperature=temperature, seed=seed, stream=index)
+            requests.append(scheduler.submit(f"g{self._stream_counter}-{index}", prompt, max_new_tokens,
+                                             sampling=sampling, ignore_eos=ignore_eos))
+        self._stream_counter += 1
+        while scheduler.has_work():
+            scheduler.step()
+        return [list(r.output_ids) for r in requests]

@@ -1,0 +1,123 @@
+"""Tensor-level entry points of the kernels.
+
+Each function checks nothing twice (the extension validates its arguments) and allocates
+only its result, from the caller's device.  Matrix products are library calls
+(:func:`linear`), as they are in the reference (``F.linear`` at ampere_kv/runner.py:64-66,
+165, 174-177, 297); everything else on the step's path is a kernel of ``_C``.  There is no
+fallback: without the extension these functions raise.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import build
+
+#: query rows of one sequence that one attention tile covers
+ATTENTION_Q_TILE = 16
+
+_EXT = None
+
+
+def ext():
+    """The loaded extension module (built on first use)."""
+    global _EXT
+    if _EXT is None:
+        _EXT = build.load()
+    return _EXT
+
+
+def smoke_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    return ext().smoke_add(a, b)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
+    """float32 residual stream [tokens, hidden] gathered from ``table`` rows."""
+    hidden = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    ext().embedding(ids, table, hidden, status)
+    return hidden
+
+
+def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+                status: torch.Tensor | None = None) -> torch.Tensor:
+    """``hidden += delta`` in place (whole-batch form), then RMSNorm times ``weight``.
+
+    With ``rows`` only those rows are normalised (``hidden`` is left as it is) and the
+    result is [len(rows), hidden].
+    """
+    n = hidden.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, hidden.shape[1]), dtype=out_dtype, device=hidden.device)
+    ext().add_rmsnorm(hidden, delta, weight, out, rows, float(eps), status)
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    out = torch.empty((gate_up.shape[0], gate_up.shape[1] // 2), dtype=gate_up.dtype, device=gate_up.device)
+    ext().silu_mul(gate_up, out)
+    return out
+
+
+def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache, *, num_heads,
+                       num_kv_heads, head_dim, rotary_dim, eps, want_kv: bool = False, status=None):
+    """Per-head RMSNorm of q and k, rotation by position, K/V written to their cache slots.
+
+    Returns q [tokens, heads * head_dim] (and the dense k, v when ``want_kv``).
+    """
+    n = qkv.shape[0]
+    q_out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    k_out = v_out = None
+    if want_kv:
+        k_out = torch.empty((n, num_kv_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        v_out = torch.empty_like(k_out)
+    ext().qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, q_out, k_out, v_out, k_cache,
+                             v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), status)
+    return (q_out, k_out, v_out) if want_kv else q_out
+
+
+def kv_write(k, v, slots, k_cache, v_cache, status=None) -> None:
+    ext().kv_write(k, v, slots, k_cache, v_cache, status)
+
+
+def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
+                  target_warps: int = 148 * 16) -> int:
+    """How many key ranges each query tile is cut into so that a small batch still fills the GPU."""
+    items = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8))
+    if items >= target_warps or max_context <= 256:
+        return 1
+    want = (target_warps + items - 1) // items
+    return int(max(1, min(want, (max_context + 255) // 256, 64)))
+
+
+def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
+                    q_tile, num_splits, num_heads, num_kv_heads, window, scale, partials=None, status=None):
+    out = torch.empty_like(q)
+    if num_splits > 1 and partials is None:
+        head_dim = q.shape[1] // num_heads
+        partials = torch.empty((q.shape[0] * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32,
+                               device=q.device)
+    ext().paged_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
+                          partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(window or 0),
+                          float(scale), status)
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
+    tokens = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    ext().sample(logits, temperature, uniform, tokens)
+    return tokens
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` by the library GEMM, float32 accumulation.
+
+    ``out_dtype=torch.float32`` with bfloat16 operands keeps the accumulator's precision in
+    the result (used for the logits).
+    """
+    if out_dtype is not None and out_dtype != x.dtype:
+        out = torch.mm(x, weight.t(), out_dtype=out_dtype)
+        if bias is not None:
+            out += bias.to(out_dtype)
+        return out
+    return torch.nn.functional.linear(x, weight, bias)

@@ -1,0 +1,97 @@
+"""A decoder assembled from a :class:`ModelSpec`: embedding, layers run in the schedule's order,
+final norm and head on the rows whose logits are wanted.
+
+This is the one forward pass of the package (the reference has three, one per batch shape:
+ampere_kv/runner.py:219-290).  It runs exactly the tokens of the step's batch, reads earlier
+tokens only through the cache, and returns float32 logits for ``ctx.logit_rows``
+(the reference returns the last position only, runner.py:293-297).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import ModelSpec, PartSpec
+from ..parts import attention, block, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheSpec, ParamSpec, build_part)
+from ..parts.embedding import LinearHead, TokenEmbedding
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, *, dtype: torch.dtype, device: torch.device | str):
+        spec.validate()
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, got {dtype}")
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        kw = dict(hidden_size=spec.hidden_size, dtype=dtype, device=self.device)
+        self.embedding = TokenEmbedding(spec.embedding, **kw)
+        self.blocks = []
+        for layer in spec.layers:
+            mixer = build_part(MIXERS, layer.mixer, **kw)
+            ff = build_part(FEED_FORWARDS, layer.feed_forward, **kw)
+            n1 = build_part(NORMS, layer.mixer_norm, **kw)
+            n2 = build_part(NORMS, layer.feed_forward_norm, **kw)
+            self.blocks.append(BLOCKS.get(layer.block)(mixer, ff, n1, n2))
+        self.final_norm = build_part(NORMS, spec.final_norm, **kw)
+        self.head = LinearHead(spec.head, **kw)
+        self.loaded = False
+
+    # ------------------------------------------------------------------ tensors
+
+    def _parts(self):
+        yield self.embedding
+        for blk in self.blocks:
+            yield blk.mixer_norm
+            yield blk.mixer
+            yield blk.feed_forward_norm
+            yield blk.feed_forward
+        yield self.final_norm
+        yield self.head
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        """Every tensor of the checkpoint by its full name."""
+        out: dict[str, ParamSpec] = {}
+        for part in self._parts():
+            for local, ps in part.param_specs().items():
+                name = f"{part.spec.prefix}.{local}" if part.spec.prefix else local
+                if name in out and out[name] != ps:
+                    raise ValueError(f"tensor {name} is declared twice with different shapes")
+                out[name] = ps
+        return out
+
+    def load_tensors(self, tensors: dict[str, torch.Tensor]) -> None:
+        """``tensors``: full name -> tensor, already validated, cast and on the device."""
+        for part in self._parts():
+            local = {}
+            for name in part.param_specs():
+                full = f"{part.spec.prefix}.{name}" if part.spec.prefix else name
+                if full in tensors:
+                    local[name] = tensors[full]
+            part.load(local)
+        self.head.tie(self.embedding)
+        self.loaded = True
+
+    # ------------------------------------------------------------------ cache needs
+
+    def cache_specs(self) -> list[CacheSpec]:
+        """One per schedule position."""
+        return [self.blocks[e.layer].mixer.cache_spec() for e in self.spec.schedule]
+
+    def cache_of(self) -> list[int | None]:
+        return [e.cache_of for e in self.spec.schedule]
+
+    # ------------------------------------------------------------------ forward
+
+    @torch.no_grad()
+    def forward(self, ctx, cache_views) -> torch.Tensor | None:
+        """Run the step's tokens through the schedule; logits [wanted, vocab] float32, or None if none wanted."""
+        hidden = self.embedding.forward(ctx.token_ids, ctx)
+        delta = None
+        for pos, entry in enumerate(self.spec.schedule):
+            hidden, delta = self.blocks[entry.layer].forward(hidden, delta, ctx, cache_views[pos])
+        if ctx.num_logit_rows == 0:
+            return None
+        normed = self.final_norm.forward(hidden, delta, ctx, rows=ctx.logit_rows)
+        return self.head.forward(normed)

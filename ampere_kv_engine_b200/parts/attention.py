@@ -1,0 +1,112 @@
+"""Grouped-query attention over the paged cache.
+
+One part covers what the reference spreads over project_qkv (ampere_kv/runner.py:60-77),
+apply_rope (runner.py:80-98), the cache write and the three attention paths of
+decoder_layer_forward (runner.py:122-152) and o_proj (runner.py:163-165): q/k/v projection
+(one product over the row-concatenated matrices), per-head RMSNorm of q and k before the
+rotation, post-rotation K and plain V written to the request's pages, causal attention of
+every new token over the pages (optionally only the last ``window`` keys), output projection.
+Prompt portions and decoded tokens of many requests go through the same two kernels.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import (POSITION_ENCODINGS, CacheSpec, Mixer, ParamSpec, build_part, register_mixer)
+
+
+@register_mixer("attention")
+class PagedAttention(Mixer):
+    """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qk_norm`` (bool), ``qk_norm_eps``,
+    ``bias`` (bool), ``window`` (keys visible including the query's own, or None),
+    ``scale`` (None = head_dim ** -0.5), ``position_encoding`` (a PartSpec)."""
+
+    def __init__(self, spec, **kw):
+        super().__init__(spec, **kw)
+        p = spec.params
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
+        self.bias = bool(p.get("bias", False))
+        self.window = p.get("window")
+        if self.window is not None and int(self.window) <= 0:
+            raise ValueError(f"attention: window must be positive, got {self.window}")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else self.head_dim ** -0.5
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"attention: {self.num_heads} heads are not a multiple of {self.num_kv_heads} kv heads")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ValueError(f"attention: head_dim must be a multiple of 16 up to 256 for the attention kernels, "
+                             f"got {self.head_dim}")
+        self.position_encoding = build_part(POSITION_ENCODINGS, p["position_encoding"], hidden_size=self.hidden_size,
+                                            dtype=self.dtype, device=self.device)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm_weight = self.k_norm_weight = None
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(kind="window" if self.window is not None else "full", num_kv_heads=self.num_kv_heads,
+                         head_dim=self.head_dim, window=None if self.window is None else int(self.window))
+
+    def param_specs(self):
+        h, d = self.hidden_size, self.head_dim
+        specs = {
+            "q_proj.weight": ParamSpec((self.num_heads * d, h)),
+            "k_proj.weight": ParamSpec((self.num_kv_heads * d, h)),
+            "v_proj.weight": ParamSpec((self.num_kv_heads * d, h)),
+            "o_proj.weight": ParamSpec((h, self.num_heads * d)),
+        }
+        if self.bias:
+            specs["q_proj.bias"] = ParamSpec((self.num_heads * d,), kind="bias")
+            specs["k_proj.bias"] = ParamSpec((self.num_kv_heads * d,), kind="bias")
+            specs["v_proj.bias"] = ParamSpec((self.num_kv_heads * d,), kind="bias")
+            specs["o_proj.bias"] = ParamSpec((h,), kind="bias")
+        if self.qk_norm:
+            specs["q_norm.weight"] = ParamSpec((d,), kind="vector", init="norm")
+            specs["k_norm.weight"] = ParamSpec((d,), kind="vector", init="norm")
+        return specs
+
+    def load(self, tensors):
+        self.w_qkv = torch.cat((tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]),
+                               dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if self.bias:
+            self.b_qkv = torch.cat((tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"])).contiguous()
+            self.b_o = tensors["o_proj.bias"].contiguous()
+        if self.qk_norm:
+            self.q_norm_weight = tensors["q_norm.weight"]
+            self.k_norm_weight = tensors["k_norm.weight"]
+
+    def forward(self, x, ctx, cache):
+        group = ctx.groups[cache.group]
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        slots = group.slot_mapping if cache.writes else None
+        k_cache = cache.k_cache if cache.writes else None
+        v_cache = cache.v_cache if cache.writes else None
+        fused = self.position_encoding.fused_rotary()
+        if fused is not None:
+            inv_freq, rotary_dim = fused
+            q = ops.qk_norm_rope_write(
+                qkv, ctx.positions, slots, self.q_norm_weight, self.k_norm_weight, inv_freq, k_cache, v_cache,
+                num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                rotary_dim=rotary_dim, eps=self.qk_norm_eps, status=ctx.status)
+        else:
+            # an encoding that is not a fused rotation: norm, encode on dense q/k, then write the pages
+            q, k, v = ops.qk_norm_rope_write(
+                qkv, ctx.positions, None, self.q_norm_weight, self.k_norm_weight, None, None, None,
+                num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, rotary_dim=0,
+                eps=self.qk_norm_eps, want_kv=True, status=ctx.status)
+            q, k = self.position_encoding.apply(q, k, ctx.positions)
+            if cache.writes:
+                ops.kv_write(k.contiguous(), v, group.slot_mapping, cache.k_cache, cache.v_cache, status=ctx.status)
+            q = q.contiguous()
+        group_size = self.num_heads // self.num_kv_heads
+        splits = ops.choose_splits(ctx.num_tiles, self.num_kv_heads, ctx.q_tile * group_size,
+                                   ctx.max_context)
+        out = ops.paged_attention(
+            q, cache.k_cache, cache.v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq, ctx.tile_q0,
+            ctx.tile_nq, num_tiles=ctx.num_tiles, q_tile=ctx.q_tile, num_splits=splits,
+            num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, window=self.window or 0, scale=self.scale,
+            status=ctx.status)
+        return ops.linear(out, self.w_o, self.b_o)

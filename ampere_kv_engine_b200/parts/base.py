@@ -1,0 +1,169 @@
+"""Interfaces and registries of the parts a model is put together from.
+
+A part is built from a :class:`~ampere_kv_engine_b200.config.spec.PartSpec` (its kind and
+its sizes and constants), declares the tensors it wants by local name, receives them, and
+computes on the flat token batch of one step.  Parts never look at a model configuration
+and do not know which architecture uses them; the reference, by contrast, wires one model's
+attribute paths into every function (ampere_kv/runner.py:60-77, 102-179).
+
+Kinds are looked up in five registries (mixers, feed-forwards, norms, position encodings,
+blocks).  Registering a new kind is one decorator call and needs no change here.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """One tensor a part wants from the checkpoint.
+
+    ``kind``: ``"matrix"`` and ``"bias"`` (kept in the compute dtype), ``"vector"`` (norm
+    weights: always float32 on the device, an exact widening of what is stored; a tensor
+    stored in 32-bit stays 32-bit) or ``"table"`` (integer tables, int32).  ``init`` names the random draw of the random-weights mode.
+    """
+
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+    init: str = "normal"        # "normal": N(0, 0.02); "norm": 1 + N(0, 0.1); "zeros"
+    optional: bool = False
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """What a mixer needs the cache manager to keep for each request.
+
+    ``kind``: ``"none"``, ``"full"`` (keys/values of every position) or ``"window"`` (only
+    the last ``window`` positions are ever read, pages behind it are given back).
+    ``state_shape`` asks for a fixed-size float32 state per request (``()`` = none).
+    Mixers whose specs are equal share a cache group: one page pool, one block table per
+    request.
+    """
+
+    kind: str = "none"
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    window: int | None = None
+    state_shape: tuple[int, ...] = ()
+
+    def group_key(self) -> tuple:
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+
+
+class Part:
+    """Common life cycle: build from a spec, declare tensors, load them."""
+
+    def __init__(self, spec: PartSpec, *, hidden_size: int, dtype: torch.dtype, device: torch.device):
+        self.spec = spec
+        self.hidden_size = hidden_size
+        self.dtype = dtype
+        self.device = device
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        """Tensors wanted, by name relative to ``spec.prefix``."""
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Receive the tensors of :meth:`param_specs` (already on the device, cast per kind)."""
+
+
+class Norm(Part):
+    def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None
+                ) -> torch.Tensor:
+        """Add ``delta`` into the float32 residual stream ``hidden`` (in place) and return the
+        normalised activations in the compute dtype.  With ``rows`` only those rows are
+        normalised and ``hidden`` is not changed."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """How positions enter a mixer.  ``fused_rotary()`` returns ``(inv_freq, rotary_dim)`` when
+    the fused q/k kernel can apply the encoding itself (a rotate-half rotation, or nothing:
+    ``(None, 0)``), else None; then :meth:`apply` is called on dense q and k
+    ([tokens, heads * head_dim]) before k is written to the cache."""
+
+    def fused_rotary(self) -> tuple[torch.Tensor, int] | None:
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        return q, k
+
+
+class Mixer(Part):
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec()
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        """x: [tokens, hidden] in the compute dtype; ``ctx`` is the step's batch
+        (:class:`~ampere_kv_engine_b200.engine.batch.StepContext`); ``cache`` is this schedule
+        position's :class:`~ampere_kv_engine_b200.cache.manager.LayerCacheView`."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of one layer's parts around the residual stream."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx, cache
+                ) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """Takes the residual stream and a not-yet-added branch output; returns the same pair."""
+        raise NotImplementedError
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: dict[str, Callable[..., Any]] = {}
+
+    def register(self, kind: str):
+        def wrap(cls):
+            if kind in self._kinds and self._kinds[kind] is not cls:
+                raise ValueError(f"{self.what} kind {kind!r} is already registered")
+            self._kinds[kind] = cls
+            return cls
+        return wrap
+
+    def unregister(self, kind: str) -> None:
+        self._kinds.pop(kind, None)
+
+    def get(self, kind: str):
+        if kind not in self._kinds:
+            raise KeyError(f"unknown {self.what} kind {kind!r}; registered: {sorted(self._kinds)}")
+        return self._kinds[kind]
+
+    def kinds(self) -> list[str]:
+        return sorted(self._kinds)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")
+
+register_mixer = MIXERS.register
+register_feed_forward = FEED_FORWARDS.register
+register_norm = NORMS.register
+register_position_encoding = POSITION_ENCODINGS.register
+register_block = BLOCKS.register
+
+
+def build_part(registry: Registry, spec: PartSpec, *, hidden_size: int, dtype: torch.dtype,
+               device: torch.device):
+    return registry.get(spec.kind)(spec, hidden_size=hidden_size, dtype=dtype, device=device)

@@ -1,0 +1,86 @@
+"""Trace replay: feed given token ids through a model step by step and write the logits.
+
+It samples nothing and owns no forward pass, cache or loader: it builds the same model,
+:class:`~ampere_kv_engine_b200.engine.step.ModelRunner` (step function, cache manager,
+kernels) that generation uses and calls its step function directly.  The reference's nearest
+relatives are its checks that feed a prompt whole versus in chunks, and a mixed batch versus
+separate ones (ampere_kv/check_chunked.py:69-111, ampere_kv/check_mixed.py:58-117).
+
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+
+Standard input carries one JSON object a line:
+
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
+
+Every entry continues its request where it stopped; ``want`` names places among the entry's
+tokens whose logits are written (in entry order, then ``want`` order) to ``<out>/<step>.f32``
+as little-endian float32 [wanted, vocab].  Requests named in ``end`` give back what they hold
+after the step.  After every step a line ``done <step>`` is printed and flushed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
+    parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16",
+                        help="bfloat16: the kernels and precisions of serving; float32: everything in true 32-bit")
+    parser.add_argument("--out", required=True, help="folder the <step>.f32 files are written to")
+    parser.add_argument("--max-tokens", type=int, required=True,
+                        help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+    parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
+    parser.add_argument("--device", default="cuda")
+    args = parser.parse_args(argv)
+    if args.max_tokens <= 0:
+        parser.error("--max-tokens must be positive")
+    if 64 % args.page_size and args.page_size % 64:
+        parser.error("--page-size must divide 64 or be a multiple of it")
+
+    from .engine.batch import SeqStep
+    from .engine.engine import Engine
+
+    os.makedirs(args.out, exist_ok=True)
+    round_to = max(64, args.page_size)
+    num_pages = (args.max_tokens + round_to - 1) // round_to * round_to // args.page_size
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, device=args.device, page_size=args.page_size,
+                                    num_pages=num_pages, max_seqs=8)
+    runner = engine.runner
+    live: dict[str, object] = {}
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        record = json.loads(line)
+        step = record["step"]
+        entries = []
+        for item in record.get("entries", []):
+            rid = str(item["id"])
+            if rid not in live:
+                live[rid] = runner.open(rid)
+            entries.append(SeqStep(live[rid], [int(t) for t in item["tokens"]], [int(w) for w in item.get("want", [])]))
+        if entries:
+            logits = runner.step(entries)
+            if logits is not None:
+                host = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+                with open(os.path.join(args.out, f"{step}.f32"), "wb") as handle:
+                    handle.write(np.ascontiguousarray(host).tobytes())
+            runner.raise_on_status()
+        for rid in record.get("end", []):
+            rid = str(rid)
+            if rid in live:
+                runner.close(live.pop(rid))
+        print(f"done {step}", flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
