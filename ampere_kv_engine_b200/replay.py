@@ -29,7 +29,9 @@ import numpy as np
 import torch
 
 
-def main(argv=None) -> int:
+def main(argv=None, stdin=None, stdout=None) -> int:
+    stdin = sys.stdin if stdin is None else stdin
+    stdout = sys.stdout if stdout is None else stdout
     parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16",
@@ -55,7 +57,7 @@ def main(argv=None) -> int:
                                     num_pages=num_pages, max_seqs=8)
     runner = engine.runner
     live: dict[str, object] = {}
-    for line in sys.stdin:
+    for line in stdin:
         line = line.strip()
         if not line:
             continue
@@ -78,7 +80,7 @@ def main(argv=None) -> int:
             rid = str(rid)
             if rid in live:
                 runner.close(live.pop(rid))
-        print(f"done {step}", flush=True)
+        print(f"done {step}", file=stdout, flush=True)
     return 0
 
 

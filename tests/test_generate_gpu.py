@@ -1,0 +1,126 @@
+"""Generation through the Python entry point and the command line: greedy equals the plain model's greedy
+loop, temperature sampling is reproducible and independent of the batch, requests that do not fit wait."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import tiny
+from models_util import model_folder, plain_weights
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def prompts_for(name, lengths, seed=7):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, tiny.CONFIGS[name][0]["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("name,lengths", [("A", (5, 17, 33)), ("B", (1, 31, 64, 130))])
+def test_greedy_generation_equals_plain(name, lengths):
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = tiny.CONFIGS[name]
+    folder = model_folder(name)
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=page, num_pages=40, max_batch_tokens=24)
+    prompts = prompts_for(name, lengths)
+    got = engine.generate(prompts, max_new_tokens=8, ignore_eos=True)
+    w = plain_weights(folder, "float32")
+    assert got == [plain.greedy_generate(w, raw, p, 8) for p in prompts]
+    assert engine.manager.free_pages() == [40] * len(engine.manager.groups)
+    engine.manager.check_invariants()
+
+
+def test_bfloat16_greedy_generation_close_to_plain():
+    """bfloat16 may pick another token where two logits are within rounding; every pick must still be
+    (nearly) the best token of the plain model given the same history."""
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = tiny.CONFIGS["A"]
+    folder = model_folder("A")
+    engine = Engine.from_pretrained(folder, dtype="bfloat16", page_size=page, num_pages=40)
+    prompts = prompts_for("A", (5, 17, 33))
+    got = engine.generate(prompts, max_new_tokens=8, ignore_eos=True)
+    w = plain_weights(folder, "bfloat16")
+    for prompt, out in zip(prompts, got):
+        ids = list(prompt)
+        for token in out:
+            logits = plain.forward_logits(w, raw, ids)[-1]
+            assert float(logits.max() - logits[token]) <= 3e-2
+            ids.append(token)
+
+
+def test_eos_stops_and_limit_stops():
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = tiny.CONFIGS["A"]
+    folder = model_folder("A")
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=page, num_pages=40)
+    prompt = prompts_for("A", (9,))[0]
+    free_run = engine.generate([prompt], max_new_tokens=12, ignore_eos=True)[0]
+    engine.eos_token_ids = (free_run[4],)
+    stopped = engine.generate([prompt], max_new_tokens=12)[0]
+    first = free_run.index(free_run[4])
+    assert stopped == free_run[:first + 1]
+
+
+def test_temperature_sampling_reproducible_and_batch_independent():
+    from ampere_kv_engine_b200.engine.engine import Engine
+    from ampere_kv_engine_b200.sampling.sampler import SamplingParams
+    raw, page = tiny.CONFIGS["B"]
+    folder = model_folder("B")
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=page, num_pages=64, max_batch_tokens=24)
+    prompts = prompts_for("B", (1, 31, 64, 130))
+    a = engine.generate(prompts, max_new_tokens=10, temperature=0.8, seed=1234, ignore_eos=True)
+    b = engine.generate(prompts, max_new_tokens=10, temperature=0.8, seed=1234, ignore_eos=True)
+    assert a == b
+    assert a != engine.generate(prompts, max_new_tokens=10, temperature=0.8, seed=99, ignore_eos=True)
+    # the same request alone (same seed and stream) draws the same tokens
+    scheduler = engine.new_scheduler()
+    alone = scheduler.submit("solo", prompts[2], 10, sampling=SamplingParams(0.8, 1234, stream=2), ignore_eos=True)
+    while scheduler.has_work():
+        scheduler.step()
+    assert alone.output_ids == a[2]
+    # and each draw is the plain inverse-CDF pick for the plain logits (up to ties at rounding level)
+    w = plain_weights(folder, "float32")
+    ids = list(prompts[1])
+    for step, token in enumerate(a[1]):
+        logits = plain.forward_logits(w, raw, ids)[-1]
+        u = plain.uniform_from_key(1234, 1, step)
+        cdf = plain.temperature_cdf(logits, 0.8)
+        lo = float(cdf[token - 1]) if token else 0.0
+        assert lo - 1e-4 <= u <= float(cdf[token]) + 1e-4
+        ids.append(token)
+
+
+def test_requests_wait_for_pages_and_all_finish():
+    """Pages for two requests at a time only: the others wait in arrival order; all finish with the tokens they
+    get when run alone; every page comes back."""
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = tiny.CONFIGS["A"]
+    folder = model_folder("A")
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=page, num_pages=8, max_batch_tokens=16)
+    prompts = prompts_for("A", (40, 33, 20, 45, 9))
+    together = engine.generate(prompts, max_new_tokens=6, ignore_eos=True)
+    alone = [engine.generate([p], max_new_tokens=6, ignore_eos=True)[0] for p in prompts]
+    assert together == alone
+    assert engine.manager.free_pages() == [8]
+
+
+def test_command_line_generate(tmp_path):
+    folder = model_folder("A")
+    prompt = prompts_for("A", (12,))[0]
+    ids_file = tmp_path / "prompt.json"
+    ids_file.write_text(json.dumps(prompt))
+    cmd = [sys.executable, "-m", "ampere_kv_engine_b200.runner", "--model", folder, "--mode", "generate",
+           "--cache", "paged", "--kv-dtype", "fp32", "--dtype", "float32", "--prompt-ids", str(ids_file),
+           "--max-new-tokens", "5", "--ignore-eos"]
+    proc = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("generated_token_ids = ")][0]
+    got = json.loads(line.split(" = ", 1)[1])
+    w = plain_weights(folder, "float32")
+    assert got == plain.greedy_generate(w, tiny.CONFIGS["A"][0], prompt, 5)

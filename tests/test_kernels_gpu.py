@@ -1,0 +1,351 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes other than the
+tiny models' (head sizes 48/80/128/256, group sizes 1/2/3/8, widths and vocabularies that are no power
+of two), in float32 and bfloat16."""
+
+import math
+
+import pytest
+import torch
+
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=1.6e-2, rtol=1.6e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ampere_kv_engine_b200.kernels import ops as module
+    module.ext()
+    return module
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def status_word():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def test_smoke_add(ops):
+    a, b = torch.randn(1000), torch.randn(1000)
+    torch.testing.assert_close(ops.smoke_add(dev(a), dev(b)).cpu(), a + b, atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(777, 200, generator=g).to(dtype)
+    ids = torch.randint(0, 777, (53,), generator=g, dtype=torch.int32)
+    status = status_word()
+    out = ops.embedding(dev(ids), dev(table), status=status)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), table.float()[ids.long()], atol=0, rtol=0)
+    assert int(status.item()) == 0
+
+
+def test_embedding_reports_a_bad_token_without_faulting(ops):
+    table = torch.randn(10, 32)
+    ids = torch.tensor([1, 10, 3], dtype=torch.int32)     # 10 is outside the vocabulary
+    status = status_word()
+    out = ops.embedding(dev(ids), dev(table), status=status)
+    assert int(status.item()) == 3
+    torch.testing.assert_close(out.cpu()[[0, 2]], table[[1, 3]], atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 200, 4096, 5120])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_add_rmsnorm(ops, dtype, hidden, with_delta):
+    g = torch.Generator().manual_seed(hidden)
+    h = torch.randn(19, hidden, generator=g)
+    delta = torch.randn(19, hidden, generator=g).to(dtype) if with_delta else None
+    w = 1 + 0.1 * torch.randn(hidden, generator=g)
+    eps = 1e-5
+    h_dev = dev(h.clone())
+    out = ops.add_rmsnorm(h_dev, dev(delta) if with_delta else None, dev(w), eps, dtype)
+    summed = h + (delta.float() if with_delta else 0)
+    torch.testing.assert_close(h_dev.cpu(), summed, atol=0, rtol=0)       # the residual sum is exact float32
+    want = plain.rms_norm(summed, w, eps)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+    # gathered form: chosen rows only, the stream is left alone
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32)
+    h_dev = dev(h.clone())
+    out = ops.add_rmsnorm(h_dev, dev(delta) if with_delta else None, dev(w), eps, dtype, rows=dev(rows))
+    torch.testing.assert_close(h_dev.cpu(), h, atol=0, rtol=0)
+    torch.testing.assert_close(out.float().cpu(), want[rows.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    g = torch.Generator().manual_seed(1)
+    gu = (3 * torch.randn(37, 2 * 300, generator=g)).to(dtype)
+    out = ops.silu_mul(dev(gu))
+    want = torch.nn.functional.silu(gu.float()[:, :300]) * gu.float()[:, 300:]
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
+def _qkv_reference(qkv, positions, q_w, k_w, nh, nkv, d, eps, theta):
+    n = qkv.shape[0]
+    x = qkv.float().view(n, nh + 2 * nkv, d)
+    q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+    q, k = plain.rms_norm(q, q_w, eps), plain.rms_norm(k, k_w, eps)
+    inv = plain.rope_inverse_frequencies(d, theta)
+    return plain.apply_rope(q, positions, inv), plain.apply_rope(k, positions, inv), v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,page", [(6, 3, 48, 8), (8, 1, 128, 16), (4, 4, 80, 32), (2, 1, 256, 16)])
+def test_qk_norm_rope_write(ops, dtype, nh, nkv, d, page):
+    g = torch.Generator().manual_seed(d)
+    n, pages, eps, theta = 29, 12, 1e-5, 50000.0
+    qkv = torch.randn(n, (nh + 2 * nkv) * d, generator=g).to(dtype)
+    positions = torch.randint(0, 3000, (n,), generator=g, dtype=torch.int32)
+    q_w = 1 + 0.1 * torch.randn(d, generator=g)
+    k_w = 1 + 0.1 * torch.randn(d, generator=g)
+    slots = torch.randperm(pages * page, generator=g)[:n].to(torch.int32)
+    slots[5] = -1                                            # a token whose K/V must not be written
+    k_cache = torch.full((pages, nkv, page, d), float("nan")).to(dtype)
+    v_cache = k_cache.clone()
+    k_dev, v_dev = dev(k_cache), dev(v_cache)
+    inv_freq = plain.rope_inverse_frequencies(d, theta)
+    status = status_word()
+    q, k_dense, v_dense = ops.qk_norm_rope_write(
+        dev(qkv), dev(positions), dev(slots), dev(q_w), dev(k_w), dev(inv_freq), k_dev, v_dev, num_heads=nh,
+        num_kv_heads=nkv, head_dim=d, rotary_dim=d, eps=eps, want_kv=True, status=status)
+    assert int(status.item()) == 0
+    q_ref, k_ref, v_ref = _qkv_reference(qkv, positions, q_w, k_w, nh, nkv, d, eps, theta)
+    torch.testing.assert_close(q.float().cpu().view(n, nh, d), q_ref, **tol(dtype))
+    torch.testing.assert_close(k_dense.float().cpu().view(n, nkv, d), k_ref, **tol(dtype))
+    torch.testing.assert_close(v_dense.float().cpu().view(n, nkv, d), v_ref, atol=0, rtol=0)
+    k_host, v_host = k_dev.cpu(), v_dev.cpu()
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    for t in range(n):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        written[s // page, s % page] = True
+        # the pages hold exactly what the dense outputs hold: post-rotation K, un-rotated V
+        torch.testing.assert_close(k_host[s // page, :, s % page], k_dense.cpu().view(n, nkv, d)[t], atol=0, rtol=0)
+        torch.testing.assert_close(v_host[s // page, :, s % page], v_dense.cpu().view(n, nkv, d)[t], atol=0, rtol=0)
+    untouched = ~written[:, None, :, None].expand_as(k_host)
+    assert bool(torch.isnan(k_host.float()[untouched]).all()), "a slot that no token owns was written"
+    assert bool(torch.isnan(v_host.float()[untouched]).all())
+
+
+def test_qk_partial_rotation_and_no_rotation(ops):
+    """rotary_dim < head_dim rotates pairs (j, j + rotary_dim/2) of the first rotary_dim dims only; no table = no rotation."""
+    g = torch.Generator().manual_seed(4)
+    n, nh, nkv, d, rd = 7, 3, 1, 64, 32
+    qkv = torch.randn(n, (nh + 2 * nkv) * d, generator=g)
+    positions = torch.arange(100, 100 + n, dtype=torch.int32)
+    inv = plain.rope_inverse_frequencies(rd, 10000.0)
+    q = ops.qk_norm_rope_write(dev(qkv), dev(positions), None, None, None, dev(inv), None, None, num_heads=nh,
+                               num_kv_heads=nkv, head_dim=d, rotary_dim=rd, eps=1e-6).cpu().view(n, nh, d)
+    x = qkv.view(n, nh + 2 * nkv, d)[:, :nh]
+    want = torch.cat((plain.apply_rope(x[..., :rd], positions, inv), x[..., rd:]), dim=-1)
+    torch.testing.assert_close(q, want, atol=2e-5, rtol=1e-4)
+    q = ops.qk_norm_rope_write(dev(qkv), dev(positions), None, None, None, None, None, None, num_heads=nh,
+                               num_kv_heads=nkv, head_dim=d, rotary_dim=0, eps=1e-6).cpu().view(n, nh, d)
+    torch.testing.assert_close(q, x, atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_kv_write(ops, dtype):
+    g = torch.Generator().manual_seed(2)
+    n, nkv, d, page, pages = 11, 3, 48, 8, 5
+    k = torch.randn(n, nkv * d, generator=g).to(dtype)
+    v = torch.randn(n, nkv * d, generator=g).to(dtype)
+    slots = torch.randperm(pages * page, generator=g)[:n].to(torch.int32)
+    k_cache = dev(torch.full((pages, nkv, page, d), float("nan")).to(dtype))
+    v_cache = k_cache.clone()
+    ops.kv_write(dev(k), dev(v), dev(slots), k_cache, v_cache)
+    for t in range(n):
+        s = int(slots[t])
+        torch.testing.assert_close(k_cache.cpu()[s // page, :, s % page].reshape(-1), k[t], atol=0, rtol=0)
+        torch.testing.assert_close(v_cache.cpu()[s // page, :, s % page].reshape(-1), v[t], atol=0, rtol=0)
+    assert int(torch.isnan(k_cache.float()).sum()) == (pages * page - n) * nkv * d
+
+
+class PagedCase:
+    """A ragged batch over a shuffled page pool whose unheld pages are NaN."""
+
+    def __init__(self, dtype, nh, nkv, d, page, q_lens, ctx_lens, seed=0, q_tile=16):
+        g = torch.Generator().manual_seed(seed)
+        self.nh, self.nkv, self.d, self.page = nh, nkv, d, page
+        self.q_lens, self.ctx_lens = q_lens, ctx_lens
+        pages_per_seq = [(c + page - 1) // page for c in ctx_lens]
+        pool = sum(pages_per_seq) + 5
+        order = torch.randperm(pool, generator=g).tolist()
+        self.k_seq = [torch.randn(c, nkv, d, generator=g).to(dtype) for c in ctx_lens]
+        self.v_seq = [torch.randn(c, nkv, d, generator=g).to(dtype) for c in ctx_lens]
+        self.q_seq = [torch.randn(n, nh, d, generator=g).to(dtype) for n in q_lens]
+        self.k_cache = torch.full((pool, nkv, page, d), float("nan")).to(dtype)
+        self.v_cache = self.k_cache.clone()
+        width = max(pages_per_seq)
+        self.table = torch.full((len(ctx_lens), width), -1, dtype=torch.int32)
+        for s, c in enumerate(ctx_lens):
+            for lp in range(pages_per_seq[s]):
+                pp = order.pop()
+                self.table[s, lp] = pp
+                lo, hi = lp * page, min(c, (lp + 1) * page)
+                self.k_cache[pp, :, :hi - lo] = self.k_seq[s][lo:hi].transpose(0, 1)
+                self.v_cache[pp, :, :hi - lo] = self.v_seq[s][lo:hi].transpose(0, 1)
+        cu = [0]
+        for n in q_lens:
+            cu.append(cu[-1] + n)
+        self.cu = torch.tensor(cu, dtype=torch.int32)
+        tile_rows = 1 if max(q_lens) == 1 else q_tile
+        tiles = [(s, cu[s] + q0, min(tile_rows, n - q0)) for s, n in enumerate(q_lens) for q0 in range(0, n, tile_rows)]
+        self.tile_rows = tile_rows
+        self.tiles = [torch.tensor([t[i] for t in tiles], dtype=torch.int32) for i in range(3)]
+
+    def run(self, ops, window=0, splits=1, scale=None):
+        scale = scale if scale is not None else self.d ** -0.5
+        q = torch.cat([x.reshape(x.shape[0], -1) for x in self.q_seq])
+        status = status_word()
+        out = ops.paged_attention(
+            dev(q), dev(self.k_cache), dev(self.v_cache), dev(self.table), dev(self.cu),
+            dev(torch.tensor(self.ctx_lens, dtype=torch.int32)), dev(self.tiles[0]), dev(self.tiles[1]),
+            dev(self.tiles[2]), num_tiles=len(self.tiles[0]), q_tile=self.tile_rows, num_splits=splits,
+            num_heads=self.nh, num_kv_heads=self.nkv, window=window, scale=scale, status=status)
+        assert int(status.item()) == 0
+        return out.float().cpu()
+
+    def reference(self, window=0, scale=None):
+        outs = []
+        for s, (n, c) in enumerate(zip(self.q_lens, self.ctx_lens)):
+            # whole-sequence attention with the queries placed at the last n positions
+            q_full = torch.zeros(c, self.nh, self.d)
+            q_full[c - n:] = self.q_seq[s].float()
+            if scale is not None:
+                q_full = q_full * (scale / self.d ** -0.5)
+            o = plain.causal_attention(q_full, self.k_seq[s].float(), self.v_seq[s].float(), window or None)
+            outs.append(o[c - n:].reshape(n, -1))
+        return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,page", [(6, 3, 48, 8), (8, 1, 128, 16), (4, 4, 80, 32), (4, 2, 256, 16), (9, 3, 16, 64)])
+@pytest.mark.parametrize("window", [0, 17])
+def test_paged_attention_mixed_batch(ops, dtype, nh, nkv, d, page, window):
+    case = PagedCase(dtype, nh, nkv, d, page, q_lens=[1, 37, 5, 1, 2], ctx_lens=[200, 37, 150, 1, 66], seed=d + page)
+    want = case.reference(window)
+    for splits in (1, 3):
+        torch.testing.assert_close(case.run(ops, window, splits), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_decode_batch_and_scale(ops, dtype):
+    case = PagedCase(dtype, 8, 2, 64, 16, q_lens=[1] * 7, ctx_lens=[1, 15, 16, 17, 300, 64, 65], seed=9)
+    for splits in (1, 4):
+        torch.testing.assert_close(case.run(ops, 0, splits, scale=0.2), case.reference(0, scale=0.2), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [1, 5])
+def test_paged_attention_finds_a_far_key(ops, dtype, splits):
+    """One key among 700 is made to dominate: the output must be (almost) that key's value row.  A kernel that
+    dropped, duplicated or misplaced a page would miss it."""
+    case = PagedCase(dtype, 4, 2, 64, 16, q_lens=[1, 3], ctx_lens=[700, 300], seed=3)
+    far = 37
+    for s in range(2):
+        for kv in range(2):
+            direction = torch.nn.functional.normalize(case.k_seq[s][far, kv].float(), dim=0)
+            for h in (2 * kv, 2 * kv + 1):
+                case.q_seq[s][:, h] = (60.0 * direction).to(dtype)
+            case.k_seq[s][far, kv] = (8.0 * direction).to(dtype)
+            pp = int(case.table[s, far // 16])
+            case.k_cache[pp, kv, far % 16] = case.k_seq[s][far, kv]
+    out = case.run(ops, 0, splits)
+    want = case.reference(0)
+    torch.testing.assert_close(out, want, **tol(dtype))
+    row = out[0].view(4, 64)
+    for h in range(4):
+        torch.testing.assert_close(row[h], case.v_seq[0][far, h // 2].float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_window_edge(ops, dtype):
+    """The key just inside the window dominates one query, the key just outside would dominate if it were seen."""
+    window = 24
+    case = PagedCase(dtype, 2, 1, 32, 8, q_lens=[4], ctx_lens=[100], seed=5)
+    pos = 99                                   # last query; sees keys 76..99
+    inside, outside = pos - window + 1, pos - window
+    direction = torch.nn.functional.normalize(torch.randn(32, generator=torch.Generator().manual_seed(1)), dim=0)
+    for key, gain in ((inside, 6.0), (outside, 12.0)):
+        case.k_seq[0][key, 0] = (gain * direction).to(dtype)
+        case.k_cache[int(case.table[0, key // 8]), 0, key % 8] = case.k_seq[0][key, 0]
+    case.q_seq[0][:, :] = (40.0 * direction).to(dtype)
+    out = case.run(ops, window)
+    torch.testing.assert_close(out, case.reference(window), **tol(dtype))
+    torch.testing.assert_close(out[3].view(2, 32)[0], case.v_seq[0][inside, 0].float(), atol=2e-2, rtol=2e-2)
+
+
+def test_paged_attention_reports_a_bad_page_without_faulting(ops):
+    case = PagedCase(torch.float32, 2, 1, 32, 8, q_lens=[1], ctx_lens=[20], seed=6)
+    case.table[0, 1] = 10 ** 6                   # far outside the pool
+    q = case.q_seq[0].reshape(1, -1)
+    status = status_word()
+    ops.paged_attention(dev(q), dev(case.k_cache), dev(case.v_cache), dev(case.table), dev(case.cu),
+                        dev(torch.tensor([20], dtype=torch.int32)), dev(case.tiles[0]), dev(case.tiles[1]),
+                        dev(case.tiles[2]), num_tiles=1, q_tile=1, num_splits=1, num_heads=2, num_kv_heads=1,
+                        window=0, scale=1.0, status=status)
+    assert int(status.item()) == 1
+
+
+def test_kernels_refuse_sizes_they_do_not_take(ops):
+    q = torch.zeros(1, 2 * 24, device="cuda")
+    cache = torch.zeros(2, 1, 8, 24, device="cuda")
+    i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ops.paged_attention(q, cache, cache, i32(0).view(1, 1), i32(0, 1), i32(1), i32(0), i32(0), i32(1),
+                            num_tiles=1, q_tile=1, num_splits=1, num_heads=2, num_kv_heads=1, window=0, scale=1.0)
+    with pytest.raises(RuntimeError, match="exceeds"):
+        h = torch.zeros(1, 60000, device="cuda")
+        ops.add_rmsnorm(h, None, torch.ones(60000, device="cuda"), 1e-6, torch.float32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.silu_mul(torch.zeros(2, 8))
+
+
+def _cdf_interval_ok(logits, temperature, u, token):
+    cdf = plain.temperature_cdf(logits, temperature)
+    lo = float(cdf[token - 1]) if token > 0 else 0.0
+    hi = float(cdf[token])
+    slack = 1e-5
+    return lo - slack <= u * float(cdf[-1]) <= hi + slack
+
+
+@pytest.mark.parametrize("vocab", [1000, 151936])
+def test_sample_greedy_and_temperature(ops, vocab):
+    g = torch.Generator().manual_seed(vocab)
+    rows = 9
+    logits = 3 * torch.randn(rows, vocab, generator=g)
+    logits[0, 17] = logits[0, 900] = 50.0              # a tie: the lowest index wins
+    temps = torch.tensor([0.0, 0.0, 0.8, 0.8, 1.5, 0.1, 1.0, 0.8, 0.8])
+    us = torch.tensor([0.0, 0.0, 0.0, 0.999999, 0.5, 0.3, 0.77, 0.123, 0.5])
+    tokens = ops.sample(dev(logits), dev(temps), dev(us)).cpu().tolist()
+    assert tokens[0] == 17
+    assert tokens[1] == int(logits[1].argmax())
+    for r in range(2, rows):
+        assert _cdf_interval_ok(logits[r], float(temps[r]), float(us[r]), tokens[r]), (r, tokens[r])
+        assert tokens[r] == plain.sample_temperature(logits[r], float(temps[r]), float(us[r])) or \
+            _cdf_interval_ok(logits[r], float(temps[r]), float(us[r]), tokens[r])
+    again = ops.sample(dev(logits), dev(temps), dev(us)).cpu().tolist()
+    assert again == tokens
+
+
+def test_sample_distribution(ops):
+    """Many draws over a small vocabulary follow softmax(logits / T)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]])
+    n = 4000
+    us = (torch.arange(n) + 0.5) / n
+    tokens = ops.sample(dev(logits.expand(n, 5).contiguous()), dev(torch.full((n,), 0.7)), dev(us)).cpu()
+    freq = torch.bincount(tokens.long(), minlength=5).float() / n
+    torch.testing.assert_close(freq, torch.softmax(logits[0] / 0.7, -1), atol=2e-3, rtol=0)

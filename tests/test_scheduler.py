@@ -1,0 +1,223 @@
+"""The scheduler's decisions, with a stub in place of the model: admission in arrival order against the page
+budget, prompts cut into portions under the token budget beside decoded tokens, finishing and freeing,
+cancel and deadline at round starts, and what happens when pages run out (wait / preempt and recompute /
+give up)."""
+
+import pytest
+import torch
+
+from ampere_kv_engine_b200.cache.manager import CacheManager
+from ampere_kv_engine_b200.engine.scheduler import (FINISHED, PREFILLING, RUNNING, WAITING, Scheduler)
+from ampere_kv_engine_b200.parts.base import CacheSpec
+from ampere_kv_engine_b200.sampling.sampler import SamplingParams
+
+VOCAB = 101
+
+
+class StubExecutor:
+    """Does what the real step does to the cache (reserve, commit) and 'predicts' a token that depends on
+    every token the request has been fed so far, so a recomputed request must come out the same."""
+
+    def __init__(self, pages=16, page=16, seqs=8, specs=None):
+        specs = specs or [CacheSpec("full", 2, 16)]
+        self.manager = CacheManager(specs, [None] * len(specs), page_size=page, num_pages=pages, max_seqs=seqs,
+                                    dtype=torch.float32, device="cpu", allocate_storage=False)
+        self.vocab_size = VOCAB
+        self.fed: dict[object, list[int]] = {}
+        self.batches: list[list[tuple[object, int, int, bool]]] = []
+
+    def execute(self, entries, wanted):
+        tokens = []
+        record = []
+        for e in entries:
+            self.manager.reserve(e.seq, len(e.tokens))
+        for e in entries:
+            history = self.fed.setdefault(e.seq.request_id, [])
+            if e.seq.length == 0:
+                history.clear()
+            assert len(history) == e.seq.length, "a step must continue where the cache stops"
+            history.extend(e.tokens)
+            record.append((e.seq.request_id, e.seq.length, len(e.tokens), bool(e.want)))
+            self.manager.commit(e.seq, len(e.tokens))
+            if e.want:
+                tokens.append(predict(history))
+        self.batches.append(record)
+        self.manager.check_invariants()
+        return tokens
+
+
+def predict(history):
+    return (sum((i + 1) * t for i, t in enumerate(history)) * 31 + len(history)) % VOCAB
+
+
+def expected_output(prompt, n):
+    ids, out = list(prompt), []
+    for _ in range(n):
+        out.append(predict(ids))
+        ids.append(out[-1])
+    return out
+
+
+def drive(s, limit=500):
+    finished = []
+    for _ in range(limit):
+        if not s.has_work():
+            return finished
+        done, _ = s.step(now=0.0)
+        finished += done
+    raise AssertionError("the scheduler did not finish")
+
+
+def prompt(n, salt=0):
+    return [(7 * i + salt) % VOCAB for i in range(n)]
+
+
+def test_prompt_is_cut_under_the_token_budget_and_mixed_with_decoding():
+    ex = StubExecutor(pages=64)
+    s = Scheduler(ex, max_batch_tokens=24)
+    a = s.submit("a", prompt(10), 5)
+    s.step(now=0.0)
+    assert a.status == RUNNING and len(a.output_ids) == 1
+    b = s.submit("b", prompt(60, 3), 3)
+    s.step(now=0.0)
+    # a's single token comes first, b's portion fills the rest of the 24-token budget, no logits for a mid-prompt portion
+    assert ex.batches[-1] == [("a", 10, 1, True), ("b", 0, 23, False)]
+    assert b.status == PREFILLING and b.output_ids == []
+    s.step(now=0.0)
+    assert ex.batches[-1] == [("a", 11, 1, True), ("b", 23, 23, False)]
+    s.step(now=0.0)
+    assert ex.batches[-1] == [("a", 12, 1, True), ("b", 46, 14, True)]
+    assert b.status == RUNNING and len(b.output_ids) == 1
+    done = drive(s)
+    assert {r.request_id for r in done} == {"a", "b"} and all(r.status == FINISHED for r in done)
+    assert a.output_ids == expected_output(prompt(10), 5) and b.output_ids == expected_output(prompt(60, 3), 3)
+    assert a.stop_reason == b.stop_reason == "length"
+    # the last chosen token is never fed: a held 10 + 5 - 1 positions at the end
+    assert len(ex.fed["a"]) == 14
+    assert ex.manager.free_pages() == [64] and s.reserved == [0]
+
+
+def test_admission_is_fifo_against_the_page_budget():
+    ex = StubExecutor(pages=8)                       # 128 positions
+    s = Scheduler(ex, max_batch_tokens=512)
+    big = s.submit("big", prompt(70), 10)            # budget (80 + 16) // 16 = 6 pages
+    small = s.submit("small", prompt(20, 1), 4)      # budget 2 pages
+    late = s.submit("late", prompt(5, 2), 4)         # budget 1 page: would fit, but must not overtake
+    s.step(now=0.0)
+    assert (big.status, small.status, late.status) == (RUNNING, RUNNING, WAITING)
+    assert s.reserved == [8]
+    done = drive(s)
+    assert [r.request_id for r in done] == ["small", "late", "big"] or [r.request_id for r in done][0] == "small"
+    assert late.output_ids == expected_output(prompt(5, 2), 4)
+    assert ex.manager.free_pages() == [8]
+    with pytest.raises(ValueError, match="pages"):
+        s.submit("huge", prompt(200), 10)
+
+
+def test_submit_validates():
+    s = Scheduler(StubExecutor(), max_context=64)
+    with pytest.raises(ValueError, match="at least one token"):
+        s.submit("x", [], 3)
+    with pytest.raises(ValueError, match="positive"):
+        s.submit("x", [1], 0)
+    with pytest.raises(ValueError, match="vocabulary"):
+        s.submit("x", [1, VOCAB], 3)
+    with pytest.raises(ValueError, match="maximum context"):
+        s.submit("x", prompt(60), 10)
+
+
+def test_eos_stops_unless_ignored():
+    ex = StubExecutor()
+    out = expected_output(prompt(6), 8)
+    s = Scheduler(ex, eos_token_ids=(out[2],))
+    a = s.submit("a", prompt(6), 8)
+    b = s.submit("b", prompt(6), 8, ignore_eos=True)
+    drive(s)
+    assert a.output_ids == out[:out.index(out[2]) + 1] and a.stop_reason == "eos"
+    assert b.output_ids == out and b.stop_reason == "length"
+
+
+def test_cancel_and_deadline_are_seen_at_round_start_only():
+    ex = StubExecutor(pages=8)
+    s = Scheduler(ex, max_batch_tokens=8)
+    running = s.submit("run", prompt(4), 50)
+    chunked = s.submit("pre", prompt(30, 1), 5, deadline=10.0)
+    queued = s.submit("wait", prompt(40, 2), 5)       # no budget left for it: stays waiting
+    s.step(now=0.0)
+    assert (running.status, chunked.status, queued.status) == (RUNNING, PREFILLING, WAITING)
+    s.cancel(running)
+    s.cancel(queued)
+    assert running.status == RUNNING                   # nothing happens until the next round starts
+    done, _ = s.step(now=5.0)
+    assert {r.request_id for r in done} == {"run", "wait"}
+    assert running.stop_reason == queued.stop_reason == "cancelled" and queued.output_ids == []
+    assert all(r[0] == "pre" for r in ex.batches[-1])  # the cancelled request ran no more
+    done, _ = s.step(now=10.0)                         # a deadline in the past, never a sleep
+    assert [r.request_id for r in done] == ["pre"] and chunked.stop_reason == "deadline"
+    assert ex.manager.free_pages() == [8] and s.reserved == [0] and not s.has_work()
+    s.cancel(running)                                  # cancelling a finished request changes nothing
+    assert running.stop_reason == "cancelled"
+
+
+def test_optimistic_admission_preempts_the_newest_and_recomputes():
+    ex = StubExecutor(pages=6)                         # 96 positions
+    s = Scheduler(ex, max_batch_tokens=64, admission="optimistic")
+    first = s.submit("first", prompt(40), 30)          # grows to 69 positions = 5 pages
+    second = s.submit("second", prompt(30, 1), 30)     # grows to 59 positions = 4 pages: both cannot finish together
+    finished = drive(s)
+    assert s.preemptions >= 1 and second.preemptions >= 1 and first.preemptions == 0
+    assert first.output_ids == expected_output(prompt(40), 30)
+    assert second.output_ids == expected_output(prompt(30, 1), 30)      # recomputed, same tokens
+    assert [r.request_id for r in finished] == ["first", "second"]
+    assert ex.manager.free_pages() == [6]
+    # under the budget policy the same load never preempts: the second request waits instead
+    ex2 = StubExecutor(pages=6)
+    s2 = Scheduler(ex2, max_batch_tokens=64)
+    a = s2.submit("first", prompt(40), 30)
+    b = s2.submit("second", prompt(30, 1), 30)
+    s2.step(now=0.0)
+    assert b.status == WAITING
+    drive(s2)
+    assert s2.preemptions == 0 and b.output_ids == second.output_ids
+
+
+def test_a_lone_request_that_cannot_be_backed_gives_up():
+    ex = StubExecutor(pages=2)
+    s = Scheduler(ex, max_batch_tokens=64, admission="optimistic")
+    with pytest.raises(ValueError, match="needs up to 3 pages"):
+        s.submit("r", prompt(20), 12)                  # can never fit: refused at once
+    ex3 = StubExecutor(pages=3)
+    s3 = Scheduler(ex3, max_batch_tokens=64, admission="optimistic")
+    hog = ex3.manager.open("someone else")             # a page the scheduler does not own
+    ex3.manager.reserve(hog, 16)
+    r = s3.submit("r", prompt(20), 20)
+    done = drive(s3)
+    assert done == [r] and r.stop_reason == "out of pages" and len(r.output_ids) > 0
+    assert ex3.manager.free_pages() == [2]
+
+
+def test_window_groups_need_fewer_pages():
+    specs = [CacheSpec("full", 2, 16), CacheSpec("window", 2, 16, window=32)]
+    ex = StubExecutor(pages=40, specs=specs)
+    s = Scheduler(ex, max_batch_tokens=16)
+    r = s.submit("r", prompt(300), 20)
+    assert r.budget[0] == (320 + 16) // 16 and r.budget[1] < 10
+    peak = 0
+    while s.has_work():
+        s.step(now=0.0)
+        if r.seq is not None:
+            peak = max(peak, len(r.seq.held_pages(1)))
+            assert len(r.seq.held_pages(1)) <= r.budget[1]
+    assert 3 <= peak <= r.budget[1] and r.output_ids == expected_output(prompt(300), 20)
+
+
+def test_stats_report_what_ran():
+    ex = StubExecutor(pages=32)
+    s = Scheduler(ex, max_batch_tokens=20)
+    s.submit("a", prompt(8), 3)
+    _, st = s.step(now=0.0)
+    assert (st.prefill_tokens, st.decode_tokens, st.num_seqs) == (8, 0, 1)
+    s.submit("b", prompt(50, 1), 3)
+    _, st = s.step(now=0.0)
+    assert (st.prefill_tokens, st.decode_tokens, st.num_seqs, st.batch_tokens) == (19, 1, 2, 20)
+    assert st.free_pages == ex.manager.free_pages()
