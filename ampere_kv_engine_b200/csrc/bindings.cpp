@@ -9,6 +9,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <string>
+
 #include "launchers.h"
 
 namespace {
@@ -16,33 +18,52 @@ namespace {
 using at::Tensor;
 using OptTensor = c10::optional<at::Tensor>;
 
+// Error text is put together with std::string only (no iostream formatting in this file).
+inline std::string text(const std::string& v) { return v; }
+inline std::string text(const char* v) { return std::string(v); }
+inline std::string text(int64_t v) { return std::to_string(v); }
+inline std::string text(int v) { return std::to_string(v); }
+inline std::string text(double v) { return std::to_string(v); }
+inline std::string text(at::ScalarType v) { return std::string(c10::toString(v)); }
+inline std::string join() { return std::string(); }
+template <typename First, typename... Rest>
+std::string join(const First& first, const Rest&... rest) { return text(first) + join(rest...); }
+
+#define AKV_CHECK(cond, ...)                          \
+  do {                                                \
+    if (!(cond)) {                                    \
+      const std::string akv_message = join(__VA_ARGS__); \
+      TORCH_CHECK(false, akv_message);                \
+    }                                                 \
+  } while (0)
+
 void check_cuda(const Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
-  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  AKV_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  AKV_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
 
 int dtype_code(const Tensor& t, const char* name) {
   if (t.scalar_type() == at::kFloat) return 0;
   if (t.scalar_type() == at::kBFloat16) return 1;
-  TORCH_CHECK(false, name, " must be float32 or bfloat16, got ", t.scalar_type());
+  AKV_CHECK(false, name, " must be float32 or bfloat16, got ", t.scalar_type());
   return -1;
 }
 
 void check_same(const Tensor& a, const Tensor& b, const char* an, const char* bn) {
-  TORCH_CHECK(a.scalar_type() == b.scalar_type(), an, " and ", bn, " must have the same dtype");
-  TORCH_CHECK(a.device() == b.device(), an, " and ", bn, " must be on the same device");
+  AKV_CHECK(a.scalar_type() == b.scalar_type(), an, " and ", bn, " must have the same dtype");
+  AKV_CHECK(a.device() == b.device(), an, " and ", bn, " must be on the same device");
 }
 
 void check_i32(const Tensor& t, const char* name, int64_t numel = -1) {
   check_cuda(t, name);
-  TORCH_CHECK(t.scalar_type() == at::kInt, name, " must be int32");
-  if (numel >= 0) TORCH_CHECK(t.numel() >= numel, name, " must hold at least ", numel, " entries, has ", t.numel());
+  AKV_CHECK(t.scalar_type() == at::kInt, name, " must be int32");
+  if (numel >= 0) AKV_CHECK(t.numel() >= numel, name, " must hold at least ", numel, " entries, has ", t.numel());
 }
 
 void check_f32(const Tensor& t, const char* name, int64_t numel = -1) {
   check_cuda(t, name);
-  TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
-  if (numel >= 0) TORCH_CHECK(t.numel() == numel, name, " must hold ", numel, " entries, has ", t.numel());
+  AKV_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
+  if (numel >= 0) AKV_CHECK(t.numel() == numel, name, " must hold ", numel, " entries, has ", t.numel());
 }
 
 int* status_ptr(const OptTensor& status) {
@@ -52,7 +73,7 @@ int* status_ptr(const OptTensor& status) {
 }
 
 void check_launch(int err, const char* what) {
-  TORCH_CHECK(err == 0, what, ": launch failed: ", cudaGetErrorString((cudaError_t)err));
+  AKV_CHECK(err == 0, what, ": launch failed: ", cudaGetErrorString((cudaError_t)err));
 }
 
 cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
@@ -70,7 +91,7 @@ Tensor smoke_add(const Tensor& a, const Tensor& b) {
 
 void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const OptTensor& status) {
   check_cuda(table, "table");
-  TORCH_CHECK(table.dim() == 2, "table must be [vocab, hidden]");
+  AKV_CHECK(table.dim() == 2, "table must be [vocab, hidden]");
   const int64_t n = ids.numel(), h = table.size(1);
   check_i32(ids, "ids");
   check_f32(hidden, "hidden", n * h);
@@ -84,17 +105,17 @@ void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const Opt
 void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, Tensor& out, const OptTensor& rows,
                  double eps, const OptTensor& status) {
   check_cuda(hidden, "hidden");
-  TORCH_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2, "hidden must be float32 [tokens, hidden]");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2, "hidden must be float32 [tokens, hidden]");
   const int64_t n = hidden.size(0), h = hidden.size(1);
   check_f32(weight, "weight", h);
   check_cuda(out, "out");
   const int code = dtype_code(out, "out");
-  TORCH_CHECK(h * 4 <= 200 * 1024, "add_rmsnorm: hidden size ", h, " exceeds the kernel's limit of 51200");
+  AKV_CHECK(h * 4 <= 200 * 1024, "add_rmsnorm: hidden size ", h, " exceeds the kernel's limit of 51200");
   const void* delta_ptr = nullptr;
   if (delta.has_value()) {
     check_cuda(*delta, "delta");
     check_same(*delta, out, "delta", "out");
-    TORCH_CHECK(delta->numel() == n * h, "delta must be [tokens, hidden]");
+    AKV_CHECK(delta->numel() == n * h, "delta must be [tokens, hidden]");
     delta_ptr = delta->data_ptr();
   }
   const int* rows_ptr = nullptr;
@@ -103,9 +124,9 @@ void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, T
     check_i32(*rows, "rows");
     rows_ptr = rows->data_ptr<int>();
     num_rows = rows->numel();
-    TORCH_CHECK(out.numel() == num_rows * h, "out must be [rows, hidden]");
+    AKV_CHECK(out.numel() == num_rows * h, "out must be [rows, hidden]");
   } else {
-    TORCH_CHECK(out.numel() == n * h, "out must be [tokens, hidden]");
+    AKV_CHECK(out.numel() == n * h, "out must be [tokens, hidden]");
   }
   c10::cuda::CUDAGuard guard(hidden.device());
   check_launch(akv::launch_add_rmsnorm(hidden.data_ptr<float>(), delta_ptr, weight.data_ptr<float>(), out.data_ptr(),
@@ -118,9 +139,9 @@ void silu_mul(const Tensor& gate_up, Tensor& out) {
   check_cuda(gate_up, "gate_up");
   check_cuda(out, "out");
   check_same(gate_up, out, "gate_up", "out");
-  TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
+  AKV_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
   const int64_t n = gate_up.size(0), inter = gate_up.size(1) / 2;
-  TORCH_CHECK(out.numel() == n * inter, "out must be [tokens, intermediate]");
+  AKV_CHECK(out.numel() == n * inter, "out must be [tokens, intermediate]");
   c10::cuda::CUDAGuard guard(gate_up.device());
   check_launch(akv::launch_silu_mul(gate_up.data_ptr(), out.data_ptr(), n, inter, dtype_code(out, "out"),
                                     stream_of(out)),
@@ -138,9 +159,9 @@ CacheGeometry check_cache(const Tensor& k_cache, const Tensor& v_cache, int num_
   check_cuda(v_cache, "v_cache");
   check_same(k_cache, v_cache, "k_cache", "v_cache");
   check_same(k_cache, like, "k_cache", "activations");
-  TORCH_CHECK(k_cache.dim() == 4 && k_cache.sizes() == v_cache.sizes(),
+  AKV_CHECK(k_cache.dim() == 4 && k_cache.sizes() == v_cache.sizes(),
               "k_cache and v_cache must both be [pages, kv_heads, page_size, head_dim]");
-  TORCH_CHECK(k_cache.size(1) == num_kv_heads && k_cache.size(3) == head_dim, "cache pages are [",
+  AKV_CHECK(k_cache.size(1) == num_kv_heads && k_cache.size(3) == head_dim, "cache pages are [",
               k_cache.size(1), " kv heads, ", k_cache.size(3), " dims], the call says [", num_kv_heads, ", ",
               head_dim, "]");
   return {k_cache.size(0), num_kv_heads, (int)k_cache.size(2), head_dim};
@@ -154,15 +175,15 @@ void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTen
   check_cuda(qkv, "qkv");
   check_cuda(q_out, "q_out");
   check_same(qkv, q_out, "qkv", "q_out");
-  TORCH_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0, "head counts and head_dim must be positive");
-  TORCH_CHECK(head_dim % 2 == 0 && head_dim <= 512, "qk_norm_rope_write: head_dim must be even and <= 512, got ",
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0, "head counts and head_dim must be positive");
+  AKV_CHECK(head_dim % 2 == 0 && head_dim <= 512, "qk_norm_rope_write: head_dim must be even and <= 512, got ",
               head_dim);
   const int64_t width = (num_heads + 2 * num_kv_heads) * head_dim;
-  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == width, "qkv must be [tokens, (heads + 2 kv_heads) * head_dim = ",
+  AKV_CHECK(qkv.dim() == 2 && qkv.size(1) == width, "qkv must be [tokens, (heads + 2 kv_heads) * head_dim = ",
               width, "]");
   const int64_t n = qkv.size(0);
   check_i32(positions, "positions", n);
-  TORCH_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
+  AKV_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
   akv::QkRopeWriteParams p{};
   p.qkv = qkv.data_ptr();
   p.positions = positions.data_ptr<int>();
@@ -174,24 +195,24 @@ void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTen
   if (q_weight.has_value()) { check_f32(*q_weight, "q_weight", head_dim); p.q_weight = q_weight->data_ptr<float>(); }
   if (k_weight.has_value()) { check_f32(*k_weight, "k_weight", head_dim); p.k_weight = k_weight->data_ptr<float>(); }
   if (inv_freq.has_value()) {
-    TORCH_CHECK(rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
+    AKV_CHECK(rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
                 "rotary_dim must be even and in (0, head_dim], got ", rotary_dim);
     check_f32(*inv_freq, "inv_freq", rotary_dim / 2);
     p.inv_freq = inv_freq->data_ptr<float>();
   }
   if (k_out.has_value()) {
     check_cuda(*k_out, "k_out"); check_same(*k_out, qkv, "k_out", "qkv");
-    TORCH_CHECK(k_out->numel() == n * num_kv_heads * head_dim, "k_out must be [tokens, kv_heads * head_dim]");
+    AKV_CHECK(k_out->numel() == n * num_kv_heads * head_dim, "k_out must be [tokens, kv_heads * head_dim]");
     p.k_out = k_out->data_ptr();
   }
   if (v_out.has_value()) {
     check_cuda(*v_out, "v_out"); check_same(*v_out, qkv, "v_out", "qkv");
-    TORCH_CHECK(v_out->numel() == n * num_kv_heads * head_dim, "v_out must be [tokens, kv_heads * head_dim]");
+    AKV_CHECK(v_out->numel() == n * num_kv_heads * head_dim, "v_out must be [tokens, kv_heads * head_dim]");
     p.v_out = v_out->data_ptr();
   }
-  TORCH_CHECK(k_cache.has_value() == v_cache.has_value(), "k_cache and v_cache come together");
+  AKV_CHECK(k_cache.has_value() == v_cache.has_value(), "k_cache and v_cache come together");
   if (k_cache.has_value()) {
-    TORCH_CHECK(slots.has_value(), "a cache to write needs slots");
+    AKV_CHECK(slots.has_value(), "a cache to write needs slots");
     const CacheGeometry g = check_cache(*k_cache, *v_cache, (int)num_kv_heads, (int)head_dim, qkv);
     p.k_cache = k_cache->data_ptr();
     p.v_cache = v_cache->data_ptr();
@@ -215,11 +236,11 @@ void kv_write(const Tensor& k, const Tensor& v, const Tensor& slots, Tensor& k_c
   check_cuda(k, "k");
   check_cuda(v, "v");
   check_same(k, v, "k", "v");
-  TORCH_CHECK(k.dim() == 2 && k.sizes() == v.sizes(), "k and v must both be [tokens, kv_heads * head_dim]");
-  TORCH_CHECK(k_cache.dim() == 4, "k_cache must be [pages, kv_heads, page_size, head_dim]");
+  AKV_CHECK(k.dim() == 2 && k.sizes() == v.sizes(), "k and v must both be [tokens, kv_heads * head_dim]");
+  AKV_CHECK(k_cache.dim() == 4, "k_cache must be [pages, kv_heads, page_size, head_dim]");
   const int nkv = (int)k_cache.size(1), d = (int)k_cache.size(3);
   const CacheGeometry g = check_cache(k_cache, v_cache, nkv, d, k);
-  TORCH_CHECK(k.size(1) == (int64_t)nkv * d, "k is ", k.size(1), " wide, the cache wants ", (int64_t)nkv * d);
+  AKV_CHECK(k.size(1) == (int64_t)nkv * d, "k is ", k.size(1), " wide, the cache wants ", (int64_t)nkv * d);
   check_i32(slots, "slots", k.size(0));
   c10::cuda::CUDAGuard guard(k.device());
   check_launch(akv::launch_kv_write(k.data_ptr(), v.data_ptr(), slots.data_ptr<int>(), k_cache.data_ptr(),
@@ -236,27 +257,27 @@ void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
   check_cuda(q, "q");
   check_cuda(out, "out");
   check_same(q, out, "q", "out");
-  TORCH_CHECK(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0,
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0,
               "paged_attention: heads (", num_heads, ") must be a positive multiple of kv heads (", num_kv_heads, ")");
-  TORCH_CHECK(q.dim() == 2 && q.size(1) % num_heads == 0, "q must be [tokens, heads * head_dim]");
+  AKV_CHECK(q.dim() == 2 && q.size(1) % num_heads == 0, "q must be [tokens, heads * head_dim]");
   const int64_t n = q.size(0), d = q.size(1) / num_heads;
-  TORCH_CHECK(d % 16 == 0 && d <= 256, "paged_attention: head_dim must be a multiple of 16 up to 256, got ", d);
-  TORCH_CHECK(out.numel() == q.numel(), "out must have q's shape");
+  AKV_CHECK(d % 16 == 0 && d <= 256, "paged_attention: head_dim must be a multiple of 16 up to 256, got ", d);
+  AKV_CHECK(out.numel() == q.numel(), "out must have q's shape");
   const CacheGeometry g = check_cache(k_cache, v_cache, (int)num_kv_heads, (int)d, q);
   check_i32(block_table, "block_table");
-  TORCH_CHECK(block_table.dim() == 2, "block_table must be [sequences, width]");
+  AKV_CHECK(block_table.dim() == 2, "block_table must be [sequences, width]");
   const int64_t s = block_table.size(0);
   check_i32(cu_q, "cu_q", s + 1);
   check_i32(ctx_lens, "ctx_lens", s);
-  TORCH_CHECK(num_tiles >= 0 && q_tile >= 1 && num_splits >= 1 && window >= 0, "bad tile / split / window counts");
+  AKV_CHECK(num_tiles >= 0 && q_tile >= 1 && num_splits >= 1 && window >= 0, "bad tile / split / window counts");
   check_i32(tile_seq, "tile_seq", num_tiles);
   check_i32(tile_q0, "tile_q0", num_tiles);
   check_i32(tile_nq, "tile_nq", num_tiles);
   akv::PagedAttentionParams p{};
   if (num_splits > 1) {
-    TORCH_CHECK(partials.has_value(), "num_splits > 1 needs a partials workspace");
+    AKV_CHECK(partials.has_value(), "num_splits > 1 needs a partials workspace");
     check_cuda(*partials, "partials");
-    TORCH_CHECK(partials->scalar_type() == at::kFloat && partials->numel() >= n * num_heads * num_splits * (d + 2),
+    AKV_CHECK(partials->scalar_type() == at::kFloat && partials->numel() >= n * num_heads * num_splits * (d + 2),
                 "partials must be float32 with at least tokens * heads * splits * (head_dim + 2) entries");
     p.partials = partials->data_ptr<float>();
   }
@@ -291,7 +312,7 @@ void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
 
 void sample(const Tensor& logits, const Tensor& temperature, const Tensor& uniform, Tensor& tokens) {
   check_cuda(logits, "logits");
-  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2, "logits must be float32 [rows, vocab]");
+  AKV_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2, "logits must be float32 [rows, vocab]");
   const int64_t rows = logits.size(0);
   check_f32(temperature, "temperature", rows);
   check_f32(uniform, "uniform", rows);
