@@ -60,6 +60,7 @@ class StepContext:
     q_lens_host: list[int] = field(default_factory=list)
     ctx_lens_host: list[int] = field(default_factory=list)
     state_slots_host: list[int] = field(default_factory=list)
+    h2d_bytes: int = 0              # size of the one host-to-device copy that carried all of the above
 
 
 def _align(n: int, to: int = 4) -> int:
@@ -148,4 +149,5 @@ def build_context(manager: CacheManager, entries: list[SeqStep], device: torch.d
         logit_rows=view(5, len(logit_rows)), num_logit_rows=len(logit_rows),
         tile_seq=view(6, len(tiles)), tile_q0=view(7, len(tiles)), tile_nq=view(8, len(tiles)),
         num_tiles=len(tiles), q_tile=tile_rows, max_context=max(ctx_lens), groups=groups, status=status,
-        q_lens_host=q_lens, ctx_lens_host=ctx_lens, state_slots_host=[e.seq.state_slot for e in entries])
+        q_lens_host=q_lens, ctx_lens_host=ctx_lens, state_slots_host=[e.seq.state_slot for e in entries],
+        h2d_bytes=int(host.nbytes))

@@ -46,6 +46,7 @@ class ModelRunner:
         self.views = self.manager.layer_views()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ requests
 
@@ -71,6 +72,7 @@ class ModelRunner:
                 self.manager.reserve(e.seq, len(e.tokens))
                 reserved.append(e)
             ctx = build_context(self.manager, entries, self.device, status=self.status)
+            self.last_h2d_bytes = ctx.h2d_bytes
             logits = self.model.forward(ctx, self.views)
         except BaseException:
             for e in reserved:

@@ -18,6 +18,14 @@ ATTENTION_Q_TILE = 16
 
 _EXT = None
 
+#: kernels of this package launched since the last reset (the benchmark reports it)
+launch_count = 0
+
+
+def _launched(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
 
 def ext():
     """The loaded extension module (built on first use)."""
@@ -35,6 +43,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor | Non
     """float32 residual stream [tokens, hidden] gathered from ``table`` rows."""
     hidden = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
     ext().embedding(ids, table, hidden, status)
+    _launched()
     return hidden
 
 
@@ -49,12 +58,14 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     n = hidden.shape[0] if rows is None else rows.numel()
     out = torch.empty((n, hidden.shape[1]), dtype=out_dtype, device=hidden.device)
     ext().add_rmsnorm(hidden, delta, weight, out, rows, float(eps), status)
+    _launched()
     return out
 
 
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty((gate_up.shape[0], gate_up.shape[1] // 2), dtype=gate_up.dtype, device=gate_up.device)
     ext().silu_mul(gate_up, out)
+    _launched()
     return out
 
 
@@ -72,11 +83,13 @@ def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_ca
         v_out = torch.empty_like(k_out)
     ext().qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, q_out, k_out, v_out, k_cache,
                              v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), status)
+    _launched()
     return (q_out, k_out, v_out) if want_kv else q_out
 
 
 def kv_write(k, v, slots, k_cache, v_cache, status=None) -> None:
     ext().kv_write(k, v, slots, k_cache, v_cache, status)
+    _launched()
 
 
 def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
@@ -99,12 +112,14 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
     ext().paged_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
                           partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(window or 0),
                           float(scale), status)
+    _launched(2 if num_splits > 1 else 1)
     return out
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
     tokens = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
     ext().sample(logits, temperature, uniform, tokens)
+    _launched()
     return tokens
 
 

@@ -1,0 +1,297 @@
+"""Benchmark of the engine on one B200: decode tokens per second at the Qwen3-8B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+Prints ONE JSON line.  A "step" is one decode step of the whole batch through the engine's own step
+function (every kernel of the model and the token choice); ``value`` is batch / step time, timed with CUDA
+events around K steps.  ``e2e`` is the same quantity through the Python entry point's scheduler loop: every
+step copies that step's token ids and index data from pinned host memory to the device and reads the
+chosen tokens back.  ``prefill`` is one 2,048-token prompt in one step; ``points`` holds decode at batch 1
+and 64; ``roofline`` compares the bytes a decode step must read (every weight once, the live requests'
+cache) with the copy bandwidth.  Weights are random (seeded), token ids synthetic (seeded uniform).
+Between timed steps nothing is flushed: every step streams the whole model (16 GB at full depth) through
+a 126 MB L2, so the inputs are larger than L2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen3-8B shape
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "max_position_embeddings": 40960, "tie_word_embeddings": False,
+    "hidden_act": "silu", "attention_bias": False,
+}
+CONTEXT = 8192          # the engine's context limit in this run
+PROMPT_LEN = 1024       # decode starts from 1,024-token prompts
+GEN_LEN = 256
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                raw = json.load(handle)
+            flat = {}
+
+            def walk(d):
+                for k, v in d.items():
+                    if isinstance(v, dict):
+                        walk(v)
+                    elif isinstance(v, (int, float)) and k not in flat:
+                        flat[k] = float(v)
+            walk(raw)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                flat["source"] = "measured"
+                return flat
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.samples: list[list[str]] = []
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        reasons = sorted({name for s in self.samples for name, flag in zip(self.NAMES, s[2:]) if flag == "Active"})
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def model_numbers(cfg: dict, layers: int) -> dict:
+    h, nh, nkv, d, i, v = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                           cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+    per_layer = (nh + 2 * nkv) * d * h + h * nh * d + 3 * i * h
+    return {"layer_params": per_layer, "head_params": v * h, "layer_norm_params": 2 * h + 2 * d,
+            "kv_bytes_per_token": 2 * nkv * d * 2 * layers}
+
+
+def decode_bytes(cfg, layers, batch, mean_ctx) -> float:
+    n = model_numbers(cfg, layers)
+    weights = 2.0 * (layers * n["layer_params"] + n["head_params"]) + 4.0 * (layers * n["layer_norm_params"])
+    return weights + batch * mean_ctx * n["kv_bytes_per_token"]
+
+
+def prefill_flops(cfg, layers, tokens) -> float:
+    n = model_numbers(cfg, layers)
+    gemm = 2.0 * tokens * layers * n["layer_params"] + 2.0 * n["head_params"]
+    attn = 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * layers * tokens * (tokens + 1) / 2
+    return gemm + attn
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                        help="run fewer layers of the same sizes (reported in config)")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference loads the published Qwen3-8B checkpoint by name with local_files_only=True "
+                          "(ampere_kv/runner.py:33-36) and builds its kernels for sm_86 only (setup.py:19); there is "
+                          "no checkpoint and no network here, and it has no random-weights mode"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from ampere_kv_engine_b200.engine.batch import SeqStep
+    from ampere_kv_engine_b200.engine.engine import Engine
+    from ampere_kv_engine_b200.kernels import ops
+    from ampere_kv_engine_b200.sampling.sampler import SamplingParams
+
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = args.layers
+    peaks = load_peaks()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    max_batch = 64 if not args.no_points else args.batch
+    pool_tokens = max(max_batch * (PROMPT_LEN + GEN_LEN + 64), args.batch * CONTEXT // 4, PREFILL_TOKENS + 64)
+    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", device=device, page_size=PAGE_SIZE,
+                                max_tokens=pool_tokens, max_seqs=max_batch + 2, max_batch_tokens=PREFILL_TOKENS)
+    runner = engine.runner
+    gen = torch.Generator().manual_seed(1234)
+    vocab = cfg["vocab_size"]
+
+    def synthetic(n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    def timed(fn, steps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps
+
+    def decode_point(batch, steps, warmup):
+        """ms per decode step of ``batch`` requests that each hold a 1,024-token prompt."""
+        seqs = [runner.open(f"d{batch}-{i}") for i in range(batch)]
+        per_step = max(1, PREFILL_TOKENS // PROMPT_LEN)
+        for i in range(0, batch, per_step):
+            runner.step([SeqStep(s, synthetic(PROMPT_LEN), []) for s in seqs[i:i + per_step]])
+        greedy = [SamplingParams()] * batch
+        zeros = [0] * batch
+
+        def one():
+            logits = runner.step([SeqStep(s, [t], [0]) for s, t in zip(seqs, synthetic(batch))])
+            engine.sampler.sample(logits, greedy, zeros)
+
+        for _ in range(warmup):
+            one()
+        ctx_start = seqs[0].length
+        ops.launch_count = 0
+        ms = timed(one, steps)
+        launches = ops.launch_count
+        mean_ctx = ctx_start + (steps + 1) / 2
+        runner.raise_on_status()
+        for s in seqs:
+            runner.close(s)
+        return ms, mean_ctx, launches
+
+    with ClockSampler() as clocks:
+        ms, mean_ctx, launches = decode_point(args.batch, args.steps, args.warmup)
+    clock_summary = clocks.summary()
+    value = args.batch / (ms / 1000)
+    bytes_step = decode_bytes(cfg, args.layers, args.batch, mean_ctx)
+    achieved = bytes_step / (ms / 1000) / 1e9
+
+    # end to end: the scheduler loop of the Python entry point, host tokens in and out every step
+    scheduler = engine.new_scheduler()
+    slack = args.batch * PROMPT_LEN // PREFILL_TOKENS + 4     # early requests decode while later ones prefill
+    requests = [scheduler.submit(f"e{i}", synthetic(PROMPT_LEN), args.warmup + args.steps + slack, ignore_eos=True)
+                for i in range(args.batch)]
+    while any(not r.output_ids for r in requests):
+        scheduler.step()
+    for _ in range(args.warmup):
+        scheduler.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    stats = None
+    for _ in range(args.steps):
+        _, stats = scheduler.step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1000 / args.steps
+    assert stats.decode_tokens == args.batch and stats.prefill_tokens == 0
+    for r in requests:
+        scheduler.cancel(r)
+    scheduler.step()
+    h2d = runner.last_h2d_bytes + 8 * args.batch      # the step's index buffer + temperatures and uniforms
+    e2e = {"value": round(args.batch / (e2e_ms / 1000), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * (args.batch + 1)}
+
+    # prefill of 2,048 tokens in one step
+    def prefill_once():
+        seq = runner.open("prefill")
+        logits = runner.step([SeqStep(seq, prompt, [PREFILL_TOKENS - 1])])
+        engine.sampler.sample(logits, [SamplingParams()], [0])
+        runner.close(seq)
+
+    prompt = synthetic(PREFILL_TOKENS)
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = timed(prefill_once, 5)
+    flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1000), 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(flops / (prefill_ms / 1000) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            p_ms, _, _ = decode_point(b, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(b / (p_ms / 1000), 2)
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, B200); prefill and batch 1/64 alongside",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded uniform token ids, seeded random weights)",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "gen_len": GEN_LEN,
+            "mean_decode_context": round(mean_ctx, 1), "page_size": PAGE_SIZE, "kv_dtype": "bf16",
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (all weights stream every step)",
+        },
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
+        "points": points,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
