@@ -67,61 +67,82 @@ def _align(n: int, to: int = 4) -> int:
     return (n + to - 1) // to * to
 
 
-def build_context(manager: CacheManager, entries: list[SeqStep], device: torch.device,
-                  status: torch.Tensor | None = None, q_tile: int | None = None) -> StepContext:
-    """Lay out the step.  Every entry's pages must already be reserved for its new tokens."""
-    if not entries:
-        raise ValueError("a step needs at least one entry")
-    q_tile = q_tile or ops.ATTENTION_Q_TILE
+@dataclass
+class BatchLayout:
+    """Sizes of one step's index buffer.  Two steps with the same layout can share device memory, which is what
+    lets a decode step be replayed as a CUDA graph."""
+
+    num_tokens: int
+    num_seqs: int
+    num_logit_rows: int
+    num_tiles: int
+    widths: tuple[int, ...]           # block-table width per cache group
+    offsets: list[int] = field(default_factory=list)
+
+    def __post_init__(self):
+        sizes = [self.num_tokens, self.num_tokens, self.num_seqs + 1, self.num_seqs, self.num_seqs,
+                 max(1, self.num_logit_rows), self.num_tiles, self.num_tiles, self.num_tiles]
+        for w in self.widths:
+            sizes += [self.num_tokens, self.num_seqs * w]
+        self.offsets = [0]
+        for size in sizes:
+            self.offsets.append(self.offsets[-1] + _align(size))
+
+    @property
+    def total(self) -> int:
+        return self.offsets[-1]
+
+    def key(self) -> tuple:
+        return (self.num_tokens, self.num_seqs, self.num_logit_rows, self.num_tiles, self.widths)
+
+
+def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout, host: np.ndarray,
+              tile_rows: int) -> tuple[list[int], list[int]]:
+    """Write the step's index data into ``host`` (int32, ``layout.total`` long).  Sequences, tokens and tiles
+    beyond the entries (a padded layout) are filled so that they do nothing: no cache slot, no tile rows.
+    Returns (q_lens, ctx_lens) of the real entries."""
     q_lens = [len(e.tokens) for e in entries]
-    if min(q_lens) <= 0:
-        raise ValueError("every entry of a step needs at least one token")
-    num_seqs, num_tokens = len(entries), sum(q_lens)
     starts = [e.seq.length for e in entries]
     ctx_lens = [s + n for s, n in zip(starts, q_lens)]
-    cu = np.zeros(num_seqs + 1, dtype=np.int64)
-    np.cumsum(q_lens, out=cu[1:])
-    tile_rows = 1 if max(q_lens) == 1 else q_tile
-    tiles: list[tuple[int, int, int]] = []
-    for s, n in enumerate(q_lens):
-        for q0 in range(0, n, tile_rows):
-            tiles.append((s, int(cu[s]) + q0, min(tile_rows, n - q0)))
-    logit_rows = [int(cu[s]) + w for s, e in enumerate(entries) for w in e.want]
-    for s, e in enumerate(entries):
-        for w in e.want:
-            if not 0 <= w < q_lens[s]:
-                raise ValueError(f"request {e.seq.request_id!r}: wanted place {w} is outside its {q_lens[s]} tokens")
-    widths = [max(1, max(len(manager.table_row(e.seq, g.index)) for e in entries)) for g in manager.groups]
-
-    # one int32 buffer: [ids | positions | cu_q | ctx_lens | state_slots | logit_rows | tile_seq | tile_q0 |
-    #                    tile_nq | per group: slot_mapping, block_table]
-    sizes = [num_tokens, num_tokens, num_seqs + 1, num_seqs, num_seqs, max(1, len(logit_rows)),
-             len(tiles), len(tiles), len(tiles)]
-    for w in widths:
-        sizes += [num_tokens, num_seqs * w]
-    offsets = [0]
-    for size in sizes:
-        offsets.append(offsets[-1] + _align(size))
-    host = np.full(offsets[-1], -1, dtype=np.int32)
+    num_seqs, num_tokens = len(entries), sum(q_lens)
+    off = layout.offsets
+    host[:] = -1
+    cu = np.zeros(layout.num_seqs + 1, dtype=np.int64)
+    np.cumsum(q_lens, out=cu[1:num_seqs + 1])
+    # padded sequences own one padded token each
+    cu[num_seqs + 1:] = num_tokens + np.arange(1, layout.num_seqs - num_seqs + 1)
 
     def put(index: int, values) -> None:
-        host[offsets[index]:offsets[index] + len(values)] = values
+        host[off[index]:off[index] + len(values)] = values
 
+    host[off[0]:off[0] + layout.num_tokens] = 0
     put(0, [t for e in entries for t in e.tokens])
+    host[off[1]:off[1] + layout.num_tokens] = 0
     put(1, np.concatenate([np.arange(s, c, dtype=np.int64) for s, c in zip(starts, ctx_lens)]))
     put(2, cu)
+    host[off[3]:off[3] + layout.num_seqs] = 1
     put(3, ctx_lens)
+    host[off[4]:off[4] + layout.num_seqs] = 0
     put(4, [e.seq.state_slot for e in entries])
-    put(5, logit_rows if logit_rows else [0])
+    host[off[5]:off[5] + max(1, layout.num_logit_rows)] = 0
+    put(5, [int(cu[s]) + w for s, e in enumerate(entries) for w in e.want])
+    tiles = [(s, int(cu[s]) + q0, min(tile_rows, n - q0)) for s, n in enumerate(q_lens) for q0 in range(0, n, tile_rows)]
+    if len(tiles) > layout.num_tiles:
+        raise ValueError("the layout has too few attention tiles for this step")
+    host[off[6]:off[6] + layout.num_tiles] = 0
+    host[off[7]:off[7] + layout.num_tiles] = 0
+    host[off[8]:off[8] + layout.num_tiles] = 0       # a tile of no rows does nothing
     put(6, [t[0] for t in tiles])
     put(7, [t[1] for t in tiles])
     put(8, [t[2] for t in tiles])
     page = manager.page_size
-    for gi, (group, width) in enumerate(zip(manager.groups, widths)):
-        slots = np.empty(num_tokens, dtype=np.int64)
-        table = np.full((num_seqs, width), -1, dtype=np.int64)
+    for gi, (group, width) in enumerate(zip(manager.groups, layout.widths)):
+        slots = np.full(layout.num_tokens, -1, dtype=np.int64)
+        table = np.full((layout.num_seqs, width), -1, dtype=np.int64)
         for s, e in enumerate(entries):
             row = np.asarray(manager.table_row(e.seq, group.index), dtype=np.int64)
+            if len(row) > width:
+                raise ValueError("the layout's block table is too narrow for this step")
             table[s, :len(row)] = row
             pos = np.arange(starts[s], ctx_lens[s], dtype=np.int64)
             pages = row[pos // page]
@@ -130,24 +151,64 @@ def build_context(manager: CacheManager, entries: list[SeqStep], device: torch.d
             slots[int(cu[s]):int(cu[s + 1])] = pages * page + pos % page
         put(9 + 2 * gi, slots)
         put(10 + 2 * gi, table.reshape(-1))
+    return q_lens, ctx_lens
 
+
+def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_context: int,
+                 status: torch.Tensor | None, q_lens: list[int], ctx_lens: list[int], state_slots: list[int],
+                 h2d_bytes: int) -> StepContext:
+    """Views into the device copy ``dev`` of a filled index buffer."""
+    off = layout.offsets
+
+    def view(index: int, size: int) -> torch.Tensor:
+        return dev[off[index]:off[index] + size]
+
+    groups = []
+    for gi, width in enumerate(layout.widths):
+        groups.append(GroupBatch(view(9 + 2 * gi, layout.num_tokens),
+                                 view(10 + 2 * gi, layout.num_seqs * width).view(layout.num_seqs, width), width))
+    return StepContext(
+        num_tokens=layout.num_tokens, num_seqs=layout.num_seqs, token_ids=view(0, layout.num_tokens),
+        positions=view(1, layout.num_tokens), cu_q=view(2, layout.num_seqs + 1), ctx_lens=view(3, layout.num_seqs),
+        state_slots=view(4, layout.num_seqs), logit_rows=view(5, layout.num_logit_rows),
+        num_logit_rows=layout.num_logit_rows, tile_seq=view(6, layout.num_tiles), tile_q0=view(7, layout.num_tiles),
+        tile_nq=view(8, layout.num_tiles), num_tiles=layout.num_tiles, q_tile=tile_rows, max_context=max_context,
+        groups=groups, status=status, q_lens_host=q_lens, ctx_lens_host=ctx_lens, state_slots_host=state_slots,
+        h2d_bytes=h2d_bytes)
+
+
+def validate_entries(entries: list[SeqStep]) -> None:
+    if not entries:
+        raise ValueError("a step needs at least one entry")
+    for e in entries:
+        if not e.tokens:
+            raise ValueError("every entry of a step needs at least one token")
+        for w in e.want:
+            if not 0 <= w < len(e.tokens):
+                raise ValueError(f"request {e.seq.request_id!r}: wanted place {w} is outside its "
+                                 f"{len(e.tokens)} tokens")
+
+
+def exact_layout(manager: CacheManager, entries: list[SeqStep], tile_rows: int) -> BatchLayout:
+    q_lens = [len(e.tokens) for e in entries]
+    widths = tuple(max(1, max(len(manager.table_row(e.seq, g.index)) for e in entries)) for g in manager.groups)
+    return BatchLayout(sum(q_lens), len(entries), sum(len(e.want) for e in entries),
+                       sum((n + tile_rows - 1) // tile_rows for n in q_lens), widths)
+
+
+def build_context(manager: CacheManager, entries: list[SeqStep], device: torch.device,
+                  status: torch.Tensor | None = None, q_tile: int | None = None) -> StepContext:
+    """Lay out the step exactly (no padding) and copy it to the device in one transfer.  Every entry's pages
+    must already be reserved for its new tokens."""
+    validate_entries(entries)
+    q_tile = q_tile or ops.ATTENTION_Q_TILE
+    tile_rows = 1 if max(len(e.tokens) for e in entries) == 1 else q_tile
+    layout = exact_layout(manager, entries, tile_rows)
+    host = np.empty(layout.total, dtype=np.int32)
+    q_lens, ctx_lens = fill_host(manager, entries, layout, host, tile_rows)
     staged = torch.from_numpy(host)
     if device.type == "cuda":
         staged = staged.pin_memory()
     dev = staged.to(device, non_blocking=True)
-
-    def view(index: int, size: int) -> torch.Tensor:
-        return dev[offsets[index]:offsets[index] + size]
-
-    groups = []
-    for gi, width in enumerate(widths):
-        groups.append(GroupBatch(view(9 + 2 * gi, num_tokens),
-                                 view(10 + 2 * gi, num_seqs * width).view(num_seqs, width), width))
-    return StepContext(
-        num_tokens=num_tokens, num_seqs=num_seqs, token_ids=view(0, num_tokens), positions=view(1, num_tokens),
-        cu_q=view(2, num_seqs + 1), ctx_lens=view(3, num_seqs), state_slots=view(4, num_seqs),
-        logit_rows=view(5, len(logit_rows)), num_logit_rows=len(logit_rows),
-        tile_seq=view(6, len(tiles)), tile_q0=view(7, len(tiles)), tile_nq=view(8, len(tiles)),
-        num_tiles=len(tiles), q_tile=tile_rows, max_context=max(ctx_lens), groups=groups, status=status,
-        q_lens_host=q_lens, ctx_lens_host=ctx_lens, state_slots_host=[e.seq.state_slot for e in entries],
-        h2d_bytes=int(host.nbytes))
+    return make_context(layout, dev, tile_rows=tile_rows, max_context=max(ctx_lens), status=status, q_lens=q_lens,
+                        ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries], h2d_bytes=int(host.nbytes))

@@ -15,7 +15,9 @@ import torch
 from ..cache.block_pool import OutOfPages
 from ..cache.manager import CacheManager, SequenceCache
 from ..kernels import ops
-from .batch import SeqStep, StepContext, build_context
+import numpy as np
+
+from .batch import (BatchLayout, SeqStep, StepContext, build_context, fill_host, make_context, validate_entries)
 
 _STATUS_TEXT = {
     1: "a block-table entry pointed outside the page pool",
@@ -30,9 +32,22 @@ class KernelStatusError(RuntimeError):
     """A kernel met an impossible index, skipped the access and reported it."""
 
 
+_SEQ_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+_WIDTH_STEP = 64            # block-table widths of captured decode steps are multiples of this many pages
+
+
+class _CapturedDecode:
+    """A decode step of a fixed layout, captured once and replayed: pinned host buffer, device buffer,
+    the context of views into it, the graph and its output logits."""
+
+    def __init__(self, layout, pinned, dev, ctx, graph, logits, launches):
+        self.layout, self.pinned, self.dev, self.ctx, self.graph, self.logits = layout, pinned, dev, ctx, graph, logits
+        self.launches = launches      # kernels of this package inside the graph
+
+
 class ModelRunner:
     def __init__(self, model, *, page_size: int = 16, num_pages: int, max_seqs: int = 256,
-                 kv_dtype: torch.dtype | None = None):
+                 kv_dtype: torch.dtype | None = None, cuda_graphs: bool = True):
         if not model.loaded:
             raise ValueError("the model has no weights yet")
         self.model = model
@@ -47,6 +62,13 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.last_h2d_bytes = 0
+        #: decode-only steps are replayed as CUDA graphs (one per batch-size and table-width bucket)
+        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and model.graph_safe
+        self._captured: dict[tuple, _CapturedDecode] = {}
+        # captured steps share one memory pool: they never run at the same time and each one's logits are
+        # consumed before the next step starts
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.cuda_graphs else None
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ requests
 
@@ -71,9 +93,13 @@ class ModelRunner:
             for e in entries:
                 self.manager.reserve(e.seq, len(e.tokens))
                 reserved.append(e)
-            ctx = build_context(self.manager, entries, self.device, status=self.status)
-            self.last_h2d_bytes = ctx.h2d_bytes
-            logits = self.model.forward(ctx, self.views)
+            validate_entries(entries)
+            if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= _SEQ_BUCKETS[-1]:
+                logits = self._decode_step_captured(entries)
+            else:
+                ctx = build_context(self.manager, entries, self.device, status=self.status)
+                self.last_h2d_bytes = ctx.h2d_bytes
+                logits = self.model.forward(ctx, self.views)
         except BaseException:
             for e in reserved:
                 self.manager.release_unused(e.seq)
@@ -82,6 +108,62 @@ class ModelRunner:
             self.manager.commit(e.seq, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ------------------------------------------------------------------ captured decode steps
+
+    def _decode_layout(self, entries: list[SeqStep]) -> BatchLayout:
+        n = len(entries)
+        bucket = next(b for b in _SEQ_BUCKETS if b >= n)
+        widths = []
+        for g in self.manager.groups:
+            widest = max(len(self.manager.table_row(e.seq, g.index)) for e in entries)
+            widths.append((max(1, widest) + _WIDTH_STEP - 1) // _WIDTH_STEP * _WIDTH_STEP)
+        # every row's logits are computed; rows that are not wanted are dropped afterwards
+        return BatchLayout(bucket, bucket, bucket, bucket, tuple(widths))
+
+    def _decode_step_captured(self, entries: list[SeqStep]) -> torch.Tensor | None:
+        layout = self._decode_layout(entries)
+        captured = self._captured.get(layout.key())
+        full = [SeqStep(e.seq, e.tokens, [0]) for e in entries]
+        if captured is None:
+            captured = self._capture(layout, full)
+        else:
+            fill_host(self.manager, full, layout, captured.pinned.numpy(), 1)
+            captured.dev.copy_(captured.pinned, non_blocking=True)
+            captured.graph.replay()
+            ops.launch_count += captured.launches
+            self.graph_replays += 1
+        self.last_h2d_bytes = int(captured.pinned.numel() * 4)
+        wanted = [i for i, e in enumerate(entries) if e.want]
+        if not wanted:
+            return None
+        if len(wanted) == len(entries):
+            return captured.logits[:len(entries)]
+        return captured.logits[torch.tensor(wanted, device=self.device)]
+
+    def _capture(self, layout: BatchLayout, entries: list[SeqStep]) -> _CapturedDecode:
+        pinned = torch.empty(layout.total, dtype=torch.int32).pin_memory()
+        dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
+        q_lens, ctx_lens = fill_host(self.manager, entries, layout, pinned.numpy(), 1)
+        dev.copy_(pinned, non_blocking=True)
+        # the split count of the attention kernels is fixed at capture: size it for the widest table of the bucket
+        max_context = max(layout.widths) * self.manager.page_size
+        ctx = make_context(layout, dev, tile_rows=1, max_context=max_context, status=self.status,
+                           q_lens=q_lens, ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries],
+                           h2d_bytes=int(layout.total * 4))
+        # one eager run first (library handles and workspaces come into being outside the capture); it writes the
+        # same cache slots the captured run writes again
+        self.model.forward(ctx, self.views)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(ctx, self.views)
+        launches = ops.launch_count - before
+        graph.replay()
+        captured = _CapturedDecode(layout, pinned, dev, ctx, graph, logits, launches)
+        self._captured[layout.key()] = captured
+        return captured
 
     def raise_on_status(self) -> None:
         """Read the kernels' status word (synchronises) and raise if a kernel reported a bad index."""

@@ -96,10 +96,10 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
                   target_warps: int = 148 * 16) -> int:
     """How many key ranges each query tile is cut into so that a small batch still fills the GPU."""
     items = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8))
-    if items >= target_warps or max_context <= 256:
+    if items >= target_warps or max_context <= 128:
         return 1
     want = (target_warps + items - 1) // items
-    return int(max(1, min(want, (max_context + 255) // 256, 64)))
+    return int(max(1, min(want, (max_context + 127) // 128, 64)))
 
 
 def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,

@@ -73,6 +73,13 @@ class DecoderModel:
         self.head.tie(self.embedding)
         self.loaded = True
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part only enqueues device work that depends on the batch layout alone."""
+        parts = list(self._parts()) + [blk.mixer.position_encoding for blk in self.blocks
+                                       if hasattr(blk.mixer, "position_encoding")]
+        return all(getattr(part, "graph_safe", False) for part in parts)
+
     # ------------------------------------------------------------------ cache needs
 
     def cache_specs(self) -> list[CacheSpec]:

@@ -23,6 +23,9 @@ class PagedAttention(Mixer):
     ``bias`` (bool), ``window`` (keys visible including the query's own, or None),
     ``scale`` (None = head_dim ** -0.5), ``position_encoding`` (a PartSpec)."""
 
+    graph_safe = True
+
+
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
         p = spec.params

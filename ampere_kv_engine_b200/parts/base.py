@@ -59,6 +59,10 @@ class CacheSpec:
 class Part:
     """Common life cycle: build from a spec, declare tensors, load them."""
 
+    #: True when ``forward`` only enqueues device work whose shapes depend on the batch layout alone (no host
+    #: loops over sequences, no host reads), so a decode step through it can be replayed as a CUDA graph.
+    graph_safe = False
+
     def __init__(self, spec: PartSpec, *, hidden_size: int, dtype: torch.dtype, device: torch.device):
         self.spec = spec
         self.hidden_size = hidden_size

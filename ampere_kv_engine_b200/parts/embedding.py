@@ -16,6 +16,9 @@ from .base import ParamSpec, Part
 class TokenEmbedding(Part):
     """params: ``vocab_size``."""
 
+    graph_safe = True
+
+
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
         self.vocab_size = int(spec.params["vocab_size"])
@@ -33,6 +36,9 @@ class TokenEmbedding(Part):
 
 class LinearHead(Part):
     """params: ``vocab_size``, ``tied`` (read the embedding's matrix instead of one's own)."""
+
+    graph_safe = True
+
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)

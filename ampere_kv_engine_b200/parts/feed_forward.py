@@ -17,6 +17,9 @@ from .base import FeedForward, ParamSpec, register_feed_forward
 class GatedMLP(FeedForward):
     """params: ``intermediate_size``, ``activation`` (only ``"silu"``)."""
 
+    graph_safe = True
+
+
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
         self.intermediate_size = int(spec.params["intermediate_size"])

@@ -19,6 +19,9 @@ from .base import Norm, ParamSpec, register_norm
 class RMSNorm(Norm):
     """params: ``size`` (defaults to the hidden size), ``eps``."""
 
+    graph_safe = True
+
+
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
         self.size = int(spec.params.get("size", self.hidden_size))

@@ -18,6 +18,9 @@ from .base import PositionEncoding, register_position_encoding
 class RotaryEmbedding(PositionEncoding):
     """params: ``theta``, ``rotary_dim``."""
 
+    graph_safe = True
+
+
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
         self.theta = float(spec.params["theta"])
@@ -33,5 +36,6 @@ class RotaryEmbedding(PositionEncoding):
 
 @register_position_encoding("none")
 class NoPositionEncoding(PositionEncoding):
+    graph_safe = True
     def fused_rotary(self):
         return None, 0
