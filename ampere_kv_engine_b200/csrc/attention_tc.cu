@@ -1,0 +1,522 @@
+// Tensor-core paged attention for bfloat16 caches: K/V pages are brought into shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, mbarrier completion, no multicast), scores and the weighted sum of
+// V run on mma.sync m16n8k16 with float32 accumulators, the softmax is an online float32 softmax in registers.
+//
+// Two kernels share the inner loop:
+//   * prompt portions: one CTA per (query tile of up to 16 tokens, kv head); warp g owns q-head kvh*G + g, its
+//     16 MMA rows are the tile's tokens; the G warps share every K/V tile (one read per GQA group).
+//   * decoded tokens: one single-warp CTA per (token, kv head, key split); the MMA rows are the G q-heads of the
+//     group; with more than one split, (acc, max, sum) partials go to the merge kernel of paged_attention.cu.
+//
+// Same mathematics as the general kernel and as the reference (ampere_kv/kv_cache.py:76-94,
+// csrc/paged_decode.cu:166-243): score = q.k * scale, key j visible to the query at position t iff j <= t (and
+// j > t - window), float32 softmax, q-head h reads kv-head h / G.
+//
+// Every mbarrier wait is bounded: a wait that runs out records kWaitTimeout in the status word and the CTA
+// leaves without writing results.  Keys past a sequence's end inside its last page may hold anything: their
+// scores are replaced (not multiplied) and their V rows are zeroed in shared memory before use.
+#include "common.cuh"
+#include "launchers.h"
+
+#include <cuda.h>
+#include <math_constants.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace akv {
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;   // try_wait attempts before giving up (about a second)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+// Returns false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_addr(bar);
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct TcParams {
+  PagedAttentionParams p;
+  int box_rows;     // rows of one TMA box = min(page_size, keys per stage)
+};
+
+// Byte offset of (key k, 16-byte chunk c of the head) inside one stage's K or V area.  The area is laid out
+// as [64-dim half][key][128 bytes]; TMA's 128-byte swizzle xors the chunk-in-row with the row's low 3 bits.
+template <int KT>
+__device__ __forceinline__ uint32_t tile_offset(int k, int chunk) {
+  const int half = chunk >> 3, c = chunk & 7;
+  return (uint32_t)(half * KT * 128 + k * 128 + ((c ^ (k & 7)) << 4));
+}
+
+// One warp's share of a key block: scores for its 16 rows against KT keys, online softmax, P.V.
+//   q_frag: A fragments of the warp's 16 query rows, D/16 k-steps of 4 registers
+//   row_pos[2]: absolute position of rows (lane/4) and (lane/4 + 8), -1 for a row that does not exist
+template <int D, int KT>
+__device__ __forceinline__ void process_block(const uint32_t (&q_frag)[D / 16][4], uint32_t k_base, uint32_t v_base,
+                                              int key0, int nvalid, const int (&row_pos)[2], int window,
+                                              float scale_log2, float (&m)[2], float (&l)[2],
+                                              float (&o)[D / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  constexpr int NT = KT / 8;   // score n-tiles
+  float s[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+  }
+  // S = Q K^T
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    if (j * 8 < nvalid) {
+#pragma unroll
+      for (int t = 0; t < D / 16; t += 2) {
+        uint32_t b0, b1, b2, b3;
+        const int key = j * 8 + (lane & 7);
+        const int chunk = 2 * t + (lane >> 3);
+        ldmatrix_x4(k_base + tile_offset<KT>(key, chunk), b0, b1, b2, b3);
+        mma_bf16(s[j], q_frag[t], b0, b1);
+        mma_bf16(s[j], q_frag[t + 1], b2, b3);
+      }
+    }
+  }
+  // mask, scale, block max
+  float bmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = e >> 1;
+      const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+      const bool visible = (j * 8 + (lane & 3) * 2 + (e & 1)) < nvalid && key <= row_pos[r] &&
+                           (window <= 0 || key > row_pos[r] - window);
+      const float v = visible ? s[j][e] * scale_log2 : -CUDART_INF_F;
+      s[j][e] = v;
+      bmax[r] = fmaxf(bmax[r], v);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    bmax[r] = fmaxf(bmax[r], __shfl_xor_sync(0xffffffffu, bmax[r], 1));
+    bmax[r] = fmaxf(bmax[r], __shfl_xor_sync(0xffffffffu, bmax[r], 2));
+  }
+  float alpha[2], m_new[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    m_new[r] = fmaxf(m[r], bmax[r]);
+    alpha[r] = (m_new[r] == -CUDART_INF_F) ? 1.f : exp2f(m[r] - m_new[r]);
+    m[r] = m_new[r];
+    l[r] *= alpha[r];
+  }
+#pragma unroll
+  for (int v = 0; v < D / 8; ++v) {
+    o[v][0] *= alpha[0];
+    o[v][1] *= alpha[0];
+    o[v][2] *= alpha[1];
+    o[v][3] *= alpha[1];
+  }
+  // P = exp2(S - m), row sums (per-lane partial sums; reduced over the quad at the end)
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = e >> 1;
+      const float pv = (s[j][e] == -CUDART_INF_F) ? 0.f : exp2f(s[j][e] - m_new[r]);
+      s[j][e] = pv;
+      l[r] += pv;
+    }
+  }
+  // O += P V, 16 keys at a time
+#pragma unroll
+  for (int u = 0; u < KT / 16; ++u) {
+    if (u * 16 < nvalid) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * u][0], s[2 * u][1]);
+      a[1] = pack_bf16(s[2 * u][2], s[2 * u][3]);
+      a[2] = pack_bf16(s[2 * u + 1][0], s[2 * u + 1][1]);
+      a[3] = pack_bf16(s[2 * u + 1][2], s[2 * u + 1][3]);
+#pragma unroll
+      for (int v = 0; v < D / 8; v += 2) {
+        uint32_t b0, b1, b2, b3;
+        const int key = u * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int chunk = v + (lane >> 4);
+        ldmatrix_x4_trans(v_base + tile_offset<KT>(key, chunk), b0, b1, b2, b3);
+        mma_bf16(o[v], a, b0, b1);
+        mma_bf16(o[v + 1], a, b2, b3);
+      }
+    }
+  }
+}
+
+// Shared-memory layout: [stage][K area | V area], each area KT * D * 2 bytes, then the mbarriers.
+template <int D, int KT, int STAGES>
+struct Smem {
+  static constexpr int kArea = KT * D * 2;
+  static constexpr int kStage = 2 * kArea;
+  static constexpr int kBytes = STAGES * kStage + STAGES * 8 + 1024;   // + alignment slack
+};
+
+// Issue the TMA loads of key block `block` (keys [lo + block*KT, ...)) into `stage`.  One thread calls this.
+template <int D, int KT>
+__device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMap* k_map, const CUtensorMap* v_map,
+                                            const int32_t* table, int kvh, int key0, int key_end, uint8_t* stage,
+                                            uint64_t* bar) {
+  const PagedAttentionParams& p = tp.p;
+  const int P = p.page_size, rows = tp.box_rows;
+  const int boxes = KT / rows;
+  uint32_t bytes = 0;
+  int page_of[KT / 8];   // rows >= 8, so at most KT / 8 boxes
+#pragma unroll
+  for (int b = 0; b < KT / 8; ++b) {
+    page_of[b] = -1;
+    if (b < boxes) {
+      const int key = key0 + b * rows;
+      if (key < key_end) {
+        const int logical = key / P;
+        int page = logical < p.table_width ? table[logical] : -1;
+        if (page < 0 || page >= p.num_pages) {
+          set_status(p.status, kBadPage);
+          page = -1;
+        }
+        page_of[b] = page;
+        if (page >= 0) bytes += 2u * rows * D * 2u;
+      }
+    }
+  }
+  mbar_expect_tx(bar, bytes);
+#pragma unroll
+  for (int b = 0; b < KT / 8; ++b) {
+    if (b < boxes && page_of[b] >= 0) {
+      const int key = key0 + b * rows;
+      const int y = (page_of[b] * p.num_kv_heads + kvh) * P + key % P;
+#pragma unroll
+      for (int h = 0; h < D / 64; ++h) {
+        tma_load_2d(stage + h * KT * 128 + b * rows * 128, k_map, h * 64, y, bar);
+        tma_load_2d(stage + KT * D * 2 + h * KT * 128 + b * rows * 128, v_map, h * 64, y, bar);
+      }
+    }
+  }
+}
+
+// Zero the V rows [first, KT) of a stage (keys past the end of the sequence).
+template <int D, int KT>
+__device__ __forceinline__ void zero_v_rows(uint8_t* stage, int first, int tid, int nthreads) {
+  uint8_t* v_area = stage + KT * D * 2;
+  const int chunks_per_row = 8;   // 128 bytes
+  for (int h = 0; h < D / 64; ++h) {
+    const int total = (KT - first) * chunks_per_row;
+    for (int i = tid; i < total; i += nthreads) {
+      const int row = first + i / chunks_per_row, c = i % chunks_per_row;
+      *reinterpret_cast<uint4*>(v_area + h * KT * 128 + row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+template <int D, int KT, int STAGES, bool DECODE>
+__global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
+                                    const __grid_constant__ CUtensorMap v_map, TcParams tp) {
+  const PagedAttentionParams& p = tp.p;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Smem<D, KT, STAGES>::kStage);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+  const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
+  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+
+  const int seq = p.tile_seq[tile];
+  const int q0 = p.tile_q0[tile];
+  const int nq = p.tile_nq[tile];
+  if (nq <= 0) return;
+  const int ctx = p.ctx_lens[seq];
+  const int seq_q0 = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - seq_q0;
+  const int tile_pos = ctx - q_len + (q0 - seq_q0);
+
+  // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
+  int row_pos[2];
+  int row_token[2], row_head[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = (lane >> 2) + 8 * r;
+    if (DECODE) {
+      row_token[r] = q0;
+      row_head[r] = kvh * G + row;
+      row_pos[r] = row < G ? tile_pos : -1;
+    } else {
+      row_token[r] = q0 + row;
+      row_head[r] = kvh * G + warp;
+      row_pos[r] = row < nq ? tile_pos + row : -1;
+    }
+  }
+  const int pos_first = tile_pos, pos_last = DECODE ? tile_pos : tile_pos + nq - 1;
+  int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  lo = lo / tp.box_rows * tp.box_rows;     // boxes start on box boundaries inside a page
+  const int hi = pos_last + 1;
+  int range_lo = lo, range_hi = hi;
+  if (DECODE && p.num_splits > 1) {
+    int per = (hi - lo + p.num_splits - 1) / p.num_splits;
+    per = (per + KT - 1) / KT * KT;
+    range_lo = lo + split * per;
+    range_hi = min(hi, range_lo + per);
+  }
+  const int num_blocks = range_hi > range_lo ? (range_hi - range_lo + KT - 1) / KT : 0;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
+  if (tid == 0) {
+    for (int b = 0; b < STAGES - 1 && b < num_blocks; ++b)
+      issue_block<D, KT>(tp, &k_map, &v_map, table, kvh, range_lo + b * KT, range_hi,
+                         smem + b * Smem<D, KT, STAGES>::kStage, &bars[b]);
+  }
+
+  // query fragments straight from global memory
+  uint32_t q_frag[D / 16][4];
+  {
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+#pragma unroll
+    for (int t = 0; t < D / 16; ++t) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int col = t * 16 + (lane & 3) * 2;
+        uint32_t lo_pair = 0, hi_pair = 0;
+        if (row_pos[r] >= 0) {
+          const __nv_bfloat16* src = q + ((int64_t)row_token[r] * NH + row_head[r]) * D + col;
+          lo_pair = *reinterpret_cast<const uint32_t*>(src);
+          hi_pair = *reinterpret_cast<const uint32_t*>(src + 8);
+        }
+        q_frag[t][r] = lo_pair;
+        q_frag[t][2 + r] = hi_pair;
+      }
+    }
+  }
+
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int v = 0; v < D / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
+  const float scale_log2 = p.scale * kLog2e;
+
+  // A warp whose wait ran out keeps walking the loop (the block-wide barriers stay matched) but computes nothing.
+  bool ok = true;
+  for (int b = 0; b < num_blocks; ++b) {
+    const int stage_index = b % STAGES;
+    uint8_t* stage = smem + stage_index * Smem<D, KT, STAGES>::kStage;
+    // everyone is done with the stage that block b + STAGES - 1 will overwrite (it held block b - 1)
+    __syncthreads();
+    if (tid == 0 && b + STAGES - 1 < num_blocks) {
+      const int nb = b + STAGES - 1;
+      issue_block<D, KT>(tp, &k_map, &v_map, table, kvh, range_lo + nb * KT, range_hi,
+                         smem + (nb % STAGES) * Smem<D, KT, STAGES>::kStage, &bars[nb % STAGES]);
+    }
+    if (ok && !mbar_wait(&bars[stage_index], (b / STAGES) & 1)) ok = false;
+    const int key0 = range_lo + b * KT;
+    const int nvalid = min(KT, range_hi - key0);
+    if (nvalid < KT) {
+      // V rows past the end may hold anything (or were never loaded): make them zero before P.V reads them
+      zero_v_rows<D, KT>(stage, nvalid, tid, nthreads);
+      __syncthreads();
+    }
+    if (ok)
+      process_block<D, KT>(q_frag, smem_addr(stage), smem_addr(stage + KT * D * 2), key0, nvalid, row_pos, p.window,
+                           scale_log2, m, l, o);
+    if (nvalid < KT) {
+      // should a later TMA load reuse the zeroed rows (async proxy), the generic writes are ordered before it
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+  }
+  if (!ok) {
+    if (lane == 0) set_status(p.status, kWaitTimeout);
+    return;
+  }
+
+  // finish: reduce the row sums over the quad, write the output row or the partial
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (row_pos[r] < 0) continue;
+    const int64_t row = (int64_t)row_token[r] * NH + row_head[r];
+    if (!DECODE || p.num_splits == 1) {
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + row * D;
+      const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+#pragma unroll
+      for (int v = 0; v < D / 8; ++v) {
+        const int col = v * 8 + (lane & 3) * 2;
+        *reinterpret_cast<uint32_t*>(out + col) = pack_bf16(o[v][2 * r] * inv, o[v][2 * r + 1] * inv);
+      }
+    } else {
+      float* part = p.partials + (row * p.num_splits + split) * (int64_t)(D + 2);
+#pragma unroll
+      for (int v = 0; v < D / 8; ++v) {
+        const int col = v * 8 + (lane & 3) * 2;
+        part[col] = o[v][2 * r];
+        part[col + 1] = o[v][2 * r + 1];
+      }
+      if ((lane & 3) == 0) {
+        part[D] = m[r] * kLn2;     // back to natural-log units, as the merge kernel expects
+        part[D + 1] = l[r];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// A 2-D map over a cache tensor seen as [pages * kv_heads * page_size rows, head_dim] bfloat16, boxes of
+// 64 columns (128 bytes) by `box_rows` rows, 128-byte swizzle.
+bool cache_map(const void* base, int64_t rows, int head_dim, int box_rows, CUtensorMap* out) {
+  static std::mutex mutex;
+  static std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> cache;
+  std::lock_guard<std::mutex> guard(mutex);
+  const auto key = std::make_tuple(base, rows, head_dim, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult res = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return false;
+  cache[key] = map;
+  *out = map;
+  return true;
+}
+
+template <int D, int KT, int STAGES, bool DECODE>
+int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
+              cudaStream_t stream) {
+  auto kernel = attention_tc_kernel<D, KT, STAGES, DECODE>;
+  constexpr int smem = Smem<D, KT, STAGES>::kBytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  const int G = p.num_heads / p.num_kv_heads;
+  TcParams tp{p, box_rows};
+  dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
+  const int threads = DECODE ? 32 : 32 * G;
+  kernel<<<grid, threads, smem, stream>>>(k_map, v_map, tp);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// Whether the tensor-core kernels take this problem; otherwise the caller uses the general kernel.
+bool attention_tc_supported(const PagedAttentionParams& p) {
+  if (p.dtype != kBFloat16) return false;
+  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  const int G = p.num_heads / p.num_kv_heads;
+  if (p.num_heads % p.num_kv_heads || G < 1 || G > 16) return false;
+  if (p.page_size < 8 || (p.page_size & (p.page_size - 1))) return false;   // boxes of 8.. rows, power of two
+  if (p.num_kv_heads > 65535 || p.num_splits > 65535) return false;
+  if (p.q_tile > 16) return false;
+  if (p.q_tile > 1 && G > 8) return false;    // prompt kernel: one warp per q-head of the group
+  return encode_fn() != nullptr;
+}
+
+int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
+  const bool decode = p.q_tile == 1;
+  const int kt = decode ? 32 : 64;
+  const int box_rows = p.page_size < kt ? p.page_size : kt;
+  const int64_t rows = p.num_pages * p.num_kv_heads * (int64_t)p.page_size;
+  CUtensorMap k_map, v_map;
+  if (!cache_map(p.k_cache, rows, p.head_dim, box_rows, &k_map) ||
+      !cache_map(p.v_cache, rows, p.head_dim, box_rows, &v_map))
+    return (int)cudaErrorInvalidValue;
+  if (decode) {
+    if (p.head_dim == 128) return launch_tc<128, 32, 4, true>(p, box_rows, k_map, v_map, stream);
+    return launch_tc<64, 32, 4, true>(p, box_rows, k_map, v_map, stream);
+  }
+  if (p.head_dim == 128) return launch_tc<128, 64, 3, false>(p, box_rows, k_map, v_map, stream);
+  return launch_tc<64, 64, 3, false>(p, box_rows, k_map, v_map, stream);
+}
+
+}  // namespace akv

@@ -253,7 +253,7 @@ void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                      const Tensor& block_table, const Tensor& cu_q, const Tensor& ctx_lens, const Tensor& tile_seq,
                      const Tensor& tile_q0, const Tensor& tile_nq, const OptTensor& partials, int64_t num_tiles,
                      int64_t q_tile, int64_t num_splits, int64_t num_heads, int64_t num_kv_heads, int64_t window,
-                     double scale, const OptTensor& status) {
+                     double scale, const OptTensor& status, int64_t kernel) {
   check_cuda(q, "q");
   check_cuda(out, "out");
   check_same(q, out, "q", "out");
@@ -303,6 +303,7 @@ void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
   p.page_size = g.page_size;
   p.num_pages = g.num_pages;
   p.window = (int)window;
+  p.kernel = (int)kernel;
   p.scale = (float)scale;
   p.dtype = dtype_code(q, "q");
   p.status = status_ptr(status);
@@ -343,6 +344,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),
         py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("window"), py::arg("scale"),
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("kernel") = 0);
   m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("uniform"), py::arg("tokens"));
 }

@@ -72,11 +72,15 @@ struct PagedAttentionParams {
   int num_heads, num_kv_heads, head_dim, page_size;
   int64_t num_pages;
   int window;                  // 0 = all keys
+  int kernel;                  // 0 = best kernel that takes the sizes, 1 = the general kernel
   float scale;
   int dtype;
   int* status;
 };
 int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream);
+// The tensor-core kernels (attention_tc.cu): whether they take the problem, and their launch (without the merge).
+bool attention_tc_supported(const PagedAttentionParams& p);
+int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream);
 
 // tokens[r] = argmax(logits[r]) where temperature[r] == 0, else the inverse-CDF draw of
 // softmax(logits[r] / temperature[r]) at uniform[r].

@@ -221,6 +221,15 @@ __global__ void merge_splits_kernel(const float* __restrict__ partials, T* __res
 }
 
 template <typename T>
+static int launch_merge(const PagedAttentionParams& p, cudaStream_t stream) {
+  const int64_t rows = p.num_tokens * p.num_heads;
+  if (rows > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const int threads = p.head_dim <= 32 ? 32 : (p.head_dim <= 64 ? 64 : 128);
+  merge_splits_kernel<T><<<(unsigned)rows, threads, 0, stream>>>(p.partials, (T*)p.out, p.num_splits, p.head_dim);
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
 static int launch_typed(const PagedAttentionParams& p, cudaStream_t stream) {
   const int G = p.num_heads / p.num_kv_heads;
   const int row_groups = (p.q_tile * G + kAttnRows - 1) / kAttnRows;
@@ -242,21 +251,20 @@ static int launch_typed(const PagedAttentionParams& p, cudaStream_t stream) {
 #undef AKV_LAUNCH
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return (int)err;
-  if (p.num_splits > 1) {
-    const int64_t rows = p.num_tokens * p.num_heads;
-    if (rows > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-    const int threads = p.head_dim <= 32 ? 32 : (p.head_dim <= 64 ? 64 : 128);
-    merge_splits_kernel<T><<<(unsigned)rows, threads, 0, stream>>>(p.partials, (T*)p.out, p.num_splits,
-                                                                  p.head_dim);
-    err = cudaGetLastError();
-  }
-  return (int)err;
+  return p.num_splits > 1 ? launch_merge<T>(p, stream) : 0;
 }
 
 int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream) {
   if (p.num_tiles == 0 || p.num_tokens == 0) return 0;
   if (p.head_dim % 16 || p.head_dim > 256 || p.num_heads % p.num_kv_heads || p.num_splits < 1)
     return (int)cudaErrorInvalidValue;
+  if (p.kernel == 0 && attention_tc_supported(p)) {
+    PagedAttentionParams q = p;
+    if (q.q_tile > 1) q.num_splits = 1;          // the prompt kernel walks all keys of a tile itself
+    const int err = launch_attention_tc(q, stream);
+    if (err != 0) return err;
+    return q.num_splits > 1 ? launch_merge<__nv_bfloat16>(q, stream) : 0;
+  }
   return p.dtype == kBFloat16 ? launch_typed<__nv_bfloat16>(p, stream) : launch_typed<float>(p, stream);
 }
 

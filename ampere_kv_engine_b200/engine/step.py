@@ -40,9 +40,29 @@ class _CapturedDecode:
     """A decode step of a fixed layout, captured once and replayed: pinned host buffer, device buffer,
     the context of views into it, the graph and its output logits."""
 
-    def __init__(self, layout, pinned, dev, ctx, graph, logits, launches):
-        self.layout, self.pinned, self.dev, self.ctx, self.graph, self.logits = layout, pinned, dev, ctx, graph, logits
+    RING = 4
+
+    def __init__(self, layout, dev, ctx, graph, logits, launches):
+        self.layout, self.dev, self.ctx, self.graph, self.logits = layout, dev, ctx, graph, logits
         self.launches = launches      # kernels of this package inside the graph
+        # The host may run several steps ahead of the device, so the staging buffer of one step must not be
+        # rewritten before its copy has run: a small ring of pinned buffers, each guarded by an event.
+        self.pinned = [torch.empty(layout.total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.copied = [None] * self.RING
+        self.turn = 0
+
+    def stage(self):
+        """The next free pinned buffer (waits for its last copy to have run)."""
+        self.turn = (self.turn + 1) % self.RING
+        if self.copied[self.turn] is not None:
+            self.copied[self.turn].synchronize()
+        return self.pinned[self.turn]
+
+    def upload(self, pinned):
+        self.dev.copy_(pinned, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.copied[self.turn] = event
 
 
 class ModelRunner:
@@ -128,12 +148,13 @@ class ModelRunner:
         if captured is None:
             captured = self._capture(layout, full)
         else:
-            fill_host(self.manager, full, layout, captured.pinned.numpy(), 1)
-            captured.dev.copy_(captured.pinned, non_blocking=True)
+            pinned = captured.stage()
+            fill_host(self.manager, full, layout, pinned.numpy(), 1)
+            captured.upload(pinned)
             captured.graph.replay()
             ops.launch_count += captured.launches
             self.graph_replays += 1
-        self.last_h2d_bytes = int(captured.pinned.numel() * 4)
+        self.last_h2d_bytes = int(layout.total * 4)
         wanted = [i for i, e in enumerate(entries) if e.want]
         if not wanted:
             return None
@@ -145,7 +166,7 @@ class ModelRunner:
         pinned = torch.empty(layout.total, dtype=torch.int32).pin_memory()
         dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         q_lens, ctx_lens = fill_host(self.manager, entries, layout, pinned.numpy(), 1)
-        dev.copy_(pinned, non_blocking=True)
+        dev.copy_(pinned, non_blocking=False)
         # the split count of the attention kernels is fixed at capture: size it for the widest table of the bucket
         max_context = max(layout.widths) * self.manager.page_size
         ctx = make_context(layout, dev, tile_rows=1, max_context=max_context, status=self.status,
@@ -161,7 +182,7 @@ class ModelRunner:
             logits = self.model.forward(ctx, self.views)
         launches = ops.launch_count - before
         graph.replay()
-        captured = _CapturedDecode(layout, pinned, dev, ctx, graph, logits, launches)
+        captured = _CapturedDecode(layout, dev, ctx, graph, logits, launches)
         self._captured[layout.key()] = captured
         return captured
 

@@ -80,7 +80,8 @@ class FakeExt:
         self._write(k.view(-1, nkv, d), v.view(-1, nkv, d), slots, k_cache, v_cache)
 
     def paged_attention(self, q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
-                        partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, window, scale, status=None):
+                        partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, window, scale, status=None,
+                        kernel=0):
         page_size, d = k_cache.shape[2], k_cache.shape[3]
         group = num_heads // num_kv_heads
         cu = cu_q.tolist()

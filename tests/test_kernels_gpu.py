@@ -206,7 +206,7 @@ class PagedCase:
         self.tile_rows = tile_rows
         self.tiles = [torch.tensor([t[i] for t in tiles], dtype=torch.int32) for i in range(3)]
 
-    def run(self, ops, window=0, splits=1, scale=None):
+    def run(self, ops, window=0, splits=1, scale=None, kernel="auto"):
         scale = scale if scale is not None else self.d ** -0.5
         q = torch.cat([x.reshape(x.shape[0], -1) for x in self.q_seq])
         status = status_word()
@@ -214,7 +214,7 @@ class PagedCase:
             dev(q), dev(self.k_cache), dev(self.v_cache), dev(self.table), dev(self.cu),
             dev(torch.tensor(self.ctx_lens, dtype=torch.int32)), dev(self.tiles[0]), dev(self.tiles[1]),
             dev(self.tiles[2]), num_tiles=len(self.tiles[0]), q_tile=self.tile_rows, num_splits=splits,
-            num_heads=self.nh, num_kv_heads=self.nkv, window=window, scale=scale, status=status)
+            num_heads=self.nh, num_kv_heads=self.nkv, window=window, scale=scale, status=status, kernel=kernel)
         assert int(status.item()) == 0
         return out.float().cpu()
 
@@ -239,6 +239,24 @@ def test_paged_attention_mixed_batch(ops, dtype, nh, nkv, d, page, window):
     want = case.reference(window)
     for splits in (1, 3):
         torch.testing.assert_close(case.run(ops, window, splits), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,d,page", [(32, 8, 128, 16), (8, 8, 64, 32), (16, 1, 128, 64), (6, 2, 128, 8)])
+@pytest.mark.parametrize("window", [0, 50])
+def test_tensor_core_and_general_kernels_agree(ops, nh, nkv, d, page, window):
+    """bfloat16 at head sizes 64 and 128 takes the TMA + tensor-core kernels; forcing the general kernel on the
+    same problem must give the same answer (both are also held against the plain reference)."""
+    dtype = torch.bfloat16
+    mixed = PagedCase(dtype, nh, nkv, d, page, q_lens=[1, 37, 5, 1, 16, 70], ctx_lens=[200, 37, 150, 1, 16, 333],
+                      seed=nh + page)
+    want = mixed.reference(window)
+    torch.testing.assert_close(mixed.run(ops, window, 1, kernel="auto"), want, **tol(dtype))
+    torch.testing.assert_close(mixed.run(ops, window, 1, kernel="general"), want, **tol(dtype))
+    decode = PagedCase(dtype, nh, nkv, d, page, q_lens=[1] * 6, ctx_lens=[1, 31, 32, 33, 700, 129], seed=nh)
+    want = decode.reference(window)
+    for splits in (1, 2, 7):
+        torch.testing.assert_close(decode.run(ops, window, splits, kernel="auto"), want, **tol(dtype))
+    torch.testing.assert_close(decode.run(ops, window, 3, kernel="general"), want, **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
