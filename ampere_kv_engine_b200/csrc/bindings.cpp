@@ -112,10 +112,19 @@ void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, T
   const int code = dtype_code(out, "out");
   AKV_CHECK(h * 4 <= 200 * 1024, "add_rmsnorm: hidden size ", h, " exceeds the kernel's limit of 51200");
   const void* delta_ptr = nullptr;
+  int delta_parts = 0;
   if (delta.has_value()) {
     check_cuda(*delta, "delta");
-    check_same(*delta, out, "delta", "out");
-    AKV_CHECK(delta->numel() == n * h, "delta must be [tokens, hidden]");
+    if (delta->dim() == 3) {
+      // float32 partial sums of a split-K product, [parts, tokens, hidden]
+      AKV_CHECK(delta->scalar_type() == at::kFloat, "a 3-D delta holds float32 partial sums");
+      AKV_CHECK(delta->size(0) >= 1 && delta->size(1) == n && delta->size(2) == h,
+                "a 3-D delta must be [parts, tokens, hidden]");
+      delta_parts = (int)delta->size(0);
+    } else {
+      check_same(*delta, out, "delta", "out");
+      AKV_CHECK(delta->numel() == n * h, "delta must be [tokens, hidden]");
+    }
     delta_ptr = delta->data_ptr();
   }
   const int* rows_ptr = nullptr;
@@ -129,7 +138,8 @@ void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, T
     AKV_CHECK(out.numel() == n * h, "out must be [tokens, hidden]");
   }
   c10::cuda::CUDAGuard guard(hidden.device());
-  check_launch(akv::launch_add_rmsnorm(hidden.data_ptr<float>(), delta_ptr, weight.data_ptr<float>(), out.data_ptr(),
+  check_launch(akv::launch_add_rmsnorm(hidden.data_ptr<float>(), delta_ptr, delta_parts, weight.data_ptr<float>(),
+                                       out.data_ptr(),
                                        rows_ptr, num_rows, n, h, (float)eps, code, status_ptr(status),
                                        stream_of(hidden)),
                "add_rmsnorm");
@@ -138,15 +148,68 @@ void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, T
 void silu_mul(const Tensor& gate_up, Tensor& out) {
   check_cuda(gate_up, "gate_up");
   check_cuda(out, "out");
-  check_same(gate_up, out, "gate_up", "out");
-  AKV_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
-  const int64_t n = gate_up.size(0), inter = gate_up.size(1) / 2;
+  int parts = 0;
+  Tensor first = gate_up;
+  if (gate_up.dim() == 3) {
+    AKV_CHECK(gate_up.scalar_type() == at::kFloat, "a 3-D gate_up holds float32 partial sums");
+    parts = (int)gate_up.size(0);
+    AKV_CHECK(parts >= 1, "gate_up must hold at least one part");
+    first = gate_up.select(0, 0);
+    AKV_CHECK(first.device() == out.device(), "gate_up and out must be on the same device");
+  } else {
+    check_same(gate_up, out, "gate_up", "out");
+  }
+  AKV_CHECK(first.dim() == 2 && first.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
+  const int64_t n = first.size(0), inter = first.size(1) / 2;
   AKV_CHECK(out.numel() == n * inter, "out must be [tokens, intermediate]");
   c10::cuda::CUDAGuard guard(gate_up.device());
-  check_launch(akv::launch_silu_mul(gate_up.data_ptr(), out.data_ptr(), n, inter, dtype_code(out, "out"),
+  check_launch(akv::launch_silu_mul(gate_up.data_ptr(), parts, out.data_ptr(), n, inter, dtype_code(out, "out"),
                                     stream_of(out)),
                "silu_mul");
 }
+
+// x @ w^T for few tokens on the tcgen05 tensor cores.  `out` is either [tokens, features] (float32 or bfloat16:
+// the K splits are added up inside the kernel) or a 3-D float32 [splits, tokens, features] that receives every
+// split's partial sum as it is.
+void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits, const OptTensor& status) {
+  check_cuda(x, "x");
+  check_cuda(w, "w");
+  check_cuda(out, "out");
+  AKV_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "x and w must be bfloat16");
+  AKV_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1), "x must be [tokens, k] and w [features, k]");
+  AKV_CHECK(akv::small_m_gemm_supported(x.size(0), w.size(0), x.size(1)),
+            "small_m_gemm takes 1..64 tokens and a K that is a multiple of 8 and at least 64; got ", x.size(0),
+            " tokens, K = ", x.size(1));
+  AKV_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0,
+            "x and w must be 16-byte aligned");
+  const int64_t kb_total = (x.size(1) + 63) / 64;
+  void* out_ptr = nullptr;
+  float* parts_ptr = nullptr;
+  int out_code = 0;
+  if (out.dim() == 3) {
+    AKV_CHECK(out.scalar_type() == at::kFloat && out.size(1) == x.size(0) && out.size(2) == w.size(0),
+              "a 3-D out must be float32 [splits, tokens, features]");
+    splits = out.size(0);
+    AKV_CHECK(splits >= 1 && splits <= kb_total, "splits must be between 1 and the number of 64-element K blocks");
+    parts_ptr = out.data_ptr<float>();
+  } else {
+    AKV_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == w.size(0), "out must be [tokens, features]");
+    AKV_CHECK((splits == 1 || splits == 2 || splits == 4 || splits == 8) && splits <= kb_total,
+              "splits must be 1, 2, 4 or 8 and at most the number of 64-element K blocks, got ", splits);
+    out_code = dtype_code(out, "out");
+    out_ptr = out.data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_small_m_gemm(x.data_ptr(), w.data_ptr(), out_ptr, out_code, parts_ptr, x.size(0), w.size(0),
+                                        x.size(1), (int)splits, status_ptr(status), stream_of(x)),
+               "small_m_gemm");
+}
+
+bool small_m_gemm_supported(int64_t tokens, int64_t features, int64_t k) {
+  return akv::small_m_gemm_supported(tokens, features, k);
+}
+
+int64_t small_m_gemm_splits(int64_t features, int64_t k) { return akv::small_m_gemm_splits(features, k); }
 
 struct CacheGeometry {
   int64_t num_pages;
@@ -174,18 +237,26 @@ void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTen
                         int64_t rotary_dim, double eps, const OptTensor& status) {
   check_cuda(qkv, "qkv");
   check_cuda(q_out, "q_out");
-  check_same(qkv, q_out, "qkv", "q_out");
+  int qkv_parts = 0;
+  if (qkv.dim() == 3) {
+    AKV_CHECK(qkv.scalar_type() == at::kFloat && qkv.size(0) >= 1, "a 3-D qkv holds float32 partial sums");
+    AKV_CHECK(qkv.device() == q_out.device(), "qkv and q_out must be on the same device");
+    qkv_parts = (int)qkv.size(0);
+  } else {
+    check_same(qkv, q_out, "qkv", "q_out");
+  }
   AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0, "head counts and head_dim must be positive");
   AKV_CHECK(head_dim % 2 == 0 && head_dim <= 512, "qk_norm_rope_write: head_dim must be even and <= 512, got ",
               head_dim);
   const int64_t width = (num_heads + 2 * num_kv_heads) * head_dim;
-  AKV_CHECK(qkv.dim() == 2 && qkv.size(1) == width, "qkv must be [tokens, (heads + 2 kv_heads) * head_dim = ",
-              width, "]");
-  const int64_t n = qkv.size(0);
+  AKV_CHECK((qkv.dim() == 2 || qkv.dim() == 3) && qkv.size(-1) == width,
+            "qkv must be [tokens, (heads + 2 kv_heads) * head_dim = ", width, "]");
+  const int64_t n = qkv.size(-2);
   check_i32(positions, "positions", n);
   AKV_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
   akv::QkRopeWriteParams p{};
   p.qkv = qkv.data_ptr();
+  p.qkv_parts = qkv_parts;
   p.positions = positions.data_ptr<int>();
   p.q_out = q_out.data_ptr();
   if (slots.has_value()) {
@@ -201,19 +272,19 @@ void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTen
     p.inv_freq = inv_freq->data_ptr<float>();
   }
   if (k_out.has_value()) {
-    check_cuda(*k_out, "k_out"); check_same(*k_out, qkv, "k_out", "qkv");
+    check_cuda(*k_out, "k_out"); check_same(*k_out, q_out, "k_out", "q_out");
     AKV_CHECK(k_out->numel() == n * num_kv_heads * head_dim, "k_out must be [tokens, kv_heads * head_dim]");
     p.k_out = k_out->data_ptr();
   }
   if (v_out.has_value()) {
-    check_cuda(*v_out, "v_out"); check_same(*v_out, qkv, "v_out", "qkv");
+    check_cuda(*v_out, "v_out"); check_same(*v_out, q_out, "v_out", "q_out");
     AKV_CHECK(v_out->numel() == n * num_kv_heads * head_dim, "v_out must be [tokens, kv_heads * head_dim]");
     p.v_out = v_out->data_ptr();
   }
   AKV_CHECK(k_cache.has_value() == v_cache.has_value(), "k_cache and v_cache come together");
   if (k_cache.has_value()) {
     AKV_CHECK(slots.has_value(), "a cache to write needs slots");
-    const CacheGeometry g = check_cache(*k_cache, *v_cache, (int)num_kv_heads, (int)head_dim, qkv);
+    const CacheGeometry g = check_cache(*k_cache, *v_cache, (int)num_kv_heads, (int)head_dim, q_out);
     p.k_cache = k_cache->data_ptr();
     p.v_cache = v_cache->data_ptr();
     p.num_pages = g.num_pages;
@@ -225,7 +296,7 @@ void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTen
   p.head_dim = (int)head_dim;
   p.rotary_dim = (int)rotary_dim;
   p.eps = (float)eps;
-  p.dtype = dtype_code(qkv, "qkv");
+  p.dtype = dtype_code(q_out, "q_out");
   p.status = status_ptr(status);
   c10::cuda::CUDAGuard guard(qkv.device());
   check_launch(akv::launch_qk_norm_rope_write(p, stream_of(qkv)), "qk_norm_rope_write");
@@ -334,6 +405,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rmsnorm", &add_rmsnorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
         py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"));
+  m.def("small_m_gemm", &small_m_gemm, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("splits") = 1,
+        py::arg("status") = py::none());
+  m.def("small_m_gemm_supported", &small_m_gemm_supported);
+  m.def("small_m_gemm_splits", &small_m_gemm_splits);
   m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),
         py::arg("q_weight"), py::arg("k_weight"), py::arg("inv_freq"), py::arg("q_out"), py::arg("k_out"),
         py::arg("v_out"), py::arg("k_cache"), py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"),

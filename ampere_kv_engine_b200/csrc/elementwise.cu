@@ -53,16 +53,17 @@ int launch_embedding(const int32_t* ids, const void* table, float* hidden, int64
   return (int)cudaGetLastError();
 }
 
-// One block per output row.  Pass 1 adds the delta into the residual stream (whole-batch
-// form) and accumulates the sum of squares; pass 2 re-reads the row (it is still in L1/L2)
-// and writes the normalised, weighted values.
-template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
+// One block per output row.  Pass 1 adds the delta into the residual stream (whole-batch form) and accumulates
+// the sum of squares; pass 2 reads the row back from shared memory and writes the normalised, weighted values.
+// The delta is either one tensor in the activation type or `num_parts` float32 partial sums of a split-K product
+// ([num_parts, tokens, hidden]) that are added up here.
+template <typename T, typename TD>
+__global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const TD* __restrict__ delta, int num_parts,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int32_t* __restrict__ rows, int64_t num_tokens,
                                    int64_t hidden_size, float eps, int* status) {
   __shared__ float scratch[33];
-  extern __shared__ float row_cache[];  // hidden_size floats when it fits, else unused
+  extern __shared__ float row_cache[];  // hidden_size floats
   const int64_t out_row = blockIdx.x;
   int64_t src = out_row;
   const bool gathered = rows != nullptr;
@@ -74,12 +75,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
     }
   }
   float* h = hidden + src * hidden_size;
-  const T* d = delta ? delta + src * hidden_size : nullptr;
+  const TD* d = delta ? delta + src * hidden_size : nullptr;
+  const int64_t part_stride = num_tokens * hidden_size;
   float ss = 0.f;
   for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) {
     float v = h[i];
     if (d) {
-      v += to_float<T>(d[i]);
+      float add = 0.f;
+      for (int s = 0; s < num_parts; ++s) add += to_float<TD>(d[s * part_stride + i]);
+      v += add;
       if (!gathered) h[i] = v;
     }
     row_cache[i] = v;
@@ -92,63 +96,76 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
     o[i] = from_float<T>(row_cache[i] * inv * weight[i]);
 }
 
-int launch_add_rmsnorm(float* hidden, const void* delta, const float* weight, void* out,
+template <typename T, typename TD>
+static int launch_add_rmsnorm_typed(float* hidden, const void* delta, int num_parts, const float* weight, void* out,
+                                    const int32_t* rows, int64_t n, int64_t num_tokens, int64_t hidden_size,
+                                    float eps, int* status, cudaStream_t stream) {
+  const size_t smem = (size_t)hidden_size * sizeof(float);
+  int threads = 32;
+  while (threads < 512 && threads * 4 < hidden_size) threads *= 2;
+  auto kernel = add_rmsnorm_kernel<T, TD>;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+  }
+  kernel<<<(unsigned)n, threads, smem, stream>>>(hidden, (const TD*)delta, num_parts, weight, (T*)out, rows,
+                                                 num_tokens, hidden_size, eps, status);
+  return (int)cudaGetLastError();
+}
+
+int launch_add_rmsnorm(float* hidden, const void* delta, int delta_parts, const float* weight, void* out,
                        const int32_t* rows, int64_t num_rows, int64_t num_tokens, int64_t hidden_size,
                        float eps, int dtype, int* status, cudaStream_t stream) {
   const int64_t n = rows ? num_rows : num_tokens;
   if (n == 0) return 0;
-  const size_t smem = (size_t)hidden_size * sizeof(float);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;  // bindings.cpp refuses this size first
-  int threads = 32;
-  while (threads < 512 && threads * 4 < hidden_size) threads *= 2;
-  cudaError_t err;
+  if ((size_t)hidden_size * sizeof(float) > 200 * 1024) return (int)cudaErrorInvalidValue;  // refused by the caller first
   if (dtype == kBFloat16) {
-    auto kernel = add_rmsnorm_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) {
-      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (err != cudaSuccess) return (int)err;
-    }
-    kernel<<<(unsigned)n, threads, smem, stream>>>(hidden, (const __nv_bfloat16*)delta, weight,
-                                                   (__nv_bfloat16*)out, rows, num_tokens, hidden_size, eps,
-                                                   status);
-  } else {
-    auto kernel = add_rmsnorm_kernel<float>;
-    if (smem > 48 * 1024) {
-      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (err != cudaSuccess) return (int)err;
-    }
-    kernel<<<(unsigned)n, threads, smem, stream>>>(hidden, (const float*)delta, weight, (float*)out, rows,
-                                                   num_tokens, hidden_size, eps, status);
+    if (delta_parts > 0)
+      return launch_add_rmsnorm_typed<__nv_bfloat16, float>(hidden, delta, delta_parts, weight, out, rows, n,
+                                                            num_tokens, hidden_size, eps, status, stream);
+    return launch_add_rmsnorm_typed<__nv_bfloat16, __nv_bfloat16>(hidden, delta, 1, weight, out, rows, n, num_tokens,
+                                                                  hidden_size, eps, status, stream);
   }
-  return (int)cudaGetLastError();
+  return launch_add_rmsnorm_typed<float, float>(hidden, delta, delta_parts > 0 ? delta_parts : 1, weight, out, rows,
+                                                n, num_tokens, hidden_size, eps, status, stream);
 }
 
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t inter,
+template <typename T, typename TI>
+__global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int num_parts, T* __restrict__ out, int64_t inter,
                                 int64_t total) {
   const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t token = idx / inter, i = idx - token * inter;
-  const T* row = gate_up + token * 2 * inter;
-  const float g = to_float<T>(row[i]);
-  const float u = to_float<T>(row[inter + i]);
+  const int64_t part_stride = (total / inter) * 2 * inter;
+  const TI* row = gate_up + token * 2 * inter;
+  float g = 0.f, u = 0.f;
+  for (int s = 0; s < num_parts; ++s) {
+    g += to_float<TI>(row[s * part_stride + i]);
+    u += to_float<TI>(row[s * part_stride + inter + i]);
+  }
   // silu(g) = g * sigmoid(g), in float (ampere_kv/runner.py:176)
   out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
-int launch_silu_mul(const void* gate_up, void* out, int64_t num_tokens, int64_t inter, int dtype,
+int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_tokens, int64_t inter, int dtype,
                     cudaStream_t stream) {
   const int64_t total = num_tokens * inter;
   if (total == 0) return 0;
   const int threads = 256;
   const int64_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-  if (dtype == kBFloat16)
-    silu_mul_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
-  else
-    silu_mul_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out,
-                                                                    inter, total);
+  if (dtype == kBFloat16) {
+    if (parts > 0)
+      silu_mul_kernel<__nv_bfloat16, float><<<(unsigned)blocks, threads, 0, stream>>>(
+          (const float*)gate_up, parts, (__nv_bfloat16*)out, inter, total);
+    else
+      silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
+          (const __nv_bfloat16*)gate_up, 1, (__nv_bfloat16*)out, inter, total);
+  } else {
+    silu_mul_kernel<float, float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up,
+                                                                            parts > 0 ? parts : 1, (float*)out,
+                                                                            inter, total);
+  }
   return (int)cudaGetLastError();
 }
 

@@ -1,0 +1,387 @@
+// Weight-streaming bfloat16 GEMM for few tokens (decode steps), on the 5th-generation tensor cores:
+//     out[t, f] = sum_k x[t, k] * w[f, k]
+// The weight matrix [features, K] is the M operand (128 features per CTA), the tokens are the N operand
+// (padded to 16/32/64), so every byte of weight is read exactly once by one CTA and feeds a full-width
+// tcgen05.mma.  K is cut into 1/2/4/8 splits so that a thin output still occupies the whole GPU.  The CTAs of
+// one output tile form a thread-block cluster: each leaves its float32 partial tile in its own shared memory,
+// and after a cluster barrier every CTA adds up, in split order, a share of the tile read from its peers'
+// shared memory (distributed shared memory) and stores it, rounded once.  With ``parts`` instead of ``out``
+// the float32 partial tiles are stored as they are, [splits, tokens, features].
+//
+// One CTA = 6 warps: warp 0 issues the TMA loads (128-byte swizzled tiles of 64 K-elements, a 4-stage ring
+// guarded by full/empty mbarriers, no multicast), warp 1 allocates TMEM and issues tcgen05.mma (one thread,
+// accumulator in TMEM, tcgen05.commit frees each stage and finally signals the epilogue), warps 2-5 read the
+// accumulator with tcgen05.ld.  Two or three CTAs share an SM, so one CTA's set-up and epilogue overlap the
+// others' streaming.  It replaces the library GEMMs the reference calls for its
+// projections (ampere_kv/runner.py:64-66, 165, 174-177, 297) when the batch is small; large batches (prompts)
+// stay on the library GEMM.
+//
+// Every wait is bounded; a wait that runs out sets kWaitTimeout in the status word, and the CTA still frees
+// its TMEM and leaves.
+#include "common.cuh"
+#include "launchers.h"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace akv {
+
+namespace {
+
+constexpr int kTileM = 128;      // features per CTA
+constexpr int kTileK = 64;       // K elements per stage: 128 bytes, one swizzle row
+constexpr int kStages = 4;
+constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// start address, leading offset 1 (unused with this swizzle), 1024 bytes between 8-row groups, version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  desc |= (uint64_t)1 << 16;
+  desc |= (uint64_t)(1024 >> 4) << 32;
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)2 << 61;
+  return desc;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmParams {
+  float* parts;        // [splits, tokens, features] float32 partial tiles, or null
+  void* out;           // [tokens, features] in OutT (cluster reduction), or null
+  int tokens, features, k;
+  int kb_total;        // K blocks of 64 in all
+  int splits;
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kA = kTileM * kTileK * 2;
+  static constexpr int kB = BN * kTileK * 2;
+  static constexpr int kStage = kA + kB;
+  static constexpr int kReduce = BN * kTileM * 4;                      // float32 partial tile, reuses the stages
+  static_assert(kReduce <= kStages * kStage, "the partial tile must fit in the stage ring");
+  static constexpr int kBytes = kStages * kStage + (2 * kStages + 1) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Float at `local_addr` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(192)
+small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+                    GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * GemmSmem<BN>::kStage);
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_ready = empty + kStages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+  // this split's K blocks: an even share, the first (kb_total % splits) splits take one more
+  const int base = p.kb_total / p.splits, extra = p.kb_total % p.splits;
+  const int kb_begin = split * base + min(split, extra);
+  const int num_kb = base + (split < extra ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        if (kb >= kStages && !mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+          ok = false;
+          break;
+        }
+        uint8_t* stage = smem + s * GemmSmem<BN>::kStage;
+        mbar_expect_tx(&full[s], GemmSmem<BN>::kStage);
+        const int k0 = (kb_begin + kb) * kTileK;
+        tma_load_2d(stage, &w_map, k0, tile * kTileM, &full[s]);
+        tma_load_2d(stage + GemmSmem<BN>::kA, &x_map, k0, 0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        if (!mbar_wait(&full[s], (kb / kStages) & 1)) {
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + s * GemmSmem<BN>::kStage);
+        const uint32_t b_addr = a_addr + GemmSmem<BN>::kA;
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k) {
+          // 16 K-elements = 32 bytes further along the swizzled row
+          umma_bf16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);     // arrives once these MMAs have read the stage
+      }
+      if (ok) umma_commit(acc_ready);
+    }
+  } else {
+    // epilogue: warp (2..5) reads the TMEM lanes of its quarter; lane = feature, column = token
+    const int quarter = warp & 3;
+    if (!mbar_wait(acc_ready, 0)) ok = false;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = quarter * 32 + lane;
+    const int feature = tile * kTileM + row;
+    float* reduce = reinterpret_cast<float*>(smem);     // [token][128 features]; the stages are drained by now
+    float* part_out = p.parts ? p.parts + (int64_t)split * p.tokens * p.features : nullptr;
+#pragma unroll
+    for (int c = 0; c < BN / 16; ++c) {
+      uint32_t v[16];
+      if (ok) {
+        tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, v);
+      } else {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) v[t] = 0u;
+      }
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const int token = c * 16 + t;
+        if (part_out) {
+          if (token < p.tokens && feature < p.features)
+            part_out[(int64_t)token * p.features + feature] = __uint_as_float(v[t]);
+        } else {
+          reduce[token * kTileM + row] = __uint_as_float(v[t]);
+        }
+      }
+    }
+  }
+  if (!ok) set_status(p.status, kWaitTimeout);
+  if (p.out != nullptr) {
+    // every CTA of the tile has its partial in shared memory: add them up across the cluster, in split order
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int row = (warp & 3) * 32 + lane;
+      const int feature = tile * kTileM + row;
+      OutT* out = reinterpret_cast<OutT*>(p.out);
+      if (feature < p.features) {
+        for (int token = split; token < p.tokens; token += p.splits) {
+          const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
+          float sum = 0.f;
+          for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+          out[(int64_t)token * p.features + feature] = from_float<OutT>(sum);
+        }
+      }
+    }
+    cluster_sync_all();      // nobody leaves while a peer may still read its shared memory
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Map over a row-major bfloat16 matrix [rows, cols]: boxes of 64 columns by `box_rows` rows, 128-byte swizzle,
+// zeros outside the matrix.
+bool matrix_map(const void* base, int64_t rows, int64_t cols, int box_rows, CUtensorMap* out) {
+  static std::mutex mutex;
+  static std::map<std::tuple<const void*, int64_t, int64_t, int>, CUtensorMap> cache;
+  std::lock_guard<std::mutex> guard(mutex);
+  const auto key = std::make_tuple(base, rows, cols, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult res = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return false;
+  if (cache.size() > 8192) cache.clear();
+  cache[key] = map;
+  *out = map;
+  return true;
+}
+
+template <int BN, typename OutT>
+int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = small_m_gemm_kernel<BN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kBytes);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)((p.features + kTileM - 1) / kTileM), (unsigned)p.splits);
+  config.blockDim = dim3(192);
+  config.dynamicSmemBytes = GemmSmem<BN>::kBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = p.out != nullptr ? (unsigned)p.splits : 1u;   // the splits of a tile form the cluster
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, w_map, x_map, p);
+}
+
+template <typename OutT>
+int launch_out(int bn, const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
+  if (bn == 16) return launch_bn<16, OutT>(w_map, x_map, p, stream);
+  if (bn == 32) return launch_bn<32, OutT>(w_map, x_map, p, stream);
+  return launch_bn<64, OutT>(w_map, x_map, p, stream);
+}
+
+}  // namespace
+
+bool small_m_gemm_supported(int64_t tokens, int64_t features, int64_t k) {
+  return tokens >= 1 && tokens <= 64 && k >= 64 && k % 8 == 0 && features >= 1 && encode_fn() != nullptr &&
+         (features + kTileM - 1) / kTileM <= 0x7fffffffLL;
+}
+
+// 1, 2, 4 or 8 splits of K: enough CTAs for about two per SM, at least four K blocks each.
+int small_m_gemm_splits(int64_t features, int64_t k) {
+  const int64_t tiles = (features + kTileM - 1) / kTileM;
+  const int64_t kb_total = (k + kTileK - 1) / kTileK;
+  int splits = 1;
+  while (splits < 8 && tiles * splits < 2 * 148 && kb_total / (splits * 2) >= 4) splits *= 2;
+  return splits;
+}
+
+// out_dtype: akv::DType of `out` when the split partials are reduced inside the kernel; parts (float32
+// [splits, tokens, features]) is written instead when `out` is null.
+int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
+                        int64_t features, int64_t k, int splits, int* status, cudaStream_t stream) {
+  if (!small_m_gemm_supported(tokens, features, k) || splits < 1) return (int)cudaErrorInvalidValue;
+  if ((out == nullptr) == (parts == nullptr)) return (int)cudaErrorInvalidValue;
+  const int bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+  const int kb_total = (int)((k + kTileK - 1) / kTileK);
+  if (splits > kb_total) return (int)cudaErrorInvalidValue;
+  if (out != nullptr && splits != 1 && splits != 2 && splits != 4 && splits != 8) return (int)cudaErrorInvalidValue;
+  CUtensorMap w_map, x_map;
+  if (!matrix_map(w, features, k, kTileM, &w_map) || !matrix_map(x, tokens, k, bn, &x_map))
+    return (int)cudaErrorInvalidValue;
+  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status};
+  if (out != nullptr && out_dtype == kBFloat16) return launch_out<__nv_bfloat16>(bn, w_map, x_map, p, stream);
+  return launch_out<float>(bn, w_map, x_map, p, stream);
+}
+
+}  // namespace akv

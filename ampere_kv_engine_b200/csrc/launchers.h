@@ -20,16 +20,27 @@ int launch_embedding(const int32_t* ids, const void* table, float* hidden, int64
 
 // hidden += delta (if delta); out = rmsnorm(hidden) * weight.  With `rows` (num_rows entries)
 // only those rows are read, hidden is left untouched and out is [num_rows, hidden_size].
-int launch_add_rmsnorm(float* hidden, const void* delta, const float* weight, void* out,
+// delta_parts > 0: delta is float32 [delta_parts, tokens, hidden], partial sums that are added up.
+int launch_add_rmsnorm(float* hidden, const void* delta, int delta_parts, const float* weight, void* out,
                        const int32_t* rows, int64_t num_rows, int64_t num_tokens, int64_t hidden_size,
                        float eps, int dtype, int* status, cudaStream_t stream);
 
-// out[n, i] = silu(gate_up[n, i]) * gate_up[n, inter + i]
-int launch_silu_mul(const void* gate_up, void* out, int64_t num_tokens, int64_t inter, int dtype,
+// out[n, i] = silu(gate_up[n, i]) * gate_up[n, inter + i]; parts > 0: gate_up is float32 [parts, tokens, 2 inter]
+// partial sums.
+int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_tokens, int64_t inter, int dtype,
                     cudaStream_t stream);
 
+// Split-K weight-streaming product for few tokens (gemm_tc.cu), x [tokens, k] and w [features, k] bfloat16.
+// Either out [tokens, features] (out_dtype: float32 or bfloat16; the splits are added up inside the kernel,
+// splits in {1, 2, 4, 8}) or parts [splits, tokens, features] float32 (each split's sum as it is).
+bool small_m_gemm_supported(int64_t tokens, int64_t features, int64_t k);
+int small_m_gemm_splits(int64_t features, int64_t k);
+int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
+                        int64_t features, int64_t k, int splits, int* status, cudaStream_t stream);
+
 struct QkRopeWriteParams {
-  const void* qkv;          // [N, (NH + 2 NKV) * D]
+  const void* qkv;          // [N, (NH + 2 NKV) * D]; with qkv_parts > 0: float32 [qkv_parts, N, ...] partial sums
+  int qkv_parts;
   const int32_t* positions; // [N]
   const int32_t* slots;     // [N] page * page_size + offset, or -1: do not write; may be null
   const float* q_weight;    // [D] or null: no norm

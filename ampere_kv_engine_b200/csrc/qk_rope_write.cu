@@ -16,7 +16,7 @@ namespace akv {
 
 constexpr int kMaxPairsPerLane = 8;  // head_dim <= 512
 
-template <typename T>
+template <typename T, typename TI>
 __global__ void qk_norm_rope_write_kernel(QkRopeWriteParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_heads = p.num_heads + 2 * p.num_kv_heads;
@@ -24,7 +24,9 @@ __global__ void qk_norm_rope_write_kernel(QkRopeWriteParams p) {
   const int64_t token = blockIdx.y + (int64_t)blockIdx.z * 65535;
   if (head >= total_heads || token >= p.num_tokens) return;
   const int D = p.head_dim, half = D / 2;
-  const T* src = (const T*)p.qkv + (token * total_heads + head) * (int64_t)D;
+  const TI* src = (const TI*)p.qkv + (token * total_heads + head) * (int64_t)D;
+  const int parts = p.qkv_parts > 0 ? p.qkv_parts : 1;
+  const int64_t part_stride = p.num_tokens * (int64_t)total_heads * D;
 
   // which kind of head, and where its results go
   const bool is_q = head < p.num_heads;
@@ -55,8 +57,13 @@ __global__ void qk_norm_rope_write_kernel(QkRopeWriteParams p) {
   for (int c = 0; c < kMaxPairsPerLane; ++c) {
     const int j = c * 32 + lane;
     if (j < half) {
-      lo[c] = to_float<T>(src[j]);
-      hi[c] = to_float<T>(src[j + half]);
+      float a = 0.f, b = 0.f;
+      for (int s = 0; s < parts; ++s) {      // float32 partial sums of a split-K product are added here
+        a += to_float<TI>(src[s * part_stride + j]);
+        b += to_float<TI>(src[s * part_stride + j + half]);
+      }
+      lo[c] = a;
+      hi[c] = b;
       ss += lo[c] * lo[c] + hi[c] * hi[c];
     } else {
       lo[c] = hi[c] = 0.f;
@@ -142,10 +149,14 @@ int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
   if (nz > 65535) return (int)cudaErrorInvalidValue;
   dim3 grid((unsigned)((total_heads + warps - 1) / warps), (unsigned)ny, (unsigned)nz);
   const size_t smem = (p.rotary_dim != p.head_dim && p.inv_freq) ? (size_t)warps * p.head_dim * sizeof(float) : 0;
-  if (p.dtype == kBFloat16)
-    qk_norm_rope_write_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(p);
-  else
-    qk_norm_rope_write_kernel<float><<<grid, warps * 32, smem, stream>>>(p);
+  if (p.dtype == kBFloat16) {
+    if (p.qkv_parts > 0)
+      qk_norm_rope_write_kernel<__nv_bfloat16, float><<<grid, warps * 32, smem, stream>>>(p);
+    else
+      qk_norm_rope_write_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, warps * 32, smem, stream>>>(p);
+  } else {
+    qk_norm_rope_write_kernel<float, float><<<grid, warps * 32, smem, stream>>>(p);
+  }
   return (int)cudaGetLastError();
 }
 

@@ -62,8 +62,14 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     return out
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    out = torch.empty((gate_up.shape[0], gate_up.shape[1] // 2), dtype=gate_up.dtype, device=gate_up.device)
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``silu(gate) * up`` of [tokens, 2 * intermediate] (gate columns first).  A 3-D float32 input is a stack of
+    split-K partial sums that are added up first; then ``out_dtype`` names the result's type."""
+    if gate_up.dim() == 3:
+        out_dtype = out_dtype or torch.bfloat16
+    else:
+        out_dtype = gate_up.dtype
+    out = torch.empty((gate_up.shape[-2], gate_up.shape[-1] // 2), dtype=out_dtype, device=gate_up.device)
     ext().silu_mul(gate_up, out)
     _launched()
     return out
@@ -75,11 +81,12 @@ def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_ca
 
     Returns q [tokens, heads * head_dim] (and the dense k, v when ``want_kv``).
     """
-    n = qkv.shape[0]
-    q_out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    n = qkv.shape[-2]
+    out_dtype = torch.bfloat16 if qkv.dim() == 3 else qkv.dtype      # 3-D: float32 split-K partial sums
+    q_out = torch.empty((n, num_heads * head_dim), dtype=out_dtype, device=qkv.device)
     k_out = v_out = None
     if want_kv:
-        k_out = torch.empty((n, num_kv_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        k_out = torch.empty((n, num_kv_heads * head_dim), dtype=out_dtype, device=qkv.device)
         v_out = torch.empty_like(k_out)
     ext().qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, q_out, k_out, v_out, k_cache,
                              v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), status)
@@ -92,14 +99,27 @@ def kv_write(k, v, slots, k_cache, v_cache, status=None) -> None:
     _launched()
 
 
+def attention_takes_tensor_cores(dtype: torch.dtype, head_dim: int, group_size: int, page_size: int) -> bool:
+    """Whether the TMA + tensor-core attention kernels take these sizes (else the general kernel runs)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group_size <= 16 and page_size >= 8
+            and page_size & (page_size - 1) == 0)
+
+
 def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
-                  target_warps: int = 148 * 16) -> int:
-    """How many key ranges each query tile is cut into so that a small batch still fills the GPU."""
-    items = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8))
-    if items >= target_warps or max_context <= 128:
+                  tensor_core: bool = False) -> int:
+    """How many key ranges each decoded token's attention is cut into so that a small batch still fills the GPU.
+
+    The tensor-core decode kernel runs one single-warp CTA per (token, kv head, split), three to an SM; the
+    general kernel one warp per (token, kv head, 8 rows, split), sixteen to an SM.
+    """
+    if tensor_core:
+        items, target, min_keys = max(1, num_tiles * num_kv_heads), 148 * 3, 128
+    else:
+        items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), 148 * 16, 128
+    if items >= target or max_context <= min_keys:
         return 1
-    want = (target_warps + items - 1) // items
-    return int(max(1, min(want, (max_context + 127) // 128, 64)))
+    want = target // items
+    return int(max(1, min(want, (max_context + min_keys - 1) // min_keys, 64)))
 
 
 def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
@@ -127,13 +147,57 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     return tokens
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-           out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)`` by the library GEMM, float32 accumulation.
+#: products of at most this many bfloat16 tokens go through the package's own tcgen05 kernel
+SMALL_M_LIMIT = 64
+use_small_m_gemm = True
+#: hand split-K partial sums to the consuming kernel instead of adding them up inside the product kernel
+prefer_partials = False
 
-    ``out_dtype=torch.float32`` with bfloat16 operands keeps the accumulator's precision in
-    the result (used for the logits).
+
+def small_m_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                 splits: int | None = None, parts: bool = False, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T`` for 1..64 bfloat16 tokens on the tcgen05 tensor cores, K cut into ``splits`` ranges.
+
+    Default: [tokens, features] in ``out_dtype`` (float32 or bfloat16); the splits (1, 2, 4 or 8 CTAs of a
+    cluster) add their float32 partial tiles up through distributed shared memory.  ``parts=True``: the float32
+    partial sums themselves, [splits, tokens, features], for a consumer kernel that adds them up.
     """
+    kb_total = (weight.shape[1] + 63) // 64
+    if splits is None:
+        splits = ext().small_m_gemm_splits(weight.shape[0], weight.shape[1])
+    splits = max(1, min(int(splits), kb_total))
+    if parts:
+        out = torch.empty((splits, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+    else:
+        while splits not in (1, 2, 4, 8):
+            splits -= 1
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+    ext().small_m_gemm(x, weight, out, splits, status)
+    _launched()
+    return out
+
+
+def _takes_small_m(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (use_small_m_gemm and x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and x.dim() == 2 and x.shape[0] <= SMALL_M_LIMIT and x.is_contiguous() and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and ext().small_m_gemm_supported(x.shape[0], weight.shape[0], weight.shape[1]))
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           out_dtype: torch.dtype | None = None, partial_ok: bool = False,
+           status: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``, float32 accumulation.
+
+    Few bfloat16 tokens (decode steps) go through this package's tcgen05 kernel; everything else is the library
+    GEMM, as in the reference.  With ``partial_ok`` the result may be a 3-D float32 stack
+    ``[parts, tokens, features]`` of split-K partial sums, for a consumer kernel that adds them up;
+    ``out_dtype=torch.float32`` keeps the accumulator's precision in the result (used for the logits).
+    """
+    if bias is None and _takes_small_m(x, weight):
+        if partial_ok and prefer_partials:
+            return small_m_gemm(x, weight, parts=True, status=status)
+        return small_m_gemm(x, weight, out_dtype=out_dtype or x.dtype, status=status)
     if out_dtype is not None and out_dtype != x.dtype:
         out = torch.mm(x, weight.t(), out_dtype=out_dtype)
         if bias is not None:

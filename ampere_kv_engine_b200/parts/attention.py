@@ -83,7 +83,7 @@ class PagedAttention(Mixer):
 
     def forward(self, x, ctx, cache):
         group = ctx.groups[cache.group]
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv, partial_ok=True, status=ctx.status)
         slots = group.slot_mapping if cache.writes else None
         k_cache = cache.k_cache if cache.writes else None
         v_cache = cache.v_cache if cache.writes else None
@@ -105,11 +105,12 @@ class PagedAttention(Mixer):
                 ops.kv_write(k.contiguous(), v, group.slot_mapping, cache.k_cache, cache.v_cache, status=ctx.status)
             q = q.contiguous()
         group_size = self.num_heads // self.num_kv_heads
-        splits = ops.choose_splits(ctx.num_tiles, self.num_kv_heads, ctx.q_tile * group_size,
-                                   ctx.max_context)
+        tensor_core = ops.attention_takes_tensor_cores(self.dtype, self.head_dim, group_size, cache.page_size)
+        splits = 1 if ctx.q_tile > 1 and tensor_core else ops.choose_splits(
+            ctx.num_tiles, self.num_kv_heads, ctx.q_tile * group_size, ctx.max_context, tensor_core)
         out = ops.paged_attention(
             q, cache.k_cache, cache.v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq, ctx.tile_q0,
             ctx.tile_nq, num_tiles=ctx.num_tiles, q_tile=ctx.q_tile, num_splits=splits,
             num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, window=self.window or 0, scale=self.scale,
             status=ctx.status)
-        return ops.linear(out, self.w_o, self.b_o)
+        return ops.linear(out, self.w_o, self.b_o, partial_ok=True, status=ctx.status)

@@ -82,7 +82,9 @@ class Norm(Part):
                 ) -> torch.Tensor:
         """Add ``delta`` into the float32 residual stream ``hidden`` (in place) and return the
         normalised activations in the compute dtype.  With ``rows`` only those rows are
-        normalised and ``hidden`` is not changed."""
+        normalised and ``hidden`` is not changed.  ``delta`` is a branch output [tokens, hidden]
+        in the compute dtype, or a 3-D float32 stack [parts, tokens, hidden] of partial sums
+        (a split-K product) that are to be added together."""
         raise NotImplementedError
 
 

@@ -42,5 +42,6 @@ class GatedMLP(FeedForward):
         self.down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x, ctx):
-        gate_up = ops.linear(x, self.gate_up)
-        return ops.linear(ops.silu_mul(gate_up), self.down)
+        status = getattr(ctx, "status", None)
+        gate_up = ops.linear(x, self.gate_up, partial_ok=True, status=status)
+        return ops.linear(ops.silu_mul(gate_up, self.dtype), self.down, partial_ok=True, status=status)

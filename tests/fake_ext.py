@@ -22,6 +22,8 @@ class FakeExt:
         hidden.copy_(table[ids.long()].float())
 
     def add_rmsnorm(self, hidden, delta, weight, out, rows, eps, status=None):
+        if delta is not None and delta.dim() == 3:
+            delta = delta.sum(0)
         if rows is None:
             if delta is not None:
                 hidden += delta.float()
@@ -34,12 +36,16 @@ class FakeExt:
         out.copy_((x * inv * weight).to(out.dtype))
 
     def silu_mul(self, gate_up, out):
+        if gate_up.dim() == 3:
+            gate_up = gate_up.sum(0)
         inter = gate_up.shape[1] // 2
         g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
         out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
     def qk_norm_rope_write(self, qkv, positions, slots, q_weight, k_weight, inv_freq, q_out, k_out, v_out, k_cache,
                            v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, eps, status=None):
+        if qkv.dim() == 3:
+            qkv = qkv.sum(0)
         n = qkv.shape[0]
         x = qkv.float().view(n, num_heads + 2 * num_kv_heads, head_dim)
         q, k, v = x[:, :num_heads], x[:, num_heads:num_heads + num_kv_heads], x[:, num_heads + num_kv_heads:]

@@ -367,3 +367,59 @@ def test_sample_distribution(ops):
     tokens = ops.sample(dev(logits.expand(n, 5).contiguous()), dev(torch.full((n,), 0.7)), dev(us)).cpu()
     freq = torch.bincount(tokens.long(), minlength=5).float() / n
     torch.testing.assert_close(freq, torch.softmax(logits[0] / 0.7, -1), atol=2e-3, rtol=0)
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 17, 64])
+@pytest.mark.parametrize("features,k", [(128, 64), (200, 200), (6144, 4096), (4096, 12288), (1000, 4096)])
+def test_small_m_gemm_on_tcgen05(ops, tokens, features, k):
+    """The weight-streaming tcgen05 kernel: partial sums of every split add up to x @ w^T (float32 reference on the
+    same bfloat16 values), for token counts that pad to 16/32/64, feature counts that are no multiple of the
+    128-row tile and K that is no multiple of the 64-element stage."""
+    g = torch.Generator().manual_seed(tokens * 1000 + features)
+    x = torch.randn(tokens, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(features, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    want = x.float() @ w.float().t()
+    status = status_word()
+    for splits in (None, 1, 3):
+        parts = ops.small_m_gemm(dev(x), dev(w), splits=splits, parts=True, status=status)
+        assert parts.dtype == torch.float32 and parts.shape[1:] == (tokens, features)
+        torch.testing.assert_close(parts.sum(0).cpu(), want, atol=2e-3, rtol=2e-3)
+    # the splits of a tile as a cluster: partial tiles added up through distributed shared memory
+    for splits in (None, 1, 2, 4, 8):
+        if splits is not None and splits > (k + 63) // 64:
+            continue
+        out = ops.small_m_gemm(dev(x), dev(w), out_dtype=torch.float32, splits=splits, status=status)
+        torch.testing.assert_close(out.cpu(), want, atol=2e-3, rtol=2e-3)
+    out = ops.small_m_gemm(dev(x), dev(w), out_dtype=torch.bfloat16, status=status)
+    torch.testing.assert_close(out.float().cpu(), want, atol=3e-2, rtol=3e-2)
+    assert int(status.item()) == 0
+    # the public product goes through the same kernel; with a bias it is the library's
+    torch.testing.assert_close(ops.linear(dev(x), dev(w), out_dtype=torch.float32).cpu(), want, atol=2e-3, rtol=2e-3)
+    torch.testing.assert_close(ops.linear(dev(x), dev(w)).float().cpu(), want, atol=3e-2, rtol=3e-2)
+    bias = torch.randn(features, generator=g).to(torch.bfloat16)
+    torch.testing.assert_close(ops.linear(dev(x), dev(w), dev(bias)).float().cpu(), want + bias.float(), atol=3e-2,
+                               rtol=3e-2)
+
+
+def test_consumers_add_up_partial_sums(ops):
+    """Norm, q/k-norm and SiLU-mul take a 3-D float32 stack of split-K partial sums and add it up themselves."""
+    g = torch.Generator().manual_seed(77)
+    parts = torch.randn(3, 5, 256, generator=g)
+    total = parts.sum(0)
+    h = torch.randn(5, 256, generator=g)
+    w = 1 + 0.1 * torch.randn(256, generator=g)
+    h_dev = dev(h.clone())
+    out = ops.add_rmsnorm(h_dev, dev(parts), dev(w), 1e-6, torch.bfloat16)
+    torch.testing.assert_close(h_dev.cpu(), h + total, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(out.float().cpu(), plain.rms_norm(h + total, w, 1e-6), **tol(torch.bfloat16))
+    out = ops.silu_mul(dev(parts), torch.bfloat16)
+    want = torch.nn.functional.silu(total[:, :128]) * total[:, 128:]
+    torch.testing.assert_close(out.float().cpu(), want, **tol(torch.bfloat16))
+    nh, nkv, d = 2, 1, 64
+    positions = torch.arange(5, dtype=torch.int32)
+    inv = plain.rope_inverse_frequencies(d, 10000.0)
+    qw, kw = torch.ones(d), torch.ones(d)
+    q = ops.qk_norm_rope_write(dev(parts), dev(positions), None, dev(qw), dev(kw), dev(inv), None, None, num_heads=nh,
+                               num_kv_heads=nkv, head_dim=d, rotary_dim=d, eps=1e-6)
+    q_ref, _, _ = _qkv_reference(total, positions, qw, kw, nh, nkv, d, 1e-6, 10000.0)
+    torch.testing.assert_close(q.float().cpu().view(5, nh, d), q_ref, **tol(torch.bfloat16))
