@@ -200,20 +200,42 @@ __device__ __forceinline__ void process_block(const uint32_t (&q_frag)[D / 16][4
   }
 }
 
-// Shared-memory layout: [stage][K area | V area], each area KT * D * 2 bytes, then the mbarriers.
+// Shared-memory layout: [stage][K area | V area], each area KT * D * 2 bytes, then the mbarriers.  The first
+// bytes of the stage ring are reused for the cross-split merge once the key loop is over.
 template <int D, int KT, int STAGES>
 struct Smem {
   static constexpr int kArea = KT * D * 2;
   static constexpr int kStage = 2 * kArea;
-  static constexpr int kBytes = STAGES * kStage + STAGES * 8 + 1024;   // + alignment slack
+  static constexpr int kMerge = 16 * (D + 2) * 4;                      // 16 rows of (acc[D], max, sum) float32
+  static_assert(kMerge <= STAGES * kStage, "the merge buffer must fit in the stage ring");
+  static constexpr int kBytes = STAGES * kStage + 2 * STAGES * 8 + 1024;   // + alignment slack
 };
 
-// Issue the TMA loads of key block `block` (keys [lo + block*KT, ...)) into `stage`.  One thread calls this.
+// The producer warp's view of the block table: each lane holds one entry of the current run of 32 logical
+// pages, so a dependent global load is paid once per 32 pages, not once per key block.
+struct TableWindow {
+  const int32_t* table;
+  int width;
+  int first;      // logical page of lane 0's entry, -1 before the first load
+  int entry;
+  __device__ __forceinline__ int page(int logical, int lane) {
+    const int base = logical & ~31;
+    if (base != first) {
+      first = base;
+      const int mine = base + lane;
+      entry = mine < width ? table[mine] : -1;
+    }
+    return __shfl_sync(0xffffffffu, entry, logical & 31);
+  }
+};
+
+// Issue the TMA loads of the key block starting at key0 into `stage`.  Called by the whole producer warp.
 template <int D, int KT>
 __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMap* k_map, const CUtensorMap* v_map,
-                                            const int32_t* table, int kvh, int key0, int key_end, uint8_t* stage,
+                                            TableWindow& window, int kvh, int key0, int key_end, uint8_t* stage,
                                             uint64_t* bar) {
   const PagedAttentionParams& p = tp.p;
+  const int lane = threadIdx.x & 31;
   const int P = p.page_size, rows = tp.box_rows;
   const int boxes = KT / rows;
   uint32_t bytes = 0;
@@ -224,10 +246,9 @@ __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMa
     if (b < boxes) {
       const int key = key0 + b * rows;
       if (key < key_end) {
-        const int logical = key / P;
-        int page = logical < p.table_width ? table[logical] : -1;
+        int page = window.page(key / P, lane);
         if (page < 0 || page >= p.num_pages) {
-          set_status(p.status, kBadPage);
+          if (lane == 0) set_status(p.status, kBadPage);
           page = -1;
         }
         page_of[b] = page;
@@ -235,16 +256,18 @@ __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMa
       }
     }
   }
-  mbar_expect_tx(bar, bytes);
+  if (lane == 0) {
+    mbar_expect_tx(bar, bytes);
 #pragma unroll
-  for (int b = 0; b < KT / 8; ++b) {
-    if (b < boxes && page_of[b] >= 0) {
-      const int key = key0 + b * rows;
-      const int y = (page_of[b] * p.num_kv_heads + kvh) * P + key % P;
+    for (int b = 0; b < KT / 8; ++b) {
+      if (b < boxes && page_of[b] >= 0) {
+        const int key = key0 + b * rows;
+        const int y = (page_of[b] * p.num_kv_heads + kvh) * P + key % P;
 #pragma unroll
-      for (int h = 0; h < D / 64; ++h) {
-        tma_load_2d(stage + h * KT * 128 + b * rows * 128, k_map, h * 64, y, bar);
-        tma_load_2d(stage + KT * D * 2 + h * KT * 128 + b * rows * 128, v_map, h * 64, y, bar);
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_2d(stage + h * KT * 128 + b * rows * 128, k_map, h * 64, y, bar);
+          tma_load_2d(stage + KT * D * 2 + h * KT * 128 + b * rows * 128, v_map, h * 64, y, bar);
+        }
       }
     }
   }
@@ -264,42 +287,54 @@ __device__ __forceinline__ void zero_v_rows(uint8_t* stage, int first, int tid, 
   }
 }
 
-template <int D, int KT, int STAGES, bool DECODE>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync(int consumers) {
+  asm volatile("bar.sync 1, %0;" ::"r"(consumers * 32) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// Warps 0 .. consumers-1 compute (prompt kernel: warp g = q-head g of the group; decode kernel: one warp, its
+// rows are the group's heads); the last warp is the producer: it walks the block table and keeps the TMA ring
+// full.  full[s]: the stage's bytes have landed; empty[s]: every consumer warp is done with the stage.
+// CLUSTER (decode only): the key splits of one (token, kv head) form a cluster; the partial results are merged
+// through distributed shared memory instead of a second kernel.
+template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
 __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                                     const __grid_constant__ CUtensorMap v_map, TcParams tp) {
   const PagedAttentionParams& p = tp.p;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Smem<D, KT, STAGES>::kStage);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Smem<D, KT, STAGES>::kStage);
+  uint64_t* empty = full + STAGES;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int consumers = (int)(blockDim.x >> 5) - 1;
+  const bool is_producer = warp == consumers;
   const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
 
   const int seq = p.tile_seq[tile];
   const int q0 = p.tile_q0[tile];
   const int nq = p.tile_nq[tile];
+  // A tile of no rows (padding of a captured layout) does nothing; with clusters every CTA of the cluster sees
+  // the same tile, so they all leave together.
   if (nq <= 0) return;
   const int ctx = p.ctx_lens[seq];
   const int seq_q0 = p.cu_q[seq];
   const int q_len = p.cu_q[seq + 1] - seq_q0;
   const int tile_pos = ctx - q_len + (q0 - seq_q0);
 
-  // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
-  int row_pos[2];
-  int row_token[2], row_head[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = (lane >> 2) + 8 * r;
-    if (DECODE) {
-      row_token[r] = q0;
-      row_head[r] = kvh * G + row;
-      row_pos[r] = row < G ? tile_pos : -1;
-    } else {
-      row_token[r] = q0 + row;
-      row_head[r] = kvh * G + warp;
-      row_pos[r] = row < nq ? tile_pos + row : -1;
-    }
-  }
   const int pos_first = tile_pos, pos_last = DECODE ? tile_pos : tile_pos + nq - 1;
   int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
   lo = lo / tp.box_rows * tp.box_rows;     // boxes start on box boundaries inside a page
@@ -315,84 +350,145 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
 
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], consumers);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
-  const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
-  if (tid == 0) {
-    for (int b = 0; b < STAGES - 1 && b < num_blocks; ++b)
-      issue_block<D, KT>(tp, &k_map, &v_map, table, kvh, range_lo + b * KT, range_hi,
-                         smem + b * Smem<D, KT, STAGES>::kStage, &bars[b]);
-  }
-
-  // query fragments straight from global memory
-  uint32_t q_frag[D / 16][4];
-  {
-    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
-#pragma unroll
-    for (int t = 0; t < D / 16; ++t) {
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int col = t * 16 + (lane & 3) * 2;
-        uint32_t lo_pair = 0, hi_pair = 0;
-        if (row_pos[r] >= 0) {
-          const __nv_bfloat16* src = q + ((int64_t)row_token[r] * NH + row_head[r]) * D + col;
-          lo_pair = *reinterpret_cast<const uint32_t*>(src);
-          hi_pair = *reinterpret_cast<const uint32_t*>(src + 8);
-        }
-        q_frag[t][r] = lo_pair;
-        q_frag[t][2 + r] = hi_pair;
-      }
-    }
-  }
-
+  bool ok = true;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
   float o[D / 8][4];
-#pragma unroll
-  for (int v = 0; v < D / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
-  const float scale_log2 = p.scale * kLog2e;
+  int row_pos[2] = {-1, -1}, row_token[2] = {0, 0}, row_head[2] = {0, 0};
 
-  // A warp whose wait ran out keeps walking the loop (the block-wide barriers stay matched) but computes nothing.
-  bool ok = true;
-  for (int b = 0; b < num_blocks; ++b) {
-    const int stage_index = b % STAGES;
-    uint8_t* stage = smem + stage_index * Smem<D, KT, STAGES>::kStage;
-    // everyone is done with the stage that block b + STAGES - 1 will overwrite (it held block b - 1)
-    __syncthreads();
-    if (tid == 0 && b + STAGES - 1 < num_blocks) {
-      const int nb = b + STAGES - 1;
-      issue_block<D, KT>(tp, &k_map, &v_map, table, kvh, range_lo + nb * KT, range_hi,
-                         smem + (nb % STAGES) * Smem<D, KT, STAGES>::kStage, &bars[nb % STAGES]);
+  if (is_producer) {
+    TableWindow window{p.block_table + (int64_t)seq * p.table_width, p.table_width, -1, -1};
+    for (int b = 0; b < num_blocks; ++b) {
+      const int s = b % STAGES;
+      if (b >= STAGES && !mbar_wait(&empty[s], ((b / STAGES) - 1) & 1)) {
+        ok = false;
+        break;
+      }
+      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi,
+                         smem + s * Smem<D, KT, STAGES>::kStage, &full[s]);
     }
-    if (ok && !mbar_wait(&bars[stage_index], (b / STAGES) & 1)) ok = false;
-    const int key0 = range_lo + b * KT;
-    const int nvalid = min(KT, range_hi - key0);
-    if (nvalid < KT) {
-      // V rows past the end may hold anything (or were never loaded): make them zero before P.V reads them
-      zero_v_rows<D, KT>(stage, nvalid, tid, nthreads);
-      __syncthreads();
+  } else {
+    // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = (lane >> 2) + 8 * r;
+      if (DECODE) {
+        row_token[r] = q0;
+        row_head[r] = kvh * G + row;
+        row_pos[r] = row < G ? tile_pos : -1;
+      } else {
+        row_token[r] = q0 + row;
+        row_head[r] = kvh * G + warp;
+        row_pos[r] = row < nq ? tile_pos + row : -1;
+      }
     }
-    if (ok)
-      process_block<D, KT>(q_frag, smem_addr(stage), smem_addr(stage + KT * D * 2), key0, nvalid, row_pos, p.window,
-                           scale_log2, m, l, o);
-    if (nvalid < KT) {
-      // should a later TMA load reuse the zeroed rows (async proxy), the generic writes are ordered before it
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // query fragments straight from global memory
+    uint32_t q_frag[D / 16][4];
+    {
+      const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+#pragma unroll
+      for (int t = 0; t < D / 16; ++t) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int col = t * 16 + (lane & 3) * 2;
+          uint32_t lo_pair = 0, hi_pair = 0;
+          if (row_pos[r] >= 0) {
+            const __nv_bfloat16* src = q + ((int64_t)row_token[r] * NH + row_head[r]) * D + col;
+            lo_pair = *reinterpret_cast<const uint32_t*>(src);
+            hi_pair = *reinterpret_cast<const uint32_t*>(src + 8);
+          }
+          q_frag[t][r] = lo_pair;
+          q_frag[t][2 + r] = hi_pair;
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < D / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
+    const float scale_log2 = p.scale * kLog2e;
+
+    // A warp whose wait ran out keeps walking the loop (the consumers' barriers stay matched) but computes nothing.
+    for (int b = 0; b < num_blocks; ++b) {
+      const int s = b % STAGES;
+      uint8_t* stage = smem + s * Smem<D, KT, STAGES>::kStage;
+      if (ok && !mbar_wait(&full[s], (b / STAGES) & 1)) ok = false;
+      const int key0 = range_lo + b * KT;
+      const int nvalid = min(KT, range_hi - key0);
+      if (nvalid < KT) {
+        // V rows past the end may hold anything (or were never loaded): make them zero before P.V reads them.
+        // This only ever happens in a range's last block, so no later TMA load touches these rows.
+        zero_v_rows<D, KT>(stage, nvalid, tid, consumers * 32);
+        if (consumers > 1) consumer_sync(consumers); else __syncwarp();
+      }
+      if (ok)
+        process_block<D, KT>(q_frag, smem_addr(stage), smem_addr(stage + KT * D * 2), key0, nvalid, row_pos,
+                             p.window, scale_log2, m, l, o);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
   }
-  if (!ok) {
-    if (lane == 0) set_status(p.status, kWaitTimeout);
+  if (!ok && lane == 0) set_status(p.status, kWaitTimeout);
+
+  if (DECODE && CLUSTER) {
+    // every split leaves (acc, max, sum) of its rows in its own shared memory; after the cluster barrier the CTA
+    // of rank r merges rows r, r + splits, ... reading its peers' shared memory in split order
+    __syncthreads();                      // the stage ring is idle: all loads have landed and been consumed
+    float* merge = reinterpret_cast<float*>(smem);
+    if (!is_producer) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        if (row < G) {
+#pragma unroll
+          for (int v = 0; v < D / 8; ++v) {
+            const int col = v * 8 + (lane & 3) * 2;
+            merge[row * (D + 2) + col] = ok ? o[v][2 * r] : 0.f;
+            merge[row * (D + 2) + col + 1] = ok ? o[v][2 * r + 1] : 0.f;
+          }
+          if ((lane & 3) == 0) {
+            merge[row * (D + 2) + D] = m[r];            // log2 units, the same in every split
+            merge[row * (D + 2) + D + 1] = ok ? l[r] : 0.f;
+          }
+        }
+      }
+    }
+    cluster_sync_all();
+    for (int row = split; row < G; row += p.num_splits) {
+      const uint32_t base = smem_addr(merge) + (uint32_t)(row * (D + 2)) * 4u;
+      float mx = -CUDART_INF_F;
+      for (int s = 0; s < p.num_splits; ++s)
+        if (ld_peer_smem(base + (D + 1) * 4u, s) > 0.f) mx = fmaxf(mx, ld_peer_smem(base + D * 4u, s));
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D;
+      for (int d = tid; d < D; d += blockDim.x) {
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < p.num_splits; ++s) {
+          const float ls = ld_peer_smem(base + (D + 1) * 4u, s);
+          if (ls > 0.f) {
+            const float w = exp2f(ld_peer_smem(base + D * 4u, s) - mx);
+            num += w * ld_peer_smem(base + d * 4u, s);
+            den += w * ls;
+          }
+        }
+        out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      }
+    }
+    cluster_sync_all();                   // nobody leaves while a peer may still read its shared memory
     return;
   }
+  if (is_producer || !ok) return;
 
-  // finish: reduce the row sums over the quad, write the output row or the partial
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-  }
+  // write the output rows, or the partials for the merge kernel
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     if (row_pos[r] < 0) continue;
@@ -468,10 +564,10 @@ bool cache_map(const void* base, int64_t rows, int head_dim, int box_rows, CUten
   return true;
 }
 
-template <int D, int KT, int STAGES, bool DECODE>
+template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
 int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
               cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<D, KT, STAGES, DECODE>;
+  auto kernel = attention_tc_kernel<D, KT, STAGES, DECODE, CLUSTER>;
   constexpr int smem = Smem<D, KT, STAGES>::kBytes;
   static bool configured = false;
   if (!configured) {
@@ -481,10 +577,19 @@ int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_
   }
   const int G = p.num_heads / p.num_kv_heads;
   TcParams tp{p, box_rows};
-  dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
-  const int threads = DECODE ? 32 : 32 * G;
-  kernel<<<grid, threads, smem, stream>>>(k_map, v_map, tp);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
+  config.blockDim = dim3(32 * ((DECODE ? 1 : G) + 1));      // the consumers and one producer warp
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = CLUSTER ? (unsigned)p.num_splits : 1u;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, k_map, v_map, tp);
 }
 
 }  // namespace
@@ -502,6 +607,11 @@ bool attention_tc_supported(const PagedAttentionParams& p) {
   return encode_fn() != nullptr;
 }
 
+// Decode with 2, 4 or 8 key splits merges them inside the kernel (a cluster per token and kv head).
+bool attention_tc_merges_in_kernel(const PagedAttentionParams& p) {
+  return p.q_tile == 1 && (p.num_splits == 2 || p.num_splits == 4 || p.num_splits == 8);
+}
+
 int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
   const bool decode = p.q_tile == 1;
   const int kt = decode ? 32 : 64;
@@ -512,11 +622,15 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
       !cache_map(p.v_cache, rows, p.head_dim, box_rows, &v_map))
     return (int)cudaErrorInvalidValue;
   if (decode) {
-    if (p.head_dim == 128) return launch_tc<128, 32, 4, true>(p, box_rows, k_map, v_map, stream);
-    return launch_tc<64, 32, 4, true>(p, box_rows, k_map, v_map, stream);
+    if (attention_tc_merges_in_kernel(p)) {
+      if (p.head_dim == 128) return launch_tc<128, 32, 4, true, true>(p, box_rows, k_map, v_map, stream);
+      return launch_tc<64, 32, 4, true, true>(p, box_rows, k_map, v_map, stream);
+    }
+    if (p.head_dim == 128) return launch_tc<128, 32, 4, true, false>(p, box_rows, k_map, v_map, stream);
+    return launch_tc<64, 32, 4, true, false>(p, box_rows, k_map, v_map, stream);
   }
-  if (p.head_dim == 128) return launch_tc<128, 64, 3, false>(p, box_rows, k_map, v_map, stream);
-  return launch_tc<64, 64, 3, false>(p, box_rows, k_map, v_map, stream);
+  if (p.head_dim == 128) return launch_tc<128, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
+  return launch_tc<64, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
 }
 
 }  // namespace akv

@@ -92,6 +92,7 @@ int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream);
 // The tensor-core kernels (attention_tc.cu): whether they take the problem, and their launch (without the merge).
 bool attention_tc_supported(const PagedAttentionParams& p);
 int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream);
+bool attention_tc_merges_in_kernel(const PagedAttentionParams& p);
 
 // tokens[r] = argmax(logits[r]) where temperature[r] == 0, else the inverse-CDF draw of
 // softmax(logits[r] / temperature[r]) at uniform[r].

@@ -263,7 +263,7 @@ int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream) {
     if (q.q_tile > 1) q.num_splits = 1;          // the prompt kernel walks all keys of a tile itself
     const int err = launch_attention_tc(q, stream);
     if (err != 0) return err;
-    return q.num_splits > 1 ? launch_merge<__nv_bfloat16>(q, stream) : 0;
+    return (q.num_splits > 1 && !attention_tc_merges_in_kernel(q)) ? launch_merge<__nv_bfloat16>(q, stream) : 0;
   }
   return p.dtype == kBFloat16 ? launch_typed<__nv_bfloat16>(p, stream) : launch_typed<float>(p, stream);
 }

@@ -139,6 +139,136 @@ __global__ void qk_norm_rope_write_kernel(QkRopeWriteParams p) {
   }
 }
 
+// Fast path (head size a multiple of 4, the whole head rotated or none of it, one input tensor): 8 warps = 8
+// heads of one token per block, the token's cos/sin table computed once per block in shared memory, every lane
+// owns two adjacent elements of the low half and their partners in the high half (4- or 8-byte accesses).
+template <typename T>
+struct Pair;
+template <>
+struct Pair<float> {
+  static __device__ __forceinline__ void load(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+  }
+  static __device__ __forceinline__ void store(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+  }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float& a, float& b) {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(p);
+    a = __uint_as_float(raw << 16); b = __uint_as_float(raw & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+constexpr int kFastWarps = 8;
+constexpr int kMaxUnitsPerLane = 4;   // head_dim <= 512
+
+template <typename T>
+__global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_write_fast_kernel(QkRopeWriteParams p) {
+  extern __shared__ float cs[];   // [2][half]: cos, sin of this token's angles
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_heads = p.num_heads + 2 * p.num_kv_heads;
+  const int64_t token = blockIdx.y + (int64_t)blockIdx.z * 65535;
+  if (token >= p.num_tokens) return;
+  const int D = p.head_dim, half = D / 2, units = D / 4;
+  const bool rotary = p.inv_freq != nullptr && p.rotary_dim == D;
+  if (rotary) {
+    const float pos = (float)p.positions[token];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float sn, co;
+      sincosf(pos * p.inv_freq[j], &sn, &co);
+      cs[j] = co;
+      cs[half + j] = sn;
+    }
+    __syncthreads();
+  }
+  const int head = blockIdx.x * kFastWarps + warp;
+  if (head >= total_heads) return;
+  const T* src = (const T*)p.qkv + (token * total_heads + head) * (int64_t)D;
+  const bool is_q = head < p.num_heads;
+  const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
+  const int local = is_q ? head : (is_k ? head - p.num_heads : head - p.num_heads - p.num_kv_heads);
+  T* dense_out = nullptr;
+  if (is_q) dense_out = (T*)p.q_out + (token * p.num_heads + local) * (int64_t)D;
+  else if (is_k && p.k_out) dense_out = (T*)p.k_out + (token * p.num_kv_heads + local) * (int64_t)D;
+  else if (!is_k && p.v_out) dense_out = (T*)p.v_out + (token * p.num_kv_heads + local) * (int64_t)D;
+  T* cache_out = nullptr;
+  if (!is_q && p.slots != nullptr && p.k_cache != nullptr) {
+    const int64_t slot = p.slots[token];
+    if (slot >= 0) {
+      if (slot >= p.num_pages * p.page_size) {
+        if (lane == 0) set_status(p.status, kBadSlot);
+      } else {
+        const int64_t page = slot / p.page_size, off = slot % p.page_size;
+        T* base = (T*)(is_k ? p.k_cache : p.v_cache);
+        cache_out = base + ((page * p.num_kv_heads + local) * p.page_size + off) * (int64_t)D;
+      }
+    }
+  }
+  float lo[kMaxUnitsPerLane][2], hi[kMaxUnitsPerLane][2];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxUnitsPerLane; ++c) {
+    const int u = c * 32 + lane;
+    if (u < units) {
+      Pair<T>::load(src + 2 * u, lo[c][0], lo[c][1]);
+      Pair<T>::load(src + half + 2 * u, hi[c][0], hi[c][1]);
+      ss += lo[c][0] * lo[c][0] + lo[c][1] * lo[c][1] + hi[c][0] * hi[c][0] + hi[c][1] * hi[c][1];
+    }
+  }
+  const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+    for (int c = 0; c < kMaxUnitsPerLane; ++c) {
+      const int u = c * 32 + lane;
+      if (u < units) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          lo[c][e] = lo[c][e] * inv * w[2 * u + e];
+          hi[c][e] = hi[c][e] * inv * w[half + 2 * u + e];
+        }
+      }
+    }
+  }
+  if (rotary && (is_q || is_k)) {
+#pragma unroll
+    for (int c = 0; c < kMaxUnitsPerLane; ++c) {
+      const int u = c * 32 + lane;
+      if (u < units) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float co = cs[2 * u + e], sn = cs[half + 2 * u + e];
+          const float a = lo[c][e], b = hi[c][e];
+          lo[c][e] = a * co - b * sn;
+          hi[c][e] = b * co + a * sn;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < kMaxUnitsPerLane; ++c) {
+    const int u = c * 32 + lane;
+    if (u < units) {
+      if (dense_out) {
+        Pair<T>::store(dense_out + 2 * u, lo[c][0], lo[c][1]);
+        Pair<T>::store(dense_out + half + 2 * u, hi[c][0], hi[c][1]);
+      }
+      if (cache_out) {
+        Pair<T>::store(cache_out + 2 * u, lo[c][0], lo[c][1]);
+        Pair<T>::store(cache_out + half + 2 * u, hi[c][0], hi[c][1]);
+      }
+    }
+  }
+}
+
 int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0) return 0;
   if (p.head_dim % 2 || p.head_dim / 2 > 32 * kMaxPairsPerLane) return (int)cudaErrorInvalidValue;
@@ -147,6 +277,18 @@ int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
   const int64_t ny = p.num_tokens < 65535 ? p.num_tokens : 65535;
   const int64_t nz = (p.num_tokens + 65534) / 65535;
   if (nz > 65535) return (int)cudaErrorInvalidValue;
+  const bool whole_or_none = p.inv_freq == nullptr || p.rotary_dim == p.head_dim || p.rotary_dim == 0;
+  if (p.qkv_parts == 0 && p.head_dim % 4 == 0 && whole_or_none && p.head_dim / 4 <= 32 * kMaxUnitsPerLane) {
+    QkRopeWriteParams q = p;
+    if (q.rotary_dim != q.head_dim) q.inv_freq = nullptr;
+    dim3 fast_grid((unsigned)((total_heads + kFastWarps - 1) / kFastWarps), (unsigned)ny, (unsigned)nz);
+    const size_t table = q.inv_freq ? (size_t)p.head_dim * sizeof(float) : 0;
+    if (p.dtype == kBFloat16)
+      qk_norm_rope_write_fast_kernel<__nv_bfloat16><<<fast_grid, kFastWarps * 32, table, stream>>>(q);
+    else
+      qk_norm_rope_write_fast_kernel<float><<<fast_grid, kFastWarps * 32, table, stream>>>(q);
+    return (int)cudaGetLastError();
+  }
   dim3 grid((unsigned)((total_heads + warps - 1) / warps), (unsigned)ny, (unsigned)nz);
   const size_t smem = (p.rotary_dim != p.head_dim && p.inv_freq) ? (size_t)warps * p.head_dim * sizeof(float) : 0;
   if (p.dtype == kBFloat16) {

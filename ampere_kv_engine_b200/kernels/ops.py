@@ -113,9 +113,19 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
     general kernel one warp per (token, kv head, 8 rows, split), sixteen to an SM.
     """
     if tensor_core:
-        items, target, min_keys = max(1, num_tiles * num_kv_heads), 148 * 3, 128
-    else:
-        items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), 148 * 16, 128
+        # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  Cost model: rounds of CTAs over the
+        # GPU's 148 x 3 slots, each CTA walking its share of 32-key blocks plus a fixed start-up of about two.
+        items, slots = max(1, num_tiles * num_kv_heads), 148 * 3
+        blocks = (max_context + 31) // 32
+        best, best_cost = 1, None
+        for s in (1, 2, 4, 8):
+            if s > 1 and blocks // s < 2:
+                break
+            cost = -(-items * s // slots) * (-(-blocks // s) + 2)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
+        return best
+    items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), 148 * 16, 128
     if items >= target or max_context <= min_keys:
         return 1
     want = target // items
