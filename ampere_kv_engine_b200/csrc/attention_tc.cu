@@ -5,8 +5,10 @@
 // Two kernels share the inner loop:
 //   * prompt portions: one CTA per (query tile of up to 16 tokens, kv head); warp g owns q-head kvh*G + g, its
 //     16 MMA rows are the tile's tokens; the G warps share every K/V tile (one read per GQA group).
-//   * decoded tokens: one single-warp CTA per (token, kv head, key split); the MMA rows are the G q-heads of the
-//     group; with more than one split, (acc, max, sum) partials go to the merge kernel of paged_attention.cu.
+//   * decoded tokens: one CTA per (token, kv head, key split); the MMA rows are the G q-heads of the group; four
+//     consumer warps take the CTA's 32-key blocks in turn and are combined in shared memory; 2, 4 or 8 key
+//     splits form a thread-block cluster and are merged through distributed shared memory (other split counts
+//     leave (acc, max, sum) partials for the merge kernel of paged_attention.cu).
 //
 // Same mathematics as the general kernel and as the reference (ampere_kv/kv_cache.py:76-94,
 // csrc/paged_decode.cu:166-243): score = q.k * scale, key j visible to the query at position t iff j <= t (and
@@ -206,7 +208,7 @@ template <int D, int KT, int STAGES>
 struct Smem {
   static constexpr int kArea = KT * D * 2;
   static constexpr int kStage = 2 * kArea;
-  static constexpr int kMerge = 16 * (D + 2) * 4;                      // 16 rows of (acc[D], max, sum) float32
+  static constexpr int kMerge = 5 * 16 * (D + 2) * 4;   // per consumer warp (up to 4) and combined: 16 rows of (acc[D], max, sum)
   static_assert(kMerge <= STAGES * kStage, "the merge buffer must fit in the stage ring");
   static constexpr int kBytes = STAGES * kStage + 2 * STAGES * 8 + 1024;   // + alignment slack
 };
@@ -229,15 +231,19 @@ struct TableWindow {
   }
 };
 
-// Issue the TMA loads of the key block starting at key0 into `stage`.  Called by the whole producer warp.
+// Issue this producer warp's share of the TMA loads of the key block starting at key0 into `stage`.  Issuing a
+// tensor copy costs the issuing thread on the order of a hundred cycles, and a block of 16-token pages needs
+// eight of them, so the copies of a block are dealt out to `num_producers` warps (copy i to warp i mod n); each
+// announces its own bytes on the stage's barrier, which counts `num_producers` arrivals.
 template <int D, int KT>
 __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMap* k_map, const CUtensorMap* v_map,
                                             TableWindow& window, int kvh, int key0, int key_end, uint8_t* stage,
-                                            uint64_t* bar) {
+                                            uint64_t* bar, int producer, int num_producers) {
   const PagedAttentionParams& p = tp.p;
   const int lane = threadIdx.x & 31;
   const int P = p.page_size, rows = tp.box_rows;
   const int boxes = KT / rows;
+  constexpr int H = D / 64;
   uint32_t bytes = 0;
   int page_of[KT / 8];   // rows >= 8, so at most KT / 8 boxes
 #pragma unroll
@@ -252,7 +258,11 @@ __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMa
           page = -1;
         }
         page_of[b] = page;
-        if (page >= 0) bytes += 2u * rows * D * 2u;
+        if (page >= 0) {
+#pragma unroll
+          for (int c = 0; c < 2 * H; ++c)
+            if ((b * 2 * H + c) % num_producers == producer) bytes += (uint32_t)rows * 128u;
+        }
       }
     }
   }
@@ -264,9 +274,13 @@ __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMa
         const int key = key0 + b * rows;
         const int y = (page_of[b] * p.num_kv_heads + kvh) * P + key % P;
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) {
-          tma_load_2d(stage + h * KT * 128 + b * rows * 128, k_map, h * 64, y, bar);
-          tma_load_2d(stage + KT * D * 2 + h * KT * 128 + b * rows * 128, v_map, h * 64, y, bar);
+        for (int c = 0; c < 2 * H; ++c) {
+          if ((b * 2 * H + c) % num_producers != producer) continue;
+          const int h = c >> 1;
+          if (c & 1)
+            tma_load_2d(stage + KT * D * 2 + h * KT * 128 + b * rows * 128, v_map, h * 64, y, bar);
+          else
+            tma_load_2d(stage + h * KT * 128 + b * rows * 128, k_map, h * 64, y, bar);
         }
       }
     }
@@ -305,9 +319,13 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-// Warps 0 .. consumers-1 compute (prompt kernel: warp g = q-head g of the group; decode kernel: one warp, its
-// rows are the group's heads); the last warp is the producer: it walks the block table and keeps the TMA ring
-// full.  full[s]: the stage's bytes have landed; empty[s]: every consumer warp is done with the stage.
+// Producer warps of one CTA.  Measured on B200: one is best; more producers only add warps that spin on the
+// barriers (decode at batch 64, 1,152 keys: 102 us with one producer, 184 us with four).
+constexpr int kProducers = 1;
+
+// Warps 0 .. consumers-1 compute (prompt kernel: warp g = q-head g of the group; decode kernel: every warp's
+// rows are the group's heads, the warps share out the key blocks); the last kProducers warps are the producers: they walk the block table and
+// keep the TMA ring full.  full[s]: the stage's bytes have landed; empty[s]: every consumer warp is done with the stage.
 // CLUSTER (decode only): the key splits of one (token, kv head) form a cluster; the partial results are merged
 // through distributed shared memory instead of a second kernel.
 template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
@@ -319,8 +337,8 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Smem<D, KT, STAGES>::kStage);
   uint64_t* empty = full + STAGES;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int consumers = (int)(blockDim.x >> 5) - 1;
-  const bool is_producer = warp == consumers;
+  const int consumers = (int)(blockDim.x >> 5) - kProducers;
+  const bool is_producer = warp >= consumers;
   const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
 
@@ -351,8 +369,8 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], consumers);
+      mbar_init(&full[s], kProducers);
+      mbar_init(&empty[s], DECODE ? 1 : consumers);     // decode: a block belongs to one consumer warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -372,7 +390,7 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         break;
       }
       issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi,
-                         smem + s * Smem<D, KT, STAGES>::kStage, &full[s]);
+                         smem + s * Smem<D, KT, STAGES>::kStage, &full[s], warp - consumers, kProducers);
     }
   } else {
     // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
@@ -413,8 +431,10 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     for (int v = 0; v < D / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
     const float scale_log2 = p.scale * kLog2e;
 
+    // Prompt kernel: every consumer warp (one q-head each) works on every block.  Decode kernel: the consumer
+    // warps take the blocks in turn (warp w: blocks w, w + consumers, ...) and are merged after the loop.
     // A warp whose wait ran out keeps walking the loop (the consumers' barriers stay matched) but computes nothing.
-    for (int b = 0; b < num_blocks; ++b) {
+    for (int b = DECODE ? warp : 0; b < num_blocks; b += DECODE ? consumers : 1) {
       const int s = b % STAGES;
       uint8_t* stage = smem + s * Smem<D, KT, STAGES>::kStage;
       if (ok && !mbar_wait(&full[s], (b / STAGES) & 1)) ok = false;
@@ -423,8 +443,13 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       if (nvalid < KT) {
         // V rows past the end may hold anything (or were never loaded): make them zero before P.V reads them.
         // This only ever happens in a range's last block, so no later TMA load touches these rows.
-        zero_v_rows<D, KT>(stage, nvalid, tid, consumers * 32);
-        if (consumers > 1) consumer_sync(consumers); else __syncwarp();
+        if (DECODE) {
+          zero_v_rows<D, KT>(stage, nvalid, lane, 32);
+          __syncwarp();
+        } else {
+          zero_v_rows<D, KT>(stage, nvalid, tid, consumers * 32);
+          consumer_sync(consumers);
+        }
       }
       if (ok)
         process_block<D, KT>(q_frag, smem_addr(stage), smem_addr(stage + KT * D * 2), key0, nvalid, row_pos,
@@ -440,12 +465,13 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   }
   if (!ok && lane == 0) set_status(p.status, kWaitTimeout);
 
-  if (DECODE && CLUSTER) {
-    // every split leaves (acc, max, sum) of its rows in its own shared memory; after the cluster barrier the CTA
-    // of rank r merges rows r, r + splits, ... reading its peers' shared memory in split order
+  if (DECODE) {
+    // 1. the consumer warps of this CTA leave (acc, max, sum) of their rows in shared memory and are combined
     __syncthreads();                      // the stage ring is idle: all loads have landed and been consumed
     float* merge = reinterpret_cast<float*>(smem);
+    constexpr int kRow = D + 2;
     if (!is_producer) {
+      float* mine = merge + (1 + warp) * 16 * kRow;
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + 8 * r;
@@ -453,66 +479,93 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
 #pragma unroll
           for (int v = 0; v < D / 8; ++v) {
             const int col = v * 8 + (lane & 3) * 2;
-            merge[row * (D + 2) + col] = ok ? o[v][2 * r] : 0.f;
-            merge[row * (D + 2) + col + 1] = ok ? o[v][2 * r + 1] : 0.f;
+            mine[row * kRow + col] = ok ? o[v][2 * r] : 0.f;
+            mine[row * kRow + col + 1] = ok ? o[v][2 * r + 1] : 0.f;
           }
           if ((lane & 3) == 0) {
-            merge[row * (D + 2) + D] = m[r];            // log2 units, the same in every split
-            merge[row * (D + 2) + D + 1] = ok ? l[r] : 0.f;
+            mine[row * kRow + D] = m[r];            // log2 units
+            mine[row * kRow + D + 1] = ok ? l[r] : 0.f;
           }
         }
       }
     }
-    cluster_sync_all();
-    for (int row = split; row < G; row += p.num_splits) {
-      const uint32_t base = smem_addr(merge) + (uint32_t)(row * (D + 2)) * 4u;
+    __syncthreads();
+    for (int idx = tid; idx < G * kRow; idx += blockDim.x) {
+      const int row = idx / kRow, col = idx - row * kRow;
       float mx = -CUDART_INF_F;
-      for (int s = 0; s < p.num_splits; ++s)
-        if (ld_peer_smem(base + (D + 1) * 4u, s) > 0.f) mx = fmaxf(mx, ld_peer_smem(base + D * 4u, s));
-      __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D;
-      for (int d = tid; d < D; d += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < p.num_splits; ++s) {
-          const float ls = ld_peer_smem(base + (D + 1) * 4u, s);
-          if (ls > 0.f) {
-            const float w = exp2f(ld_peer_smem(base + D * 4u, s) - mx);
-            num += w * ld_peer_smem(base + d * 4u, s);
-            den += w * ls;
-          }
+      for (int w = 0; w < consumers; ++w) {
+        const float* part = merge + (1 + w) * 16 * kRow + row * kRow;
+        if (part[D + 1] > 0.f) mx = fmaxf(mx, part[D]);
+      }
+      float acc = 0.f;
+      if (col == D) {
+        acc = mx;
+      } else {
+        for (int w = 0; w < consumers; ++w) {
+          const float* part = merge + (1 + w) * 16 * kRow + row * kRow;
+          if (part[D + 1] > 0.f) acc += exp2f(part[D] - mx) * part[col];     // col == D + 1: the sums
         }
-        out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      }
+      merge[row * kRow + col] = acc;
+    }
+    __syncthreads();
+    // 2. across the key splits
+    if (CLUSTER) {
+      // after the cluster barrier the CTA of rank r merges rows r, r + splits, ... reading its peers' shared
+      // memory in split order
+      cluster_sync_all();
+      for (int row = split; row < G; row += p.num_splits) {
+        const uint32_t base = smem_addr(merge) + (uint32_t)(row * kRow) * 4u;
+        float mx = -CUDART_INF_F;
+        for (int s = 0; s < p.num_splits; ++s)
+          if (ld_peer_smem(base + (D + 1) * 4u, s) > 0.f) mx = fmaxf(mx, ld_peer_smem(base + D * 4u, s));
+        __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D;
+        for (int d = tid; d < D; d += blockDim.x) {
+          float num = 0.f, den = 0.f;
+          for (int s = 0; s < p.num_splits; ++s) {
+            const float ls = ld_peer_smem(base + (D + 1) * 4u, s);
+            if (ls > 0.f) {
+              const float w = exp2f(ld_peer_smem(base + D * 4u, s) - mx);
+              num += w * ld_peer_smem(base + d * 4u, s);
+              den += w * ls;
+            }
+          }
+          out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        }
+      }
+      cluster_sync_all();                   // nobody leaves while a peer may still read its shared memory
+      return;
+    }
+    for (int idx = tid; idx < G * D; idx += blockDim.x) {
+      const int row = idx / D, d = idx - row * D;
+      const int64_t out_row = (int64_t)q0 * NH + kvh * G + row;
+      const float sum = merge[row * kRow + D + 1];
+      if (p.num_splits == 1) {
+        ((__nv_bfloat16*)p.out)[out_row * D + d] = __float2bfloat16_rn(sum > 0.f ? merge[row * kRow + d] / sum : 0.f);
+      } else {
+        float* part = p.partials + (out_row * p.num_splits + split) * (int64_t)kRow;
+        part[d] = merge[row * kRow + d];
+        if (d == 0) {
+          part[D] = merge[row * kRow + D] * kLn2;     // natural-log units, as the merge kernel expects
+          part[D + 1] = sum;
+        }
       }
     }
-    cluster_sync_all();                   // nobody leaves while a peer may still read its shared memory
     return;
   }
   if (is_producer || !ok) return;
 
-  // write the output rows, or the partials for the merge kernel
+  // prompt kernel: every warp writes its own head's rows
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     if (row_pos[r] < 0) continue;
     const int64_t row = (int64_t)row_token[r] * NH + row_head[r];
-    if (!DECODE || p.num_splits == 1) {
-      __nv_bfloat16* out = (__nv_bfloat16*)p.out + row * D;
-      const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    __nv_bfloat16* out = (__nv_bfloat16*)p.out + row * D;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
 #pragma unroll
-      for (int v = 0; v < D / 8; ++v) {
-        const int col = v * 8 + (lane & 3) * 2;
-        *reinterpret_cast<uint32_t*>(out + col) = pack_bf16(o[v][2 * r] * inv, o[v][2 * r + 1] * inv);
-      }
-    } else {
-      float* part = p.partials + (row * p.num_splits + split) * (int64_t)(D + 2);
-#pragma unroll
-      for (int v = 0; v < D / 8; ++v) {
-        const int col = v * 8 + (lane & 3) * 2;
-        part[col] = o[v][2 * r];
-        part[col + 1] = o[v][2 * r + 1];
-      }
-      if ((lane & 3) == 0) {
-        part[D] = m[r] * kLn2;     // back to natural-log units, as the merge kernel expects
-        part[D + 1] = l[r];
-      }
+    for (int v = 0; v < D / 8; ++v) {
+      const int col = v * 8 + (lane & 3) * 2;
+      *reinterpret_cast<uint32_t*>(out + col) = pack_bf16(o[v][2 * r] * inv, o[v][2 * r + 1] * inv);
     }
   }
 }
@@ -564,6 +617,8 @@ bool cache_map(const void* base, int64_t rows, int head_dim, int box_rows, CUten
   return true;
 }
 
+constexpr int kDecodeConsumers = 4;
+
 template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
 int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
               cudaStream_t stream) {
@@ -579,7 +634,7 @@ int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_
   TcParams tp{p, box_rows};
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
-  config.blockDim = dim3(32 * ((DECODE ? 1 : G) + 1));      // the consumers and one producer warp
+  config.blockDim = dim3(32 * ((DECODE ? kDecodeConsumers : G) + kProducers));      // consumer and producer warps
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -623,11 +678,11 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
     return (int)cudaErrorInvalidValue;
   if (decode) {
     if (attention_tc_merges_in_kernel(p)) {
-      if (p.head_dim == 128) return launch_tc<128, 32, 4, true, true>(p, box_rows, k_map, v_map, stream);
-      return launch_tc<64, 32, 4, true, true>(p, box_rows, k_map, v_map, stream);
+      if (p.head_dim == 128) return launch_tc<128, 32, 6, true, true>(p, box_rows, k_map, v_map, stream);
+      return launch_tc<64, 32, 6, true, true>(p, box_rows, k_map, v_map, stream);
     }
-    if (p.head_dim == 128) return launch_tc<128, 32, 4, true, false>(p, box_rows, k_map, v_map, stream);
-    return launch_tc<64, 32, 4, true, false>(p, box_rows, k_map, v_map, stream);
+    if (p.head_dim == 128) return launch_tc<128, 32, 6, true, false>(p, box_rows, k_map, v_map, stream);
+    return launch_tc<64, 32, 6, true, false>(p, box_rows, k_map, v_map, stream);
   }
   if (p.head_dim == 128) return launch_tc<128, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
   return launch_tc<64, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);

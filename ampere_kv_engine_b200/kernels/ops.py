@@ -109,19 +109,20 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
                   tensor_core: bool = False) -> int:
     """How many key ranges each decoded token's attention is cut into so that a small batch still fills the GPU.
 
-    The tensor-core decode kernel runs one single-warp CTA per (token, kv head, split), three to an SM; the
-    general kernel one warp per (token, kv head, 8 rows, split), sixteen to an SM.
+    The tensor-core decode kernel runs one CTA per (token, kv head, split), two to an SM; the general kernel
+    one warp per (token, kv head, 8 rows, split), sixteen to an SM.
     """
     if tensor_core:
         # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  Cost model: rounds of CTAs over the
-        # GPU's 148 x 3 slots, each CTA walking its share of 32-key blocks plus a fixed start-up of about two.
-        items, slots = max(1, num_tiles * num_kv_heads), 148 * 3
+        # GPU's 148 x 2 slots; a CTA's four consumer warps walk its share of 32-key blocks four at a time, plus a
+        # fixed start-up and merge worth about three blocks.
+        items, slots = max(1, num_tiles * num_kv_heads), 148 * 2
         blocks = (max_context + 31) // 32
         best, best_cost = 1, None
         for s in (1, 2, 4, 8):
-            if s > 1 and blocks // s < 2:
+            if s > 1 and blocks // s < 4:
                 break
-            cost = -(-items * s // slots) * (-(-blocks // s) + 2)
+            cost = -(-items * s // slots) * (-(-blocks // (4 * s)) + 3)
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
@@ -157,8 +158,9 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     return tokens
 
 
-#: products of at most this many bfloat16 tokens go through the package's own tcgen05 kernel
-SMALL_M_LIMIT = 64
+#: products of at most this many bfloat16 tokens go through the package's own tcgen05 kernel (the kernel takes
+#: up to 64; measured on B200 the library is faster from 33 tokens on)
+SMALL_M_LIMIT = 32
 use_small_m_gemm = True
 #: hand split-K partial sums to the consuming kernel instead of adding them up inside the product kernel
 prefer_partials = False
