@@ -148,9 +148,10 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference loads the published Qwen3-8B checkpoint by name with local_files_only=True "
-                          "(ampere_kv/runner.py:33-36) and builds its kernels for sm_86 only (setup.py:19); there is "
-                          "no checkpoint and no network here, and it has no random-weights mode"}))
+                          "installed offline into baseline/_ref, but it only runs the published Qwen3-8B checkpoint, "
+                          "loaded by name with local_files_only=True (ampere_kv/runner.py:33-36; no checkpoint and no "
+                          "network here, no random-weights mode), and its extension holds sm_86 machine code only "
+                          "(setup.py:19), which a B200 cannot load"}))
         return 0
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
