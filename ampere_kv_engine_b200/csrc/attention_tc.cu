@@ -342,6 +342,7 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
 
+  pdl_launch_dependents();
   const int seq = p.tile_seq[tile];
   const int q0 = p.tile_q0[tile];
   const int nq = p.tile_nq[tile];
@@ -375,6 +376,7 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_wait();      // q and this step's K/V pages come from the previous kernels
 
   bool ok = true;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
@@ -632,19 +634,10 @@ int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_
   }
   const int G = p.num_heads / p.num_kv_heads;
   TcParams tp{p, box_rows};
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
-  config.blockDim = dim3(32 * ((DECODE ? kDecodeConsumers : G) + kProducers));      // consumer and producer warps
-  config.dynamicSmemBytes = smem;
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = CLUSTER ? (unsigned)p.num_splits : 1u;
-  config.attrs = attr;
-  config.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&config, kernel, k_map, v_map, tp);
+  const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
+  const dim3 block(32 * ((DECODE ? kDecodeConsumers : G) + kProducers));      // consumer and producer warps
+  const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
+  return (int)launch_chain(kernel, grid, block, smem, stream, cluster, k_map, v_map, tp);
 }
 
 }  // namespace

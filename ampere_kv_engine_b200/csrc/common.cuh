@@ -93,4 +93,43 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Programmatic dependent launch.  A kernel of the step's chain lets the next kernel start while it still runs
+// (pdl_launch_dependents, at its top) and waits for the previous kernel's results right before it first touches
+// them (pdl_wait).  What a kernel does before pdl_wait must not depend on the previous kernel: set-up, barrier
+// initialisation, and, in the weight-streaming GEMM, filling the TMA ring with weights.  Both are no-ops in a
+// kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with the programmatic-stream-serialization attribute (and, if cluster_z/cluster_y > 1, a cluster).
+// AKV_NO_PDL=1 in the environment launches without it (for comparisons).
+bool pdl_enabled();
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, dim3 cluster, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  if (cluster.x * cluster.y * cluster.z > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = cluster.x;
+    attrs[n].val.clusterDim.y = cluster.y;
+    attrs[n].val.clusterDim.z = cluster.z;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  config.attrs = attrs;
+  config.numAttrs = n;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 }  // namespace akv

@@ -10,7 +10,17 @@
 #include "common.cuh"
 #include "launchers.h"
 
+#include <stdlib.h>
+
 namespace akv {
+
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("AKV_NO_PDL");
+    return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+  }();
+  return enabled;
+}
 
 __global__ void smoke_add_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                  float* __restrict__ out, int64_t n) {
@@ -29,6 +39,8 @@ template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ hidden, int64_t hidden_size, int64_t vocab,
                                  int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t token = blockIdx.x;
   int64_t id = ids[token];
   if (id < 0 || id >= vocab) {
@@ -45,12 +57,10 @@ int launch_embedding(const int32_t* ids, const void* table, float* hidden, int64
   if (num_tokens == 0) return 0;
   const int threads = (int)(hidden_size >= 1024 ? 256 : (hidden_size >= 128 ? 128 : 32));
   if (dtype == kBFloat16)
-    embedding_kernel<__nv_bfloat16><<<(unsigned)num_tokens, threads, 0, stream>>>(
-        ids, (const __nv_bfloat16*)table, hidden, hidden_size, vocab, status);
-  else
-    embedding_kernel<float><<<(unsigned)num_tokens, threads, 0, stream>>>(
-        ids, (const float*)table, hidden, hidden_size, vocab, status);
-  return (int)cudaGetLastError();
+    return (int)launch_chain(embedding_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(threads), 0, stream,
+                             dim3(1, 1, 1), ids, (const __nv_bfloat16*)table, hidden, hidden_size, vocab, status);
+  return (int)launch_chain(embedding_kernel<float>, dim3((unsigned)num_tokens), dim3(threads), 0, stream,
+                           dim3(1, 1, 1), ids, (const float*)table, hidden, hidden_size, vocab, status);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -73,6 +83,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const TD* __restr
                                    int64_t hidden_size, float eps, int* status) {
   __shared__ float scratch[33];
   extern __shared__ float row_cache[];  // hidden_size floats
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t out_row = blockIdx.x;
   int64_t src = out_row;
   const bool gathered = rows != nullptr;
@@ -138,6 +150,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const T* __re
                                        const int32_t* __restrict__ rows, int64_t num_tokens, int hidden_size,
                                        float eps, int* status) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t out_row = blockIdx.x;
   int64_t src = out_row;
   const bool gathered = rows != nullptr;
@@ -196,9 +210,8 @@ static int launch_add_rmsnorm_general(float* hidden, const void* delta, int num_
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
-  kernel<<<(unsigned)n, threads, smem, stream>>>(hidden, (const TD*)delta, num_parts, weight, (T*)out, rows,
-                                                 num_tokens, hidden_size, eps, status);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(kernel, dim3((unsigned)n), dim3(threads), smem, stream, dim3(1, 1, 1), hidden,
+                           (const TD*)delta, num_parts, weight, (T*)out, rows, num_tokens, hidden_size, eps, status);
 }
 
 template <typename T>
@@ -209,15 +222,14 @@ static int launch_add_rmsnorm_fast(float* hidden, const void* delta, const float
   int threads = 32;
   while (threads < 512 && threads * 2 <= quads) threads *= 2;      // two rounds per thread when the row is long
   const int iters = (quads + threads - 1) / threads;
-#define AKV_NORM(IT)                                                                                         \
-  add_rmsnorm_vec_kernel<T, IT><<<(unsigned)n, threads, 0, stream>>>(hidden, (const T*)delta, weight, (T*)out, \
-                                                                     rows, num_tokens, (int)hidden_size, eps, status)
-  if (iters <= 1) AKV_NORM(1);
-  else if (iters <= 2) AKV_NORM(2);
-  else if (iters <= 4) AKV_NORM(4);
-  else AKV_NORM(8);
+#define AKV_NORM(IT)                                                                                           \
+  launch_chain(add_rmsnorm_vec_kernel<T, IT>, dim3((unsigned)n), dim3(threads), 0, stream, dim3(1, 1, 1), hidden, \
+               (const T*)delta, weight, (T*)out, rows, num_tokens, (int)hidden_size, eps, status)
+  if (iters <= 1) return (int)AKV_NORM(1);
+  if (iters <= 2) return (int)AKV_NORM(2);
+  if (iters <= 4) return (int)AKV_NORM(4);
+  return (int)AKV_NORM(8);
 #undef AKV_NORM
-  return (int)cudaGetLastError();
 }
 
 int launch_add_rmsnorm(float* hidden, const void* delta, int delta_parts, const float* weight, void* out,
@@ -257,6 +269,8 @@ int launch_add_rmsnorm(float* hidden, const void* delta, int delta_parts, const 
 template <typename T, typename TI, bool PARTS>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int num_parts, T* __restrict__ out, int64_t inter,
                                 int64_t total, int64_t part_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t token = idx / inter, i = idx - token * inter;
@@ -280,6 +294,8 @@ template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter_vecs,
                                     int64_t total_vecs) {
   constexpr int V = 16 / sizeof(T);     // elements per 16-byte vector
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (idx >= total_vecs) return;
   const int64_t token = idx / inter_vecs;
@@ -319,12 +335,11 @@ int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_token
     const int64_t blocks = (total_vecs + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
     if (dtype == kBFloat16)
-      silu_mul_vec_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
-          (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (int)(inter / vec), total_vecs);
-    else
-      silu_mul_vec_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out,
-                                                                          (int)(inter / vec), total_vecs);
-    return (int)cudaGetLastError();
+      return (int)launch_chain(silu_mul_vec_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream,
+                               dim3(1, 1, 1), (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (int)(inter / vec),
+                               total_vecs);
+    return (int)launch_chain(silu_mul_vec_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream,
+                             dim3(1, 1, 1), (const float*)gate_up, (float*)out, (int)(inter / vec), total_vecs);
   }
   const int64_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;

@@ -160,6 +160,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   const int kb_begin = split * base + min(split, extra);
   const int num_kb = base + (split < extra ? 1 : 0);
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
@@ -182,9 +183,20 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // The weights do not depend on the kernel before this one: fill the ring's weight halves first, then wait
+      // for that kernel and fetch the activations.
+      const int ahead = min(num_kb, kStages);
+      for (int kb = 0; kb < ahead; ++kb) {
+        mbar_expect_tx(&full[kb], GemmSmem<BN>::kStage);
+        tma_load_2d(smem + kb * GemmSmem<BN>::kStage, &w_map, (kb_begin + kb) * kTileK, tile * kTileM, &full[kb]);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < ahead; ++kb)
+        tma_load_2d(smem + kb * GemmSmem<BN>::kStage + GemmSmem<BN>::kA, &x_map, (kb_begin + kb) * kTileK, 0,
+                    &full[kb]);
+      for (int kb = ahead; kb < num_kb; ++kb) {
         const int s = kb % kStages;
-        if (kb >= kStages && !mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+        if (!mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
           ok = false;
           break;
         }
@@ -328,19 +340,9 @@ int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmPara
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)((p.features + kTileM - 1) / kTileM), (unsigned)p.splits);
-  config.blockDim = dim3(192);
-  config.dynamicSmemBytes = GemmSmem<BN>::kBytes;
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = p.out != nullptr ? (unsigned)p.splits : 1u;   // the splits of a tile form the cluster
-  attr[0].val.clusterDim.z = 1;
-  config.attrs = attr;
-  config.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&config, kernel, w_map, x_map, p);
+  const dim3 grid((unsigned)((p.features + kTileM - 1) / kTileM), (unsigned)p.splits);
+  const dim3 cluster(1, p.out != nullptr ? (unsigned)p.splits : 1u, 1);   // the splits of a tile form the cluster
+  return (int)launch_chain(kernel, grid, dim3(192), GemmSmem<BN>::kBytes, stream, cluster, w_map, x_map, p);
 }
 
 template <typename OutT>

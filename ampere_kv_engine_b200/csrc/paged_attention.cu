@@ -31,6 +31,8 @@ template <typename T, int DC>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 paged_attention_kernel(PagedAttentionParams p, int row_groups, int64_t total_items) {
   constexpr int R = kAttnRows;
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t item = (int64_t)blockIdx.x * kAttnWarps + warp;
   if (item >= total_items) return;
@@ -198,6 +200,8 @@ paged_attention_kernel(PagedAttentionParams p, int row_groups, int64_t total_ite
 template <typename T>
 __global__ void merge_splits_kernel(const float* __restrict__ partials, T* __restrict__ out, int num_splits,
                                     int head_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const float* base = partials + row * num_splits * (int64_t)(head_dim + 2);
   float m = -CUDART_INF_F;

@@ -172,6 +172,8 @@ constexpr int kMaxUnitsPerLane = 4;   // head_dim <= 512
 template <typename T>
 __global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_write_fast_kernel(QkRopeWriteParams p) {
   extern __shared__ float cs[];   // [2][half]: cos, sin of this token's angles
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_heads = p.num_heads + 2 * p.num_kv_heads;
   const int64_t token = blockIdx.y + (int64_t)blockIdx.z * 65535;
@@ -284,10 +286,10 @@ int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
     dim3 fast_grid((unsigned)((total_heads + kFastWarps - 1) / kFastWarps), (unsigned)ny, (unsigned)nz);
     const size_t table = q.inv_freq ? (size_t)p.head_dim * sizeof(float) : 0;
     if (p.dtype == kBFloat16)
-      qk_norm_rope_write_fast_kernel<__nv_bfloat16><<<fast_grid, kFastWarps * 32, table, stream>>>(q);
-    else
-      qk_norm_rope_write_fast_kernel<float><<<fast_grid, kFastWarps * 32, table, stream>>>(q);
-    return (int)cudaGetLastError();
+      return (int)launch_chain(qk_norm_rope_write_fast_kernel<__nv_bfloat16>, fast_grid, dim3(kFastWarps * 32), table,
+                               stream, dim3(1, 1, 1), q);
+    return (int)launch_chain(qk_norm_rope_write_fast_kernel<float>, fast_grid, dim3(kFastWarps * 32), table, stream,
+                             dim3(1, 1, 1), q);
   }
   dim3 grid((unsigned)((total_heads + warps - 1) / warps), (unsigned)ny, (unsigned)nz);
   const size_t smem = (p.rotary_dim != p.head_dim && p.inv_freq) ? (size_t)warps * p.head_dim * sizeof(float) : 0;

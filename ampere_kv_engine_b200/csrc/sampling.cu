@@ -22,6 +22,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __shared__ int s_arg[32];
   __shared__ double s_sum[kSampleThreads];
   __shared__ int s_winner;
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const float* x = logits + row * vocab;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -102,9 +104,8 @@ int launch_sample(const float* logits, const float* temperature, const float* un
                   int64_t num_rows, int64_t vocab, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   if (vocab <= 0 || vocab > 0x7ffffffeLL || num_rows > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-  sample_kernel<<<(unsigned)num_rows, kSampleThreads, 0, stream>>>(logits, temperature, uniform, tokens,
-                                                                  vocab);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(sample_kernel, dim3((unsigned)num_rows), dim3(kSampleThreads), 0, stream, dim3(1, 1, 1),
+                           logits, temperature, uniform, tokens, vocab);
 }
 
 }  // namespace akv
