@@ -94,12 +94,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 struct TcParams {
   PagedAttentionParams p;
   int box_rows;     // rows of one TMA box = min(page_size, keys per stage)
+  int use_tma;      // 1: pages arrive by TMA boxes; 0: by 16-byte cp.async copies (small pages, see issue_block_cp)
 };
 
 // Byte offset of (key k, 16-byte chunk c of the head) inside one stage's K or V area.  The area is laid out
 // as [64-dim half][key][128 bytes]; TMA's 128-byte swizzle xors the chunk-in-row with the row's low 3 bits.
-template <int KT>
-__device__ __forceinline__ uint32_t tile_offset(int k, int chunk) {
+// (Fetching both halves of a page with one 3-D box, [key][half][128 bytes], was tried: it halves the number of
+// TMA instructions, changes decode attention by 3 % and costs the prompt kernel 70 % through two-way ldmatrix
+// bank conflicts.)
+template <int D, int KT>
+__device__ __forceinline__ uint32_t tile_offset_d(int k, int chunk) {
   const int half = chunk >> 3, c = chunk & 7;
   return (uint32_t)(half * KT * 128 + k * 128 + ((c ^ (k & 7)) << 4));
 }
@@ -128,7 +132,7 @@ __device__ __forceinline__ void process_block(const uint32_t (&q_frag)[D / 16][4
         uint32_t b0, b1, b2, b3;
         const int key = j * 8 + (lane & 7);
         const int chunk = 2 * t + (lane >> 3);
-        ldmatrix_x4(k_base + tile_offset<KT>(key, chunk), b0, b1, b2, b3);
+        ldmatrix_x4(k_base + tile_offset_d<D, KT>(key, chunk), b0, b1, b2, b3);
         mma_bf16(s[j], q_frag[t], b0, b1);
         mma_bf16(s[j], q_frag[t + 1], b2, b3);
       }
@@ -194,7 +198,7 @@ __device__ __forceinline__ void process_block(const uint32_t (&q_frag)[D / 16][4
         uint32_t b0, b1, b2, b3;
         const int key = u * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int chunk = v + (lane >> 4);
-        ldmatrix_x4_trans(v_base + tile_offset<KT>(key, chunk), b0, b1, b2, b3);
+        ldmatrix_x4_trans(v_base + tile_offset_d<D, KT>(key, chunk), b0, b1, b2, b3);
         mma_bf16(o[v], a, b0, b1);
         mma_bf16(o[v + 1], a, b2, b3);
       }
@@ -301,6 +305,55 @@ __device__ __forceinline__ void zero_v_rows(uint8_t* stage, int first, int tid, 
   }
 }
 
+// The same block, fetched with 16-byte cp.async copies by the 32 lanes of a producer warp, into the same swizzled
+// layout.  A TMA copy of one 16-token page is a 2 KB box, and the SM's TMA unit takes on the order of 150 ns per
+// box whatever its size: measured on B200, a CTA streamed 16-token pages at 14 GB/s that way (8 boxes per
+// 32-key block), which caps decode attention near 3 TB/s and made the prompt kernel TMA-bound as well.  Plain
+// asynchronous copies have no such per-page cost.  Each lane finishes with cp.async.mbarrier.arrive.noinc on the
+// stage's barrier, which therefore counts 32 arrivals per producer warp.
+template <int D, int KT>
+__device__ __forceinline__ void issue_block_cp(const TcParams& tp, TableWindow& window, int kvh, int key0,
+                                               int key_end, uint8_t* stage, uint64_t* bar) {
+  const PagedAttentionParams& p = tp.p;
+  const int lane = threadIdx.x & 31;
+  const int P = p.page_size;
+  constexpr int CH = D * 2 / 16;                 // 16-byte chunks per row
+  // lane b keeps the page of the block's b-th run of (up to) 8 keys; runs never straddle a page (P >= 8)
+  int my_page = -1;
+#pragma unroll
+  for (int b = 0; b < KT / 8; ++b) {
+    const int key = key0 + b * 8;
+    int page = -1;
+    if (key < key_end) {
+      page = window.page(key / P, lane);
+      if (page < 0 || page >= p.num_pages) {
+        if (lane == 0) set_status(p.status, kBadPage);
+        page = -1;
+      }
+    }
+    if (lane == b) my_page = page;
+  }
+  const uint32_t stage_addr = smem_addr(stage);
+  const char* k_base = (const char*)p.k_cache;
+  const char* v_base = (const char*)p.v_cache;
+#pragma unroll 4
+  for (int i = 0; i < 2 * KT * CH / 32; ++i) {
+    const int c = i * 32 + lane;
+    const int kv = c / (KT * CH);
+    const int rem = c - kv * (KT * CH);
+    const int row = rem / CH, ch = rem - row * CH;
+    const int key = key0 + row;
+    const int page = __shfl_sync(0xffffffffu, my_page, row >> 3);
+    if (key < key_end && page >= 0) {
+      const char* src = (kv ? v_base : k_base) +
+                        ((((int64_t)page * p.num_kv_heads + kvh) * P + key % P) * (int64_t)D) * 2 + ch * 16;
+      const uint32_t dst = stage_addr + (kv ? KT * D * 2 : 0) + tile_offset_d<D, KT>(row, ch);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+  }
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
@@ -329,7 +382,7 @@ constexpr int kProducers = 1;
 // CLUSTER (decode only): the key splits of one (token, kv head) form a cluster; the partial results are merged
 // through distributed shared memory instead of a second kernel.
 template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
-__global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
+__global__ void __launch_bounds__(32 * (8 + kProducers)) attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                                     const __grid_constant__ CUtensorMap v_map, TcParams tp) {
   const PagedAttentionParams& p = tp.p;
   extern __shared__ uint8_t smem_raw[];
@@ -370,7 +423,7 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], kProducers);
+      mbar_init(&full[s], tp.use_tma ? kProducers : 32 * kProducers);
       mbar_init(&empty[s], DECODE ? 1 : consumers);     // decode: a block belongs to one consumer warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -391,8 +444,12 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         ok = false;
         break;
       }
-      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi,
-                         smem + s * Smem<D, KT, STAGES>::kStage, &full[s], warp - consumers, kProducers);
+      if (tp.use_tma)
+        issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi,
+                           smem + s * Smem<D, KT, STAGES>::kStage, &full[s], warp - consumers, kProducers);
+      else
+        issue_block_cp<D, KT>(tp, window, kvh, range_lo + b * KT, range_hi, smem + s * Smem<D, KT, STAGES>::kStage,
+                              &full[s]);
     }
   } else {
     // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
@@ -572,6 +629,298 @@ __global__ void attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- decode, cooperative
+// Decoded tokens, second form: the four consumer warps of a CTA work on the SAME 32-key block, so a stage of the
+// TMA ring is held for a quarter of the time and the ring turns over four times faster (decode attention is bound
+// by how many bytes a CTA keeps in flight, not by arithmetic).  Warp w scores keys [8w, 8w + 8) of the block
+// (Q K^T, one 16 x 8 tile over all of D), the warps exchange their row maxima and their probabilities through
+// shared memory, then warp w accumulates P V for head dims [w D/4, (w + 1) D/4).  The MMA rows are the G q-heads
+// of the group, as before; 2, 4 or 8 key splits form a cluster and are merged through distributed shared memory.
+constexpr int kCoopWarps = 4;
+constexpr int kPRow = 40;      // bf16 elements per row of the probability tile: 32 keys + padding against bank conflicts
+
+template <int D, int STAGES>
+struct CoopSmem {
+  static constexpr int KT = 32;
+  static constexpr int kStage = 2 * KT * D * 2;
+  static constexpr int kExchange = 2 * (kCoopWarps * 16 * 4 + 16 * kPRow * 2);   // double-buffered maxima + P tile
+  static constexpr int kMerge = 16 * (D + 2) * 4;
+  static_assert(kMerge <= STAGES * kStage, "the merge buffer must fit in the stage ring");
+  static constexpr int kBytes = STAGES * kStage + kExchange + 2 * STAGES * 8 + kCoopWarps * 16 * 4 + 1024;
+};
+
+template <int D, int STAGES, bool CLUSTER>
+__global__ void __launch_bounds__((kCoopWarps + 1) * 32)
+attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                             TcParams tp) {
+  constexpr int KT = 32;
+  constexpr int NV = D / 8 / kCoopWarps;       // P.V n-tiles (8 dims each) per warp
+  using Layout = CoopSmem<D, STAGES>;
+  const PagedAttentionParams& p = tp.p;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* smax = reinterpret_cast<float*>(smem + STAGES * Layout::kStage);                  // [2][warps][16]
+  __nv_bfloat16* ptile = reinterpret_cast<__nv_bfloat16*>(smax + 2 * kCoopWarps * 16);     // [2][16][kPRow]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Layout::kStage + Layout::kExchange);
+  uint64_t* empty = full + STAGES;
+  float* lpart = reinterpret_cast<float*>(empty + STAGES);                                 // [warps][16] row sums
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool is_producer = warp == kCoopWarps;
+  const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
+  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+
+  pdl_launch_dependents();
+  const int seq = p.tile_seq[tile];
+  const int q0 = p.tile_q0[tile];
+  const int nq = p.tile_nq[tile];
+  if (nq <= 0) return;     // padding of a captured layout; the whole cluster sees the same tile
+  const int ctx = p.ctx_lens[seq];
+  const int seq_q0 = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - seq_q0;
+  const int pos = ctx - q_len + (q0 - seq_q0);
+
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  lo = lo / tp.box_rows * tp.box_rows;
+  const int hi = pos + 1;
+  int range_lo = lo, range_hi = hi;
+  if (p.num_splits > 1) {
+    int per = (hi - lo + p.num_splits - 1) / p.num_splits;
+    per = (per + KT - 1) / KT * KT;
+    range_lo = lo + split * per;
+    range_hi = min(hi, range_lo + per);
+  }
+  const int num_blocks = range_hi > range_lo ? (range_hi - range_lo + KT - 1) / KT : 0;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], tp.use_tma ? 1 : 32);
+      mbar_init(&empty[s], kCoopWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();      // q and this step's K/V pages come from the previous kernels
+
+  bool ok = true;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  float o[NV][4];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
+
+  if (is_producer) {
+    TableWindow window{p.block_table + (int64_t)seq * p.table_width, p.table_width, -1, -1};
+    for (int b = 0; b < num_blocks; ++b) {
+      const int s = b % STAGES;
+      if (b >= STAGES && !mbar_wait(&empty[s], ((b / STAGES) - 1) & 1)) {
+        ok = false;
+        break;
+      }
+      if (tp.use_tma)
+        issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage,
+                           &full[s], 0, 1);
+      else
+        issue_block_cp<D, KT>(tp, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage, &full[s]);
+    }
+  } else {
+    // query fragments: rows are the heads of the group (row < G), all D/16 k-steps
+    const int row_a = lane >> 2, row_b = row_a + 8;
+    uint32_t q_frag[D / 16][4];
+    {
+      const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+#pragma unroll
+      for (int t = 0; t < D / 16; ++t) {
+        const int col = t * 16 + (lane & 3) * 2;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int row = r ? row_b : row_a;
+          uint32_t lo_pair = 0, hi_pair = 0;
+          if (row < G) {
+            const __nv_bfloat16* src = q + ((int64_t)q0 * NH + kvh * G + row) * D + col;
+            lo_pair = *reinterpret_cast<const uint32_t*>(src);
+            hi_pair = *reinterpret_cast<const uint32_t*>(src + 8);
+          }
+          q_frag[t][r] = lo_pair;
+          q_frag[t][2 + r] = hi_pair;
+        }
+      }
+    }
+    const float scale_log2 = p.scale * kLog2e;
+    const bool live[2] = {row_a < G, row_b < G};
+
+    for (int b = 0; b < num_blocks; ++b) {
+      const int s = b % STAGES;
+      uint8_t* stage = smem + s * Layout::kStage;
+      const uint32_t k_base = smem_addr(stage), v_base = smem_addr(stage + KT * D * 2);
+      float* my_max = smax + (b & 1) * kCoopWarps * 16;
+      __nv_bfloat16* my_p = ptile + (b & 1) * 16 * kPRow;
+      if (ok && !mbar_wait(&full[s], (b / STAGES) & 1)) ok = false;
+      const int key0 = range_lo + b * KT;
+      const int nvalid = min(KT, range_hi - key0);
+      if (nvalid < KT) zero_v_rows<D, KT>(stage, nvalid, tid, kCoopWarps * 32);   // made visible by the barriers below
+
+      // scores of this warp's 8 keys
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (ok && warp * 8 < nvalid) {
+#pragma unroll
+        for (int t = 0; t < D / 16; t += 2) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(k_base + tile_offset_d<D, KT>(warp * 8 + (lane & 7), 2 * t + (lane >> 3)), b0, b1, b2, b3);
+          mma_bf16(sc, q_frag[t], b0, b1);
+          mma_bf16(sc, q_frag[t + 1], b2, b3);
+        }
+      }
+      float bmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int in_block = warp * 8 + (lane & 3) * 2 + (e & 1);
+        const int key = key0 + in_block;
+        const bool visible = ok && live[r] && in_block < nvalid && key <= pos &&
+                             (p.window <= 0 || key > pos - p.window);
+        sc[e] = visible ? sc[e] * scale_log2 : -CUDART_INF_F;
+        bmax[r] = fmaxf(bmax[r], sc[e]);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        bmax[r] = fmaxf(bmax[r], __shfl_xor_sync(0xffffffffu, bmax[r], 1));
+        bmax[r] = fmaxf(bmax[r], __shfl_xor_sync(0xffffffffu, bmax[r], 2));
+      }
+      if ((lane & 3) == 0) {
+        my_max[warp * 16 + row_a] = bmax[0];
+        my_max[warp * 16 + row_b] = bmax[1];
+      }
+      consumer_sync(kCoopWarps);
+      float alpha[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = r ? row_b : row_a;
+        float mx = m[r];
+#pragma unroll
+        for (int w = 0; w < kCoopWarps; ++w) mx = fmaxf(mx, my_max[w * 16 + row]);
+        alpha[r] = (mx == -CUDART_INF_F) ? 1.f : exp2f(m[r] - mx);
+        m[r] = mx;
+        l[r] *= alpha[r];
+      }
+      float pr[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        pr[e] = (sc[e] == -CUDART_INF_F) ? 0.f : exp2f(sc[e] - m[r]);
+        l[r] += pr[e];
+      }
+      {
+        const int col = warp * 8 + (lane & 3) * 2;
+        *reinterpret_cast<uint32_t*>(my_p + row_a * kPRow + col) = pack_bf16(pr[0], pr[1]);
+        *reinterpret_cast<uint32_t*>(my_p + row_b * kPRow + col) = pack_bf16(pr[2], pr[3]);
+      }
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        o[v][0] *= alpha[0];
+        o[v][1] *= alpha[0];
+        o[v][2] *= alpha[1];
+        o[v][3] *= alpha[1];
+      }
+      consumer_sync(kCoopWarps);
+      // O[:, this warp's dims] += P V
+      if (ok) {
+#pragma unroll
+        for (int u = 0; u < KT / 16; ++u) {
+          if (u * 16 < nvalid) {
+            uint32_t a[4];
+            // A fragment of P: rows (lane & 15), 16-byte column chunk (lane >> 4) of the 16 keys of group u
+            ldmatrix_x4(smem_addr(my_p + (lane & 15) * kPRow + u * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int v = 0; v < NV; v += 2) {
+              uint32_t b0, b1, b2, b3;
+              const int key = u * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+              const int chunk = warp * NV + v + (lane >> 4);
+              ldmatrix_x4_trans(v_base + tile_offset_d<D, KT>(key, chunk), b0, b1, b2, b3);
+              mma_bf16(o[v], a, b0, b1);
+              if (v + 1 < NV) mma_bf16(o[v + 1], a, b2, b3);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    if ((lane & 3) == 0) {
+      lpart[warp * 16 + row_a] = ok ? l[0] : 0.f;     // each warp summed the probabilities of its own keys
+      lpart[warp * 16 + row_b] = ok ? l[1] : 0.f;
+    }
+  }
+  if (!ok && lane == 0) set_status(p.status, kWaitTimeout);
+
+  // the CTA's (acc, max, sum) for its rows, in the (idle) stage ring: every warp owns its own head dims
+  __syncthreads();
+  float* merge = reinterpret_cast<float*>(smem);
+  constexpr int kRow = D + 2;
+  if (!is_producer) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = (lane >> 2) + 8 * r;
+      if (row < G) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int col = (warp * NV + v) * 8 + (lane & 3) * 2;
+          merge[row * kRow + col] = ok ? o[v][2 * r] : 0.f;
+          merge[row * kRow + col + 1] = ok ? o[v][2 * r + 1] : 0.f;
+        }
+        if (warp == 0 && (lane & 3) == 0) {
+          merge[row * kRow + D] = m[r];          // log2 units; the same in every warp
+          merge[row * kRow + D + 1] = (lpart[row] + lpart[16 + row]) + (lpart[32 + row] + lpart[48 + row]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (CLUSTER) {
+    cluster_sync_all();
+    for (int row = split; row < G; row += p.num_splits) {
+      const uint32_t base = smem_addr(merge) + (uint32_t)(row * kRow) * 4u;
+      float mx = -CUDART_INF_F;
+      for (int s = 0; s < p.num_splits; ++s)
+        if (ld_peer_smem(base + (D + 1) * 4u, s) > 0.f) mx = fmaxf(mx, ld_peer_smem(base + D * 4u, s));
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D;
+      for (int d = tid; d < D; d += blockDim.x) {
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < p.num_splits; ++s) {
+          const float ls = ld_peer_smem(base + (D + 1) * 4u, s);
+          if (ls > 0.f) {
+            const float w = exp2f(ld_peer_smem(base + D * 4u, s) - mx);
+            num += w * ld_peer_smem(base + d * 4u, s);
+            den += w * ls;
+          }
+        }
+        out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      }
+    }
+    cluster_sync_all();
+    return;
+  }
+  for (int idx = tid; idx < G * D; idx += blockDim.x) {
+    const int row = idx / D, d = idx - row * D;
+    const int64_t out_row = (int64_t)q0 * NH + kvh * G + row;
+    const float sum = merge[row * kRow + D + 1];
+    if (p.num_splits == 1) {
+      ((__nv_bfloat16*)p.out)[out_row * D + d] = __float2bfloat16_rn(sum > 0.f ? merge[row * kRow + d] / sum : 0.f);
+    } else {
+      float* part = p.partials + (out_row * p.num_splits + split) * (int64_t)kRow;
+      part[d] = merge[row * kRow + d];
+      if (d == 0) {
+        part[D] = merge[row * kRow + D] * kLn2;
+        part[D + 1] = sum;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -620,6 +969,8 @@ bool cache_map(const void* base, int64_t rows, int head_dim, int box_rows, CUten
 }
 
 constexpr int kDecodeConsumers = 4;
+constexpr int kMinTmaRows = 8;     // pages of at least this many tokens are fetched as TMA boxes (all of them; the
+                                   // cp.async path is kept for measurements: one warp cannot keep enough copies in flight)
 
 template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
 int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
@@ -633,7 +984,7 @@ int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_
     configured = true;
   }
   const int G = p.num_heads / p.num_kv_heads;
-  TcParams tp{p, box_rows};
+  TcParams tp{p, box_rows, box_rows >= kMinTmaRows ? 1 : 0};
   const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
   const dim3 block(32 * ((DECODE ? kDecodeConsumers : G) + kProducers));      // consumer and producer warps
   const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
@@ -655,6 +1006,23 @@ bool attention_tc_supported(const PagedAttentionParams& p) {
   return encode_fn() != nullptr;
 }
 
+template <int D, int STAGES, bool CLUSTER>
+int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
+                cudaStream_t stream) {
+  auto kernel = attention_decode_coop_kernel<D, STAGES, CLUSTER>;
+  constexpr int smem = CoopSmem<D, STAGES>::kBytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  TcParams tp{p, box_rows, box_rows >= kMinTmaRows ? 1 : 0};
+  const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, (unsigned)p.num_splits);
+  const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
+  return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
+}
+
 // Decode with 2, 4 or 8 key splits merges them inside the kernel (a cluster per token and kv head).
 bool attention_tc_merges_in_kernel(const PagedAttentionParams& p) {
   return p.q_tile == 1 && (p.num_splits == 2 || p.num_splits == 4 || p.num_splits == 8);
@@ -671,11 +1039,11 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
     return (int)cudaErrorInvalidValue;
   if (decode) {
     if (attention_tc_merges_in_kernel(p)) {
-      if (p.head_dim == 128) return launch_tc<128, 32, 6, true, true>(p, box_rows, k_map, v_map, stream);
-      return launch_tc<64, 32, 6, true, true>(p, box_rows, k_map, v_map, stream);
+      if (p.head_dim == 128) return launch_coop<128, 6, true>(p, box_rows, k_map, v_map, stream);
+      return launch_coop<64, 6, true>(p, box_rows, k_map, v_map, stream);
     }
-    if (p.head_dim == 128) return launch_tc<128, 32, 6, true, false>(p, box_rows, k_map, v_map, stream);
-    return launch_tc<64, 32, 6, true, false>(p, box_rows, k_map, v_map, stream);
+    if (p.head_dim == 128) return launch_coop<128, 6, false>(p, box_rows, k_map, v_map, stream);
+    return launch_coop<64, 6, false>(p, box_rows, k_map, v_map, stream);
   }
   if (p.head_dim == 128) return launch_tc<128, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
   return launch_tc<64, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);

@@ -22,6 +22,7 @@
 #include "launchers.h"
 
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <map>
 #include <mutex>
@@ -33,7 +34,6 @@ namespace {
 
 constexpr int kTileM = 128;      // features per CTA
 constexpr int kTileK = 64;       // K elements per stage: 128 bytes, one swizzle row
-constexpr int kStages = 4;
 constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -118,7 +118,7 @@ struct GemmParams {
   int* status;
 };
 
-template <int BN>
+template <int BN, int kStages>
 struct GemmSmem {
   static constexpr int kA = kTileM * kTileK * 2;
   static constexpr int kB = BN * kTileK * 2;
@@ -141,13 +141,13 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, int kStages>
 __global__ void __launch_bounds__(192)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                     GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * GemmSmem<BN>::kStage);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * GemmSmem<BN, kStages>::kStage);
   uint64_t* empty = full + kStages;
   uint64_t* acc_ready = empty + kStages;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
@@ -187,12 +187,12 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // for that kernel and fetch the activations.
       const int ahead = min(num_kb, kStages);
       for (int kb = 0; kb < ahead; ++kb) {
-        mbar_expect_tx(&full[kb], GemmSmem<BN>::kStage);
-        tma_load_2d(smem + kb * GemmSmem<BN>::kStage, &w_map, (kb_begin + kb) * kTileK, tile * kTileM, &full[kb]);
+        mbar_expect_tx(&full[kb], GemmSmem<BN, kStages>::kStage);
+        tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage, &w_map, (kb_begin + kb) * kTileK, tile * kTileM, &full[kb]);
       }
       pdl_wait();
       for (int kb = 0; kb < ahead; ++kb)
-        tma_load_2d(smem + kb * GemmSmem<BN>::kStage + GemmSmem<BN>::kA, &x_map, (kb_begin + kb) * kTileK, 0,
+        tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA, &x_map, (kb_begin + kb) * kTileK, 0,
                     &full[kb]);
       for (int kb = ahead; kb < num_kb; ++kb) {
         const int s = kb % kStages;
@@ -200,11 +200,11 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           ok = false;
           break;
         }
-        uint8_t* stage = smem + s * GemmSmem<BN>::kStage;
-        mbar_expect_tx(&full[s], GemmSmem<BN>::kStage);
+        uint8_t* stage = smem + s * GemmSmem<BN, kStages>::kStage;
+        mbar_expect_tx(&full[s], GemmSmem<BN, kStages>::kStage);
         const int k0 = (kb_begin + kb) * kTileK;
         tma_load_2d(stage, &w_map, k0, tile * kTileM, &full[s]);
-        tma_load_2d(stage + GemmSmem<BN>::kA, &x_map, k0, 0, &full[s]);
+        tma_load_2d(stage + GemmSmem<BN, kStages>::kA, &x_map, k0, 0, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -217,8 +217,8 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + s * GemmSmem<BN>::kStage);
-        const uint32_t b_addr = a_addr + GemmSmem<BN>::kA;
+        const uint32_t a_addr = smem_u32(smem + s * GemmSmem<BN, kStages>::kStage);
+        const uint32_t b_addr = a_addr + GemmSmem<BN, kStages>::kA;
 #pragma unroll
         for (int k = 0; k < kTileK / 16; ++k) {
           // 16 K-elements = 32 bytes further along the swizzled row
@@ -331,18 +331,38 @@ bool matrix_map(const void* base, int64_t rows, int64_t cols, int box_rows, CUte
   return true;
 }
 
-template <int BN, typename OutT>
-int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = small_m_gemm_kernel<BN, OutT>;
+template <int BN, typename OutT, int kStages>
+int launch_stages(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = small_m_gemm_kernel<BN, OutT, kStages>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kBytes);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, kStages>::kBytes);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
   const dim3 grid((unsigned)((p.features + kTileM - 1) / kTileM), (unsigned)p.splits);
   const dim3 cluster(1, p.out != nullptr ? (unsigned)p.splits : 1u, 1);   // the splits of a tile form the cluster
-  return (int)launch_chain(kernel, grid, dim3(192), GemmSmem<BN>::kBytes, stream, cluster, w_map, x_map, p);
+  return (int)launch_chain(kernel, grid, dim3(192), GemmSmem<BN, kStages>::kBytes, stream, cluster, w_map, x_map, p);
+}
+
+// Stages of the TMA ring.  Four stages of 18-24 KB let three (two at 64 tokens) CTAs share an SM.
+// AKV_GEMM_STAGES=2|4|8 in the environment overrides it (for measurements).
+int ring_stages() {
+  static const int stages = [] {
+    const char* v = getenv("AKV_GEMM_STAGES");
+    const int n = v ? atoi(v) : 4;
+    return (n == 2 || n == 8) ? n : 4;
+  }();
+  return stages;
+}
+
+template <int BN, typename OutT>
+int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
+  switch (ring_stages()) {
+    case 2: return launch_stages<BN, OutT, 2>(w_map, x_map, p, stream);
+    case 8: return launch_stages<BN, OutT, 8>(w_map, x_map, p, stream);
+    default: return launch_stages<BN, OutT, 4>(w_map, x_map, p, stream);
+  }
 }
 
 template <typename OutT>
