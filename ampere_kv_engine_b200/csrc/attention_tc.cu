@@ -22,6 +22,7 @@
 
 #include <cuda.h>
 #include <math_constants.h>
+#include <stdlib.h>
 
 #include <map>
 #include <mutex>
@@ -636,10 +637,10 @@ __global__ void __launch_bounds__(32 * (8 + kProducers)) attention_tc_kernel(con
 // (Q K^T, one 16 x 8 tile over all of D), the warps exchange their row maxima and their probabilities through
 // shared memory, then warp w accumulates P V for head dims [w D/4, (w + 1) D/4).  The MMA rows are the G q-heads
 // of the group, as before; 2, 4 or 8 key splits form a cluster and are merged through distributed shared memory.
-constexpr int kCoopWarps = 4;
+constexpr int kMaxCoopWarps = 4;
 constexpr int kPRow = 40;      // bf16 elements per row of the probability tile: 32 keys + padding against bank conflicts
 
-template <int D, int STAGES>
+template <int D, int STAGES, int kCoopWarps>
 struct CoopSmem {
   static constexpr int KT = 32;
   static constexpr int kStage = 2 * KT * D * 2;
@@ -649,13 +650,14 @@ struct CoopSmem {
   static constexpr int kBytes = STAGES * kStage + kExchange + 2 * STAGES * 8 + kCoopWarps * 16 * 4 + 1024;
 };
 
-template <int D, int STAGES, bool CLUSTER>
+template <int D, int STAGES, bool CLUSTER, int kCoopWarps>
 __global__ void __launch_bounds__((kCoopWarps + 1) * 32)
 attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              TcParams tp) {
   constexpr int KT = 32;
   constexpr int NV = D / 8 / kCoopWarps;       // P.V n-tiles (8 dims each) per warp
-  using Layout = CoopSmem<D, STAGES>;
+  using Layout = CoopSmem<D, STAGES, kCoopWarps>;
+  constexpr int NQ = KT / 8 / kCoopWarps;      // score n-tiles (8 keys each) per warp
   const PagedAttentionParams& p = tp.p;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -759,27 +761,36 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
       const int nvalid = min(KT, range_hi - key0);
       if (nvalid < KT) zero_v_rows<D, KT>(stage, nvalid, tid, kCoopWarps * 32);   // made visible by the barriers below
 
-      // scores of this warp's 8 keys
-      float sc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (ok && warp * 8 < nvalid) {
+      // scores of this warp's keys: NQ tiles of 8
+      float sc[NQ][4];
 #pragma unroll
-        for (int t = 0; t < D / 16; t += 2) {
-          uint32_t b0, b1, b2, b3;
-          ldmatrix_x4(k_base + tile_offset_d<D, KT>(warp * 8 + (lane & 7), 2 * t + (lane >> 3)), b0, b1, b2, b3);
-          mma_bf16(sc, q_frag[t], b0, b1);
-          mma_bf16(sc, q_frag[t + 1], b2, b3);
+      for (int j = 0; j < NQ; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        const int first = (warp * NQ + j) * 8;
+        if (ok && first < nvalid) {
+#pragma unroll
+          for (int t = 0; t < D / 16; t += 2) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(k_base + tile_offset_d<D, KT>(first + (lane & 7), 2 * t + (lane >> 3)), b0, b1, b2, b3);
+            mma_bf16(sc[j], q_frag[t], b0, b1);
+            mma_bf16(sc[j], q_frag[t + 1], b2, b3);
+          }
         }
       }
       float bmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        const int in_block = warp * 8 + (lane & 3) * 2 + (e & 1);
-        const int key = key0 + in_block;
-        const bool visible = ok && live[r] && in_block < nvalid && key <= pos &&
-                             (p.window <= 0 || key > pos - p.window);
-        sc[e] = visible ? sc[e] * scale_log2 : -CUDART_INF_F;
-        bmax[r] = fmaxf(bmax[r], sc[e]);
+      for (int j = 0; j < NQ; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int in_block = (warp * NQ + j) * 8 + (lane & 3) * 2 + (e & 1);
+          const int key = key0 + in_block;
+          const bool visible = ok && live[r] && in_block < nvalid && key <= pos &&
+                               (p.window <= 0 || key > pos - p.window);
+          sc[j][e] = visible ? sc[j][e] * scale_log2 : -CUDART_INF_F;
+          bmax[r] = fmaxf(bmax[r], sc[j][e]);
+        }
       }
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
@@ -802,15 +813,16 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
         m[r] = mx;
         l[r] *= alpha[r];
       }
-      float pr[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        pr[e] = (sc[e] == -CUDART_INF_F) ? 0.f : exp2f(sc[e] - m[r]);
-        l[r] += pr[e];
-      }
-      {
-        const int col = warp * 8 + (lane & 3) * 2;
+      for (int j = 0; j < NQ; ++j) {
+        float pr[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          pr[e] = (sc[j][e] == -CUDART_INF_F) ? 0.f : exp2f(sc[j][e] - m[r]);
+          l[r] += pr[e];
+        }
+        const int col = (warp * NQ + j) * 8 + (lane & 3) * 2;
         *reinterpret_cast<uint32_t*>(my_p + row_a * kPRow + col) = pack_bf16(pr[0], pr[1]);
         *reinterpret_cast<uint32_t*>(my_p + row_b * kPRow + col) = pack_bf16(pr[2], pr[3]);
       }
@@ -874,7 +886,10 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
         }
         if (warp == 0 && (lane & 3) == 0) {
           merge[row * kRow + D] = m[r];          // log2 units; the same in every warp
-          merge[row * kRow + D + 1] = (lpart[row] + lpart[16 + row]) + (lpart[32 + row] + lpart[48 + row]);
+          float total = 0.f;
+#pragma unroll
+          for (int w = 0; w < kCoopWarps; ++w) total += lpart[w * 16 + row];     // fixed order
+          merge[row * kRow + D + 1] = total;
         }
       }
     }
@@ -1006,11 +1021,11 @@ bool attention_tc_supported(const PagedAttentionParams& p) {
   return encode_fn() != nullptr;
 }
 
-template <int D, int STAGES, bool CLUSTER>
+template <int D, int STAGES, bool CLUSTER, int kCoopWarps>
 int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
                 cudaStream_t stream) {
-  auto kernel = attention_decode_coop_kernel<D, STAGES, CLUSTER>;
-  constexpr int smem = CoopSmem<D, STAGES>::kBytes;
+  auto kernel = attention_decode_coop_kernel<D, STAGES, CLUSTER, kCoopWarps>;
+  constexpr int smem = CoopSmem<D, STAGES, kCoopWarps>::kBytes;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1021,6 +1036,21 @@ int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& 
   const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, (unsigned)p.num_splits);
   const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
   return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
+}
+
+// Shape of the decode kernel's CTAs: (TMA ring stages of 16 KB at head size 128, consumer warps).  One CTA
+// streams pages at 13-15 GB/s whatever its ring depth (measured on B200), so bandwidth comes from CTAs per SM.
+// Few CTAs in flight (small batches): 2 stages x 2 warps, the smallest CTA, which also shares an SM best with the
+// next kernel's early CTAs; enough CTAs to fill the GPU: 3 stages x 4 warps.  Measured: batch 8 step 3.73 ms vs
+// 3.94 ms, batch 64 kernel 59.7 us vs 64.9 us.  AKV_ATTN_CONFIG=2|3|4|6 forces (2,2) | (3,4) | (2,4) | (3,2).
+int decode_config(int64_t ctas) {
+  static const int forced = [] {
+    const char* v = getenv("AKV_ATTN_CONFIG");
+    const int n = v ? atoi(v) : 0;
+    return (n == 2 || n == 3 || n == 4 || n == 6) ? n : 0;
+  }();
+  if (forced) return forced;
+  return ctas >= 148 * 4 ? 3 : 2;
 }
 
 // Decode with 2, 4 or 8 key splits merges them inside the kernel (a cluster per token and kv head).
@@ -1038,12 +1068,20 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
       !cache_map(p.v_cache, rows, p.head_dim, box_rows, &v_map))
     return (int)cudaErrorInvalidValue;
   if (decode) {
-    if (attention_tc_merges_in_kernel(p)) {
-      if (p.head_dim == 128) return launch_coop<128, 6, true>(p, box_rows, k_map, v_map, stream);
-      return launch_coop<64, 6, true>(p, box_rows, k_map, v_map, stream);
+    const bool merge = attention_tc_merges_in_kernel(p);
+#define AKV_COOP(ST, W)                                                                                       \
+  if (p.head_dim == 128)                                                                                      \
+    return merge ? launch_coop<128, ST, true, W>(p, box_rows, k_map, v_map, stream)                           \
+                 : launch_coop<128, ST, false, W>(p, box_rows, k_map, v_map, stream);                         \
+  return merge ? launch_coop<64, ST, true, W>(p, box_rows, k_map, v_map, stream)                              \
+               : launch_coop<64, ST, false, W>(p, box_rows, k_map, v_map, stream);
+    switch (decode_config((int64_t)p.num_tiles * p.num_kv_heads * p.num_splits)) {
+      case 2: AKV_COOP(2, 2)
+      case 4: AKV_COOP(2, 4)
+      case 6: AKV_COOP(3, 2)
+      default: AKV_COOP(3, 4)
     }
-    if (p.head_dim == 128) return launch_coop<128, 6, false>(p, box_rows, k_map, v_map, stream);
-    return launch_coop<64, 6, false>(p, box_rows, k_map, v_map, stream);
+#undef AKV_COOP
   }
   if (p.head_dim == 128) return launch_tc<128, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
   return launch_tc<64, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);

@@ -109,20 +109,21 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
                   tensor_core: bool = False) -> int:
     """How many key ranges each decoded token's attention is cut into so that a small batch still fills the GPU.
 
-    The tensor-core decode kernel runs one CTA per (token, kv head, split), two to an SM; the general kernel
+    The tensor-core decode kernel runs one CTA per (token, kv head, split), four to an SM; the general kernel
     one warp per (token, kv head, 8 rows, split), sixteen to an SM.
     """
     if tensor_core:
         # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  Cost model: rounds of CTAs over the
-        # GPU's 148 x 2 slots; a CTA's four consumer warps walk its share of 32-key blocks four at a time, plus a
-        # fixed start-up and merge worth about three blocks.
-        items, slots = max(1, num_tiles * num_kv_heads), 148 * 2
+        # GPU's 148 x 4 slots, each CTA walking its share of 32-key blocks plus a fixed start-up and merge worth
+        # about three blocks (measured on B200: batch 8 at 1,152 keys 15 us with 8 splits, 19 us with 4;
+        # batch 64: 60 us with 1 split, 67 us with 2).
+        items, slots = max(1, num_tiles * num_kv_heads), 148 * 4
         blocks = (max_context + 31) // 32
         best, best_cost = 1, None
         for s in (1, 2, 4, 8):
-            if s > 1 and blocks // s < 4:
+            if s > 1 and blocks // s < 2:
                 break
-            cost = -(-items * s // slots) * (-(-blocks // (4 * s)) + 3)
+            cost = -(-items * s // slots) * (-(-blocks // s) + 3)
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
