@@ -382,8 +382,8 @@ constexpr int kProducers = 1;
 // keep the TMA ring full.  full[s]: the stage's bytes have landed; empty[s]: every consumer warp is done with the stage.
 // CLUSTER (decode only): the key splits of one (token, kv head) form a cluster; the partial results are merged
 // through distributed shared memory instead of a second kernel.
-template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
-__global__ void __launch_bounds__(32 * (8 + kProducers)) attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
+template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER, int WARPS, int MIN_CTAS>
+__global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                                     const __grid_constant__ CUtensorMap v_map, TcParams tp) {
   const PagedAttentionParams& p = tp.p;
   extern __shared__ uint8_t smem_raw[];
@@ -397,11 +397,12 @@ __global__ void __launch_bounds__(32 * (8 + kProducers)) attention_tc_kernel(con
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
 
   pdl_launch_dependents();
-  const int seq = p.tile_seq[tile];
-  const int q0 = p.tile_q0[tile];
-  const int nq = p.tile_nq[tile];
-  // A tile of no rows (padding of a captured layout) does nothing; with clusters every CTA of the cluster sees
-  // the same tile, so they all leave together.
+  // a batch tile holds up to q_tile tokens; this kernel's CTAs take 16 of them each
+  const int subtiles = (p.q_tile + 15) / 16;
+  const int batch_tile = tile / subtiles, sub = tile - batch_tile * subtiles;
+  const int seq = p.tile_seq[batch_tile];
+  const int q0 = p.tile_q0[batch_tile] + 16 * sub;
+  const int nq = min(16, p.tile_nq[batch_tile] - 16 * sub);
   if (nq <= 0) return;
   const int ctx = p.ctx_lens[seq];
   const int seq_q0 = p.cu_q[seq];
@@ -987,10 +988,10 @@ constexpr int kDecodeConsumers = 4;
 constexpr int kMinTmaRows = 8;     // pages of at least this many tokens are fetched as TMA boxes (all of them; the
                                    // cp.async path is kept for measurements: one warp cannot keep enough copies in flight)
 
-template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER>
-int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
-              cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<D, KT, STAGES, DECODE, CLUSTER>;
+template <int D, int KT, int STAGES, int WARPS, int MIN_CTAS>
+int launch_prompt(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
+                  cudaStream_t stream) {
+  auto kernel = attention_tc_kernel<D, KT, STAGES, false, false, WARPS, MIN_CTAS>;
   constexpr int smem = Smem<D, KT, STAGES>::kBytes;
   static bool configured = false;
   if (!configured) {
@@ -1000,25 +1001,9 @@ int launch_tc(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_
   }
   const int G = p.num_heads / p.num_kv_heads;
   TcParams tp{p, box_rows, box_rows >= kMinTmaRows ? 1 : 0};
-  const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, DECODE ? (unsigned)p.num_splits : 1u);
-  const dim3 block(32 * ((DECODE ? kDecodeConsumers : G) + kProducers));      // consumer and producer warps
-  const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
-  return (int)launch_chain(kernel, grid, block, smem, stream, cluster, k_map, v_map, tp);
-}
-
-}  // namespace
-
-// Whether the tensor-core kernels take this problem; otherwise the caller uses the general kernel.
-bool attention_tc_supported(const PagedAttentionParams& p) {
-  if (p.dtype != kBFloat16) return false;
-  if (p.head_dim != 64 && p.head_dim != 128) return false;
-  const int G = p.num_heads / p.num_kv_heads;
-  if (p.num_heads % p.num_kv_heads || G < 1 || G > 16) return false;
-  if (p.page_size < 8 || (p.page_size & (p.page_size - 1))) return false;   // boxes of 8.. rows, power of two
-  if (p.num_kv_heads > 65535 || p.num_splits > 65535) return false;
-  if (p.q_tile > 16) return false;
-  if (p.q_tile > 1 && G > 8) return false;    // prompt kernel: one warp per q-head of the group
-  return encode_fn() != nullptr;
+  const dim3 grid((unsigned)(p.num_tiles * ((p.q_tile + 15) / 16)), (unsigned)p.num_kv_heads, 1u);
+  const dim3 block(32 * (G + kProducers));      // one consumer warp per q-head of the group, and the producer
+  return (int)launch_chain(kernel, grid, block, smem, stream, dim3(1, 1, 1), k_map, v_map, tp);
 }
 
 template <int D, int STAGES, bool CLUSTER, int kCoopWarps>
@@ -1053,6 +1038,21 @@ int decode_config(int64_t ctas) {
   return ctas >= 148 * 4 ? 3 : 2;
 }
 
+}  // namespace
+
+// Whether the tensor-core kernels take this problem; otherwise the caller uses the general kernel.
+bool attention_tc_supported(const PagedAttentionParams& p) {
+  if (p.dtype != kBFloat16) return false;
+  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  const int G = p.num_heads / p.num_kv_heads;
+  if (p.num_heads % p.num_kv_heads || G < 1 || G > 16) return false;
+  if (p.page_size < 8 || (p.page_size & (p.page_size - 1))) return false;   // boxes of 8.. rows, power of two
+  if (p.num_kv_heads > 65535 || p.num_splits > 65535) return false;
+  if (p.q_tile > 128) return false;
+  if (p.q_tile > 1 && G > 8) return false;    // prompt kernel: one warp per q-head of the group
+  return encode_fn() != nullptr;
+}
+
 // Decode with 2, 4 or 8 key splits merges them inside the kernel (a cluster per token and kv head).
 bool attention_tc_merges_in_kernel(const PagedAttentionParams& p) {
   return p.q_tile == 1 && (p.num_splits == 2 || p.num_splits == 4 || p.num_splits == 8);
@@ -1060,7 +1060,10 @@ bool attention_tc_merges_in_kernel(const PagedAttentionParams& p) {
 
 int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
   const bool decode = p.q_tile == 1;
-  const int kt = decode ? 32 : 64;
+  const int G_all = p.num_heads / p.num_kv_heads;
+  const char* prompt_config = getenv("AKV_PROMPT_CONFIG");
+  const bool narrow_prompt = prompt_config != nullptr && atoi(prompt_config) == 32 && G_all <= 4 && p.page_size <= 32;
+  const int kt = (decode || narrow_prompt) ? 32 : 64;
   const int box_rows = p.page_size < kt ? p.page_size : kt;
   const int64_t rows = p.num_pages * p.num_kv_heads * (int64_t)p.page_size;
   CUtensorMap k_map, v_map;
@@ -1083,8 +1086,15 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
     }
 #undef AKV_COOP
   }
-  if (p.head_dim == 128) return launch_tc<128, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
-  return launch_tc<64, 64, 3, false, false>(p, box_rows, k_map, v_map, stream);
+  // Prompt tiles: 64-key blocks, three stages, two CTAs per SM.  A variant with 32-key blocks and three CTAs per SM
+  // (AKV_PROMPT_CONFIG=32, groups of up to four q-heads) measured the same on a 2,048-token prompt (294 vs 290 us)
+  // and worse on a 512-token portion after 7,680 keys (638 vs 510 us).
+  if (kt == 32) {
+    if (p.head_dim == 128) return launch_prompt<128, 32, 3, 4, 3>(p, box_rows, k_map, v_map, stream);
+    return launch_prompt<64, 32, 3, 4, 3>(p, box_rows, k_map, v_map, stream);
+  }
+  if (p.head_dim == 128) return launch_prompt<128, 64, 3, 8, 1>(p, box_rows, k_map, v_map, stream);
+  return launch_prompt<64, 64, 3, 8, 1>(p, box_rows, k_map, v_map, stream);
 }
 
 }  // namespace akv

@@ -13,8 +13,8 @@ import torch
 
 from . import build
 
-#: query rows of one sequence that one attention tile covers
-ATTENTION_Q_TILE = 16
+#: query tokens of one sequence that one attention tile covers (the kernels cut it further as they need)
+ATTENTION_Q_TILE = 32
 
 _EXT = None
 
