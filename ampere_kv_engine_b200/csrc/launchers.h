@@ -83,7 +83,7 @@ struct PagedAttentionParams {
   int num_heads, num_kv_heads, head_dim, page_size;
   int64_t num_pages;
   int window;                  // 0 = all keys
-  int kernel;                  // 0 = best kernel that takes the sizes, 1 = the general kernel
+  int kernel;                  // 0 = best kernel that takes the sizes, 1 = the general kernel, 2 = no tcgen05 prompt kernel
   float scale;
   int dtype;
   int* status;
@@ -93,6 +93,9 @@ int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream);
 bool attention_tc_supported(const PagedAttentionParams& p);
 int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream);
 bool attention_tc_merges_in_kernel(const PagedAttentionParams& p);
+// The tcgen05 prompt kernel (attention_tcgen05.cu): bfloat16, head size 128, groups of 2, 4 or 8 q-heads.
+bool attention_tcgen05_supported(const PagedAttentionParams& p);
+int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream);
 
 // tokens[r] = argmax(logits[r]) where temperature[r] == 0, else the inverse-CDF draw of
 // softmax(logits[r] / temperature[r]) at uniform[r].

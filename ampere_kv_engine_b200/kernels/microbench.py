@@ -92,8 +92,8 @@ def bench_attention(args, q_len: int, batch: int, context: int) -> dict:
                                                               args.head_dim, args.page_size, copies)
     group = args.heads // args.kv_heads
     out = {}
-    for kernel in ("auto", "general"):
-        tensor_core = kernel == "auto" and ops.attention_takes_tensor_cores(torch.bfloat16, args.head_dim, group,
+    for kernel in ("auto", "mma", "general"):
+        tensor_core = kernel != "general" and ops.attention_takes_tensor_cores(torch.bfloat16, args.head_dim, group,
                                                                             args.page_size)
         splits = args.splits or (1 if q_len > 1 and tensor_core else ops.choose_splits(
             len(tiles[0]), args.kv_heads, tile_rows * group, context, tensor_core))
@@ -105,6 +105,8 @@ def bench_attention(args, q_len: int, batch: int, context: int) -> dict:
                                        num_heads=args.heads, num_kv_heads=args.kv_heads, window=0,
                                        scale=args.head_dim ** -0.5, kernel=kernel)
         if kernel == "general" and q_len > 1 and not args.with_general:
+            continue
+        if kernel == "mma" and q_len == 1:
             continue
         us = timed(run, args.calls)
         out[f"{kernel}_us"] = us

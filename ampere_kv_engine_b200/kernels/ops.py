@@ -138,8 +138,9 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
                     q_tile, num_splits, num_heads, num_kv_heads, window, scale, partials=None, status=None,
                     kernel: str = "auto"):
     """Causal attention of the batch's new tokens over the paged cache.  ``kernel``: ``"auto"`` takes the
-    tensor-core kernels where they fit (bfloat16, head size 64 or 128) and the general kernel elsewhere;
-    ``"general"`` forces the latter."""
+    tensor-core kernels where they fit (bfloat16, head size 64 or 128; prompt portions at head size 128 and groups
+    of 2, 4 or 8 q-heads on tcgen05) and the general kernel elsewhere; ``"general"`` forces the latter, ``"mma"``
+    keeps prompt portions on the mma.sync kernel."""
     out = torch.empty_like(q)
     if num_splits > 1 and partials is None:
         head_dim = q.shape[1] // num_heads
@@ -147,7 +148,7 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
                                device=q.device)
     ext().paged_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
                           partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(window or 0),
-                          float(scale), status, {"auto": 0, "general": 1}[kernel])
+                          float(scale), status, {"auto": 0, "general": 1, "mma": 2}[kernel])
     _launched(2 if num_splits > 1 else 1)
     return out
 

@@ -190,13 +190,10 @@ class PagedCase:
         self.v_cache = self.k_cache.clone()
         width = max(pages_per_seq)
         self.table = torch.full((len(ctx_lens), width), -1, dtype=torch.int32)
-        for s, c in enumerate(ctx_lens):
+        for s in range(len(ctx_lens)):
             for lp in range(pages_per_seq[s]):
-                pp = order.pop()
-                self.table[s, lp] = pp
-                lo, hi = lp * page, min(c, (lp + 1) * page)
-                self.k_cache[pp, :, :hi - lo] = self.k_seq[s][lo:hi].transpose(0, 1)
-                self.v_cache[pp, :, :hi - lo] = self.v_seq[s][lo:hi].transpose(0, 1)
+                self.table[s, lp] = order.pop()
+        self.rewrite_cache()
         cu = [0]
         for n in q_lens:
             cu.append(cu[-1] + n)
@@ -205,6 +202,15 @@ class PagedCase:
         tiles = [(s, cu[s] + q0, min(tile_rows, n - q0)) for s, n in enumerate(q_lens) for q0 in range(0, n, tile_rows)]
         self.tile_rows = tile_rows
         self.tiles = [torch.tensor([t[i] for t in tiles], dtype=torch.int32) for i in range(3)]
+
+    def rewrite_cache(self):
+        """Copies k_seq / v_seq into the pages that the table names (again, after a test changed some keys)."""
+        for s, c in enumerate(self.ctx_lens):
+            for lp in range((c + self.page - 1) // self.page):
+                pp = int(self.table[s, lp])
+                lo, hi = lp * self.page, min(c, (lp + 1) * self.page)
+                self.k_cache[pp, :, :hi - lo] = self.k_seq[s][lo:hi].transpose(0, 1)
+                self.v_cache[pp, :, :hi - lo] = self.v_seq[s][lo:hi].transpose(0, 1)
 
     def run(self, ops, window=0, splits=1, scale=None, kernel="auto"):
         scale = scale if scale is not None else self.d ** -0.5
@@ -251,12 +257,51 @@ def test_tensor_core_and_general_kernels_agree(ops, nh, nkv, d, page, window):
                       seed=nh + page)
     want = mixed.reference(window)
     torch.testing.assert_close(mixed.run(ops, window, 1, kernel="auto"), want, **tol(dtype))
+    torch.testing.assert_close(mixed.run(ops, window, 1, kernel="mma"), want, **tol(dtype))
     torch.testing.assert_close(mixed.run(ops, window, 1, kernel="general"), want, **tol(dtype))
     decode = PagedCase(dtype, nh, nkv, d, page, q_lens=[1] * 6, ctx_lens=[1, 31, 32, 33, 700, 129], seed=nh)
     want = decode.reference(window)
     for splits in (1, 2, 7):
         torch.testing.assert_close(decode.run(ops, window, splits, kernel="auto"), want, **tol(dtype))
     torch.testing.assert_close(decode.run(ops, window, 3, kernel="general"), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,page,q_tile", [(32, 8, 16, 32), (16, 8, 32, 64), (8, 1, 64, 16), (32, 8, 16, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_tcgen05_prompt_attention(ops, nh, nkv, page, q_tile, window):
+    """Prompt portions at head size 128 with groups of 2, 4 and 8 q-heads run on the tcgen05 kernel: whole
+    prompts, portions after a long history, tiles that end mid-way, a portion of one token beside them."""
+    dtype = torch.bfloat16
+    case = PagedCase(dtype, nh, nkv, 128, page, q_lens=[300, 77, 33, 1, 128], ctx_lens=[300, 500, 33, 40, 128],
+                     seed=page + nh, q_tile=q_tile)
+    want = case.reference(window)
+    torch.testing.assert_close(case.run(ops, window, 1, kernel="auto"), want, **tol(dtype))
+    torch.testing.assert_close(case.run(ops, window, 1, kernel="mma"), want, **tol(dtype))
+
+
+def test_tcgen05_prompt_attention_repeats_and_rescales(ops):
+    """The tcgen05 kernel keeps a stale running maximum and rescales its accumulator only when a score exceeds it
+    by 2^8: keys of growing norm force that path in every block, a dominant key early and late in a long history
+    tests both sides of it, and repeated launches must agree bit for bit (its warps run at different speeds)."""
+    dtype = torch.bfloat16
+    case = PagedCase(dtype, 8, 2, 128, 16, q_lens=[96, 200, 40], ctx_lens=[900, 200, 1500], seed=77, q_tile=32)
+    # sequence 0: key norms grow along the sequence, so that later blocks keep raising the maximum
+    ramp = torch.linspace(0.2, 6.0, 900).view(900, 1, 1)
+    case.k_seq[0] = (case.k_seq[0].float() * ramp).to(dtype)
+    # sequence 2: one dominant key near the start and one near the end, seen by every query of the portion
+    for far, gain in ((5, 6.0), (1490, 9.0)):
+        for kv in range(2):
+            direction = torch.nn.functional.normalize(case.k_seq[2][far, kv].float(), dim=0)
+            case.k_seq[2][far, kv] = (gain * direction).to(dtype)
+            for h in range(4 * kv, 4 * kv + 4):
+                case.q_seq[2][:, h] = (case.q_seq[2][:, h].float() + 25.0 * direction).to(dtype)
+    case.rewrite_cache()
+    want = case.reference(0)
+    first = case.run(ops, 0, 1, kernel="auto")
+    torch.testing.assert_close(first, want, **tol(dtype))
+    for _ in range(8):
+        assert torch.equal(case.run(ops, 0, 1, kernel="auto"), first)
+    torch.testing.assert_close(case.run(ops, 0, 1, kernel="mma"), want, **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
