@@ -145,7 +145,7 @@ void add_rmsnorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, T
                "add_rmsnorm");
 }
 
-void silu_mul(const Tensor& gate_up, Tensor& out) {
+void silu_mul(const Tensor& gate_up, Tensor& out, int64_t block) {
   check_cuda(gate_up, "gate_up");
   check_cuda(out, "out");
   int parts = 0;
@@ -162,16 +162,20 @@ void silu_mul(const Tensor& gate_up, Tensor& out) {
   AKV_CHECK(first.dim() == 2 && first.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
   const int64_t n = first.size(0), inter = first.size(1) / 2;
   AKV_CHECK(out.numel() == n * inter, "out must be [tokens, intermediate]");
+  if (block == 0) block = inter;
+  AKV_CHECK(inter == 0 || (block > 0 && inter % block == 0),
+            "the run length of gate and up columns must divide the intermediate size, got ", block, " for ", inter);
   c10::cuda::CUDAGuard guard(gate_up.device());
-  check_launch(akv::launch_silu_mul(gate_up.data_ptr(), parts, out.data_ptr(), n, inter, dtype_code(out, "out"),
-                                    stream_of(out)),
+  check_launch(akv::launch_silu_mul(gate_up.data_ptr(), parts, out.data_ptr(), n, inter, block,
+                                    dtype_code(out, "out"), stream_of(out)),
                "silu_mul");
 }
 
 // x @ w^T for few tokens on the tcgen05 tensor cores.  `out` is either [tokens, features] (float32 or bfloat16:
 // the K splits are added up inside the kernel) or a 3-D float32 [splits, tokens, features] that receives every
 // split's partial sum as it is.
-void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits, const OptTensor& status) {
+void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits, const OptTensor& status,
+                  bool gated) {
   check_cuda(x, "x");
   check_cuda(w, "w");
   check_cuda(out, "out");
@@ -192,8 +196,18 @@ void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits,
     splits = out.size(0);
     AKV_CHECK(splits >= 1 && splits <= kb_total, "splits must be between 1 and the number of 64-element K blocks");
     parts_ptr = out.data_ptr<float>();
+    AKV_CHECK(!gated, "the gated epilogue writes a 2-D bfloat16 out");
   } else {
-    AKV_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == w.size(0), "out must be [tokens, features]");
+    if (gated) {
+      AKV_CHECK(w.size(0) % 128 == 0 && out.scalar_type() == at::kBFloat16,
+                "the gated epilogue takes a weight of gate and up rows in alternating runs of 64 (rows a multiple "
+                "of 128) and a bfloat16 out");
+      AKV_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) * 2 == w.size(0),
+                "a gated out must be [tokens, features / 2]");
+    } else {
+      AKV_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == w.size(0),
+                "out must be [tokens, features]");
+    }
     AKV_CHECK((splits == 1 || splits == 2 || splits == 4 || splits == 8) && splits <= kb_total,
               "splits must be 1, 2, 4 or 8 and at most the number of 64-element K blocks, got ", splits);
     out_code = dtype_code(out, "out");
@@ -201,7 +215,8 @@ void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits,
   }
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(akv::launch_small_m_gemm(x.data_ptr(), w.data_ptr(), out_ptr, out_code, parts_ptr, x.size(0), w.size(0),
-                                        x.size(1), (int)splits, status_ptr(status), stream_of(x)),
+                                        x.size(1), (int)splits, gated ? akv::kEpilogueGated : akv::kEpiloguePlain,
+                                        status_ptr(status), stream_of(x)),
                "small_m_gemm");
 }
 
@@ -404,9 +419,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("hidden"), py::arg("status") = py::none());
   m.def("add_rmsnorm", &add_rmsnorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
         py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
-  m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"));
+  m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"), py::arg("block") = 0);
   m.def("small_m_gemm", &small_m_gemm, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("splits") = 1,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("gated") = false);
   m.def("small_m_gemm_supported", &small_m_gemm_supported);
   m.def("small_m_gemm_splits", &small_m_gemm_splits);
   m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),

@@ -268,23 +268,25 @@ int launch_add_rmsnorm(float* hidden, const void* delta, int delta_parts, const 
 // any size, optional float32 partial sums.
 template <typename T, typename TI, bool PARTS>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int num_parts, T* __restrict__ out, int64_t inter,
-                                int64_t total, int64_t part_stride) {
+                                int64_t total, int64_t part_stride, int64_t block) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t token = idx / inter, i = idx - token * inter;
   const TI* row = gate_up + token * 2 * inter;
+  // gate and up columns alternate in runs of `block` (block == inter: all gate columns, then all up columns)
+  const int64_t gi = i / block * 2 * block + i % block, ui = gi + block;
   float g, u;
   if (PARTS) {
     g = u = 0.f;
     for (int s = 0; s < num_parts; ++s) {
-      g += to_float<TI>(row[s * part_stride + i]);
-      u += to_float<TI>(row[s * part_stride + inter + i]);
+      g += to_float<TI>(row[s * part_stride + gi]);
+      u += to_float<TI>(row[s * part_stride + ui]);
     }
   } else {
-    g = to_float<TI>(row[i]);
-    u = to_float<TI>(row[inter + i]);
+    g = to_float<TI>(row[gi]);
+    u = to_float<TI>(row[ui]);
   }
   // silu(g) = g * sigmoid(g), in float (ampere_kv/runner.py:176)
   out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
@@ -292,7 +294,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int num_parts, T
 
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter_vecs,
-                                    int64_t total_vecs) {
+                                    int64_t total_vecs, int block) {
   constexpr int V = 16 / sizeof(T);     // elements per 16-byte vector
   pdl_launch_dependents();
   pdl_wait();
@@ -302,13 +304,14 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
   const int i = (int)(idx - token * inter_vecs) * V;
   const int64_t inter = (int64_t)inter_vecs * V;
   const T* row = gate_up + token * 2 * inter;
+  const int gi = i / block * 2 * block + i % block;     // `block` is a multiple of V
   float g[V], u[V], r[V];
   if constexpr (sizeof(T) == 2) {
-    load8<T>(row + i, g);
-    load8<T>(row + inter + i, u);
+    load8<T>(row + gi, g);
+    load8<T>(row + gi + block, u);
   } else {
-    load4<T>(row + i, g);
-    load4<T>(row + inter + i, u);
+    load4<T>(row + gi, g);
+    load4<T>(row + gi + block, u);
   }
 #pragma unroll
   for (int e = 0; e < V; ++e) r[e] = g[e] / (1.f + expf(-g[e])) * u[e];
@@ -322,13 +325,14 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
   }
 }
 
-int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_tokens, int64_t inter, int dtype,
-                    cudaStream_t stream) {
+int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_tokens, int64_t inter, int64_t block,
+                    int dtype, cudaStream_t stream) {
   const int64_t total = num_tokens * inter;
   if (total == 0) return 0;
+  if (block <= 0 || inter % block != 0) return (int)cudaErrorInvalidValue;
   const int threads = 256;
   const int vec = dtype == kBFloat16 ? 8 : 4;
-  const bool aligned = parts == 0 && inter % vec == 0 && inter / vec < 0x7fffffffLL &&
+  const bool aligned = parts == 0 && inter % vec == 0 && block % vec == 0 && inter < 0x3fffffffLL &&
                        (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
   if (aligned) {
     const int64_t total_vecs = total / vec;
@@ -337,9 +341,9 @@ int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_token
     if (dtype == kBFloat16)
       return (int)launch_chain(silu_mul_vec_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream,
                                dim3(1, 1, 1), (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (int)(inter / vec),
-                               total_vecs);
+                               total_vecs, (int)block);
     return (int)launch_chain(silu_mul_vec_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream,
-                             dim3(1, 1, 1), (const float*)gate_up, (float*)out, (int)(inter / vec), total_vecs);
+                             dim3(1, 1, 1), (const float*)gate_up, (float*)out, (int)(inter / vec), total_vecs, (int)block);
   }
   const int64_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
@@ -347,16 +351,16 @@ int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_token
   if (parts > 0) {
     if (dtype == kBFloat16)
       silu_mul_kernel<__nv_bfloat16, float, true><<<(unsigned)blocks, threads, 0, stream>>>(
-          (const float*)gate_up, parts, (__nv_bfloat16*)out, inter, total, part_stride);
+          (const float*)gate_up, parts, (__nv_bfloat16*)out, inter, total, part_stride, block);
     else
       silu_mul_kernel<float, float, true><<<(unsigned)blocks, threads, 0, stream>>>(
-          (const float*)gate_up, parts, (float*)out, inter, total, part_stride);
+          (const float*)gate_up, parts, (float*)out, inter, total, part_stride, block);
   } else if (dtype == kBFloat16) {
     silu_mul_kernel<__nv_bfloat16, __nv_bfloat16, false><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)gate_up, 1, (__nv_bfloat16*)out, inter, total, part_stride);
+        (const __nv_bfloat16*)gate_up, 1, (__nv_bfloat16*)out, inter, total, part_stride, block);
   } else {
     silu_mul_kernel<float, float, false><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const float*)gate_up, 1, (float*)out, inter, total, part_stride);
+        (const float*)gate_up, 1, (float*)out, inter, total, part_stride, block);
   }
   return (int)cudaGetLastError();
 }

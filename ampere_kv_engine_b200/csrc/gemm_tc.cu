@@ -141,7 +141,7 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-template <int BN, typename OutT, int kStages>
+template <int BN, typename OutT, int kStages, int kEpilogue>
 __global__ void __launch_bounds__(192)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                     GemmParams p) {
@@ -265,14 +265,35 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     cluster_sync_all();
     if (warp >= 2) {
       const int row = (warp & 3) * 32 + lane;
-      const int feature = tile * kTileM + row;
       OutT* out = reinterpret_cast<OutT*>(p.out);
-      if (feature < p.features) {
-        for (int token = split; token < p.tokens; token += p.splits) {
-          const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-          float sum = 0.f;
-          for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
-          out[(int64_t)token * p.features + feature] = from_float<OutT>(sum);
+      if constexpr (kEpilogue == kEpilogueGated) {
+        // rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64 outputs.  A thread takes
+        // output j of every other token of this CTA's share and adds up both of its rows.
+        const int j = row & 63, half = row >> 6;
+        const int out_features = p.features / 2;
+        const int feature = tile * (kTileM / 2) + j;
+        if (feature < out_features) {
+          for (int token = split + half * p.splits; token < p.tokens; token += 2 * p.splits) {
+            const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + j) * 4u;
+            float g = 0.f, u = 0.f;
+            for (int s = 0; s < p.splits; ++s) {
+              g += ld_peer_smem(addr, (uint32_t)s);
+              u += ld_peer_smem(addr + (kTileM / 2) * 4u, (uint32_t)s);
+            }
+            g = __bfloat162float(__float2bfloat16_rn(g));
+            u = __bfloat162float(__float2bfloat16_rn(u));
+            out[(int64_t)token * out_features + feature] = from_float<OutT>(g / (1.f + expf(-g)) * u);
+          }
+        }
+      } else {
+        const int feature = tile * kTileM + row;
+        if (feature < p.features) {
+          for (int token = split; token < p.tokens; token += p.splits) {
+            const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
+            float sum = 0.f;
+            for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+            out[(int64_t)token * p.features + feature] = from_float<OutT>(sum);
+          }
         }
       }
     }
@@ -331,9 +352,9 @@ bool matrix_map(const void* base, int64_t rows, int64_t cols, int box_rows, CUte
   return true;
 }
 
-template <int BN, typename OutT, int kStages>
+template <int BN, typename OutT, int kStages, int kEpilogue>
 int launch_stages(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = small_m_gemm_kernel<BN, OutT, kStages>;
+  auto kernel = small_m_gemm_kernel<BN, OutT, kStages, kEpilogue>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, kStages>::kBytes);
@@ -346,7 +367,7 @@ int launch_stages(const CUtensorMap& w_map, const CUtensorMap& x_map, const Gemm
 }
 
 // Stages of the TMA ring.  Four stages of 18-24 KB let three (two at 64 tokens) CTAs share an SM.
-// AKV_GEMM_STAGES=2|4|8 in the environment overrides it (for measurements).
+// AKV_GEMM_STAGES=2|4|8 in the environment overrides it for the plain epilogue (for measurements).
 int ring_stages() {
   static const int stages = [] {
     const char* v = getenv("AKV_GEMM_STAGES");
@@ -357,19 +378,24 @@ int ring_stages() {
 }
 
 template <int BN, typename OutT>
-int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
+int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue,
+              cudaStream_t stream) {
+  if constexpr (sizeof(OutT) == 2) {
+    if (epilogue == kEpilogueGated) return launch_stages<BN, OutT, 4, kEpilogueGated>(w_map, x_map, p, stream);
+  }
   switch (ring_stages()) {
-    case 2: return launch_stages<BN, OutT, 2>(w_map, x_map, p, stream);
-    case 8: return launch_stages<BN, OutT, 8>(w_map, x_map, p, stream);
-    default: return launch_stages<BN, OutT, 4>(w_map, x_map, p, stream);
+    case 2: return launch_stages<BN, OutT, 2, kEpiloguePlain>(w_map, x_map, p, stream);
+    case 8: return launch_stages<BN, OutT, 8, kEpiloguePlain>(w_map, x_map, p, stream);
+    default: return launch_stages<BN, OutT, 4, kEpiloguePlain>(w_map, x_map, p, stream);
   }
 }
 
 template <typename OutT>
-int launch_out(int bn, const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
-  if (bn == 16) return launch_bn<16, OutT>(w_map, x_map, p, stream);
-  if (bn == 32) return launch_bn<32, OutT>(w_map, x_map, p, stream);
-  return launch_bn<64, OutT>(w_map, x_map, p, stream);
+int launch_out(int bn, const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue,
+               cudaStream_t stream) {
+  if (bn == 16) return launch_bn<16, OutT>(w_map, x_map, p, epilogue, stream);
+  if (bn == 32) return launch_bn<32, OutT>(w_map, x_map, p, epilogue, stream);
+  return launch_bn<64, OutT>(w_map, x_map, p, epilogue, stream);
 }
 
 }  // namespace
@@ -391,9 +417,12 @@ int small_m_gemm_splits(int64_t features, int64_t k) {
 // out_dtype: akv::DType of `out` when the split partials are reduced inside the kernel; parts (float32
 // [splits, tokens, features]) is written instead when `out` is null.
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
-                        int64_t features, int64_t k, int splits, int* status, cudaStream_t stream) {
+                        int64_t features, int64_t k, int splits, int epilogue, int* status, cudaStream_t stream) {
   if (!small_m_gemm_supported(tokens, features, k) || splits < 1) return (int)cudaErrorInvalidValue;
   if ((out == nullptr) == (parts == nullptr)) return (int)cudaErrorInvalidValue;
+  if (epilogue != kEpiloguePlain && epilogue != kEpilogueGated) return (int)cudaErrorInvalidValue;
+  if (epilogue == kEpilogueGated && (out == nullptr || out_dtype != kBFloat16 || features % kTileM != 0))
+    return (int)cudaErrorInvalidValue;
   const int bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
   const int kb_total = (int)((k + kTileK - 1) / kTileK);
   if (splits > kb_total) return (int)cudaErrorInvalidValue;
@@ -402,8 +431,8 @@ int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, 
   if (!matrix_map(w, features, k, kTileM, &w_map) || !matrix_map(x, tokens, k, bn, &x_map))
     return (int)cudaErrorInvalidValue;
   GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status};
-  if (out != nullptr && out_dtype == kBFloat16) return launch_out<__nv_bfloat16>(bn, w_map, x_map, p, stream);
-  return launch_out<float>(bn, w_map, x_map, p, stream);
+  if (out != nullptr && out_dtype == kBFloat16) return launch_out<__nv_bfloat16>(bn, w_map, x_map, p, epilogue, stream);
+  return launch_out<float>(bn, w_map, x_map, p, epilogue, stream);
 }
 
 }  // namespace akv

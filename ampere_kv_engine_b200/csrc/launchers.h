@@ -25,18 +25,25 @@ int launch_add_rmsnorm(float* hidden, const void* delta, int delta_parts, const 
                        const int32_t* rows, int64_t num_rows, int64_t num_tokens, int64_t hidden_size,
                        float eps, int dtype, int* status, cudaStream_t stream);
 
-// out[n, i] = silu(gate_up[n, i]) * gate_up[n, inter + i]; parts > 0: gate_up is float32 [parts, tokens, 2 inter]
+// out[n, i] = silu(gate(n, i)) * up(n, i).  The gate and up columns of gate_up [tokens, 2 inter] alternate in runs
+// of `block` columns (block == inter: all gate columns first, the stored form of separate matrices; block == 64:
+// the form that lets one 128-row GEMM tile hold both).  parts > 0: gate_up is float32 [parts, tokens, 2 inter]
 // partial sums.
-int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_tokens, int64_t inter, int dtype,
-                    cudaStream_t stream);
+int launch_silu_mul(const void* gate_up, int parts, void* out, int64_t num_tokens, int64_t inter, int64_t block,
+                    int dtype, cudaStream_t stream);
 
 // Split-K weight-streaming product for few tokens (gemm_tc.cu), x [tokens, k] and w [features, k] bfloat16.
 // Either out [tokens, features] (out_dtype: float32 or bfloat16; the splits are added up inside the kernel,
 // splits in {1, 2, 4, 8}) or parts [splits, tokens, features] float32 (each split's sum as it is).
 bool small_m_gemm_supported(int64_t tokens, int64_t features, int64_t k);
 int small_m_gemm_splits(int64_t features, int64_t k);
+// What the kernel does with a finished output tile besides storing it.
+//   kEpilogueGated: w holds gate and up rows alternating in runs of 64, so that a 128-row tile has both for 64
+//   outputs; out is [tokens, features / 2] bfloat16 = silu(gate) * up, with gate and up rounded to bfloat16 first
+//   (what the unfused pair, product then launch_silu_mul, computes).
+enum GemmEpilogue : int { kEpiloguePlain = 0, kEpilogueGated = 1 };
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
-                        int64_t features, int64_t k, int splits, int* status, cudaStream_t stream);
+                        int64_t features, int64_t k, int splits, int epilogue, int* status, cudaStream_t stream);
 
 struct QkRopeWriteParams {
   const void* qkv;          // [N, (NH + 2 NKV) * D]; with qkv_parts > 0: float32 [qkv_parts, N, ...] partial sums

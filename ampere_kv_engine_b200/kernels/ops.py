@@ -62,17 +62,37 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``silu(gate) * up`` of [tokens, 2 * intermediate] (gate columns first).  A 3-D float32 input is a stack of
-    split-K partial sums that are added up first; then ``out_dtype`` names the result's type."""
+GATE_UP_RUN = 64   # gate and up rows alternate in runs of this many when one GEMM tile is to hold both
+
+
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype | None = None, block: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` of [tokens, 2 * intermediate].  Gate and up columns alternate in runs of ``block``
+    columns (0: all gate columns first).  A 3-D float32 input is a stack of split-K partial sums that are added
+    up first; then ``out_dtype`` names the result's type."""
     if gate_up.dim() == 3:
         out_dtype = out_dtype or torch.bfloat16
     else:
         out_dtype = gate_up.dtype
     out = torch.empty((gate_up.shape[-2], gate_up.shape[-1] // 2), dtype=out_dtype, device=gate_up.device)
-    ext().silu_mul(gate_up, out)
+    ext().silu_mul(gate_up, out, int(block))
     _launched()
     return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.Tensor:
+    """One matrix [2 * intermediate, k] whose rows are ``block`` gate rows, then the ``block`` up rows of the same
+    outputs, and so on."""
+    inter, k = gate.shape
+    return torch.stack((gate.view(inter // block, block, k), up.view(inter // block, block, k)), dim=1).reshape(2 * inter, k)
+
+
+def gated_linear(x: torch.Tensor, gate_up: torch.Tensor, block: int, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(x @ gate.T) * (x @ up.T)`` with gate and up rows stored in alternating runs of ``block`` (0: all gate
+    rows first).  Few bfloat16 tokens and ``block == GATE_UP_RUN``: one tcgen05 kernel that applies the activation
+    to its output tile; otherwise the product and the activation kernel."""
+    if block == GATE_UP_RUN and _takes_small_m(x, gate_up) and gate_up.shape[0] % 128 == 0:
+        return small_m_gemm(x, gate_up, status=status, gated=True)
+    return silu_mul(linear(x, gate_up, partial_ok=True, status=status), x.dtype, block)
 
 
 def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache, *, num_heads,
@@ -169,12 +189,15 @@ prefer_partials = False
 
 
 def small_m_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                 splits: int | None = None, parts: bool = False, status: torch.Tensor | None = None) -> torch.Tensor:
+                 splits: int | None = None, parts: bool = False, status: torch.Tensor | None = None,
+                 gated: bool = False) -> torch.Tensor:
     """``x @ weight.T`` for 1..64 bfloat16 tokens on the tcgen05 tensor cores, K cut into ``splits`` ranges.
 
     Default: [tokens, features] in ``out_dtype`` (float32 or bfloat16); the splits (1, 2, 4 or 8 CTAs of a
     cluster) add their float32 partial tiles up through distributed shared memory.  ``parts=True``: the float32
     partial sums themselves, [splits, tokens, features], for a consumer kernel that adds them up.
+    ``gated=True``: ``weight`` holds gate and up rows in alternating runs of 64 and the result is
+    ``silu(gate) * up``, [tokens, features / 2] bfloat16.
     """
     kb_total = (weight.shape[1] + 63) // 64
     if splits is None:
@@ -185,8 +208,9 @@ def small_m_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype =
     else:
         while splits not in (1, 2, 4, 8):
             splits -= 1
-        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
-    ext().small_m_gemm(x, weight, out, splits, status)
+        out = torch.empty((x.shape[0], weight.shape[0] // 2 if gated else weight.shape[0]),
+                          dtype=torch.bfloat16 if gated else out_dtype, device=x.device)
+    ext().small_m_gemm(x, weight, out, splits, status, gated)
     _launched()
     return out
 

@@ -1,8 +1,11 @@
 """Dense gated feed-forward: ``down(act(gate(x)) * up(x))``.
 
 The reference's form (ampere_kv/runner.py:172-177) with SiLU.  gate and up are stored as one
-matrix (gate rows first), so one product feeds the activation kernel; each output element
-keeps its own row's accumulation order.
+matrix, so one product feeds the activation; each output element keeps its own row's
+accumulation order.  Where the intermediate size allows it the rows alternate in runs of 64
+gate rows and the 64 up rows of the same outputs: a 128-row tile of the decode GEMM then holds
+both and applies the activation itself, and the prompt path's activation kernel reads the same
+layout.  Otherwise all gate rows come first.
 """
 
 from __future__ import annotations
@@ -27,6 +30,7 @@ class GatedMLP(FeedForward):
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation {activation!r} is not supported (only 'silu')")
         self.gate_up: torch.Tensor | None = None
+        self.run = ops.GATE_UP_RUN if self.intermediate_size % ops.GATE_UP_RUN == 0 else 0
         self.down: torch.Tensor | None = None
 
     def param_specs(self):
@@ -38,10 +42,14 @@ class GatedMLP(FeedForward):
         }
 
     def load(self, tensors):
-        self.gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0).contiguous()
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        if self.run:
+            self.gate_up = ops.interleave_gate_up(gate, up, self.run).contiguous()
+        else:
+            self.gate_up = torch.cat((gate, up), dim=0).contiguous()
         self.down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x, ctx):
         status = getattr(ctx, "status", None)
-        gate_up = ops.linear(x, self.gate_up, partial_ok=True, status=status)
-        return ops.linear(ops.silu_mul(gate_up, self.dtype), self.down, partial_ok=True, status=status)
+        act = ops.gated_linear(x, self.gate_up, self.run, status=status)
+        return ops.linear(act, self.down, partial_ok=True, status=status)

@@ -35,11 +35,13 @@ class FakeExt:
         inv = torch.rsqrt(x.square().mean(-1, keepdim=True) + eps)
         out.copy_((x * inv * weight).to(out.dtype))
 
-    def silu_mul(self, gate_up, out):
+    def silu_mul(self, gate_up, out, block=0):
         if gate_up.dim() == 3:
             gate_up = gate_up.sum(0)
         inter = gate_up.shape[1] // 2
-        g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        block = block or inter
+        pairs = gate_up.float().view(gate_up.shape[0], inter // block, 2, block)
+        g, u = pairs[:, :, 0].reshape(-1, inter), pairs[:, :, 1].reshape(-1, inter)
         out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
     def qk_norm_rope_write(self, qkv, positions, slots, q_weight, k_weight, inv_freq, q_out, k_out, v_out, k_cache,

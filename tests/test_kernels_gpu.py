@@ -91,6 +91,47 @@ def test_silu_mul(ops, dtype):
     torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter,block", [(320, 64), (300, 4), (96, 32), (66, 3)])
+def test_silu_mul_with_alternating_runs(ops, dtype, inter, block):
+    """Gate and up columns in alternating runs (the layout of the fused decode GEMM), vector and scalar paths."""
+    g = torch.Generator().manual_seed(inter)
+    gate, up = (3 * torch.randn(2, 23, inter, generator=g)).to(dtype)
+    mixed = torch.stack((gate.view(23, inter // block, block), up.view(23, inter // block, block)), dim=2)
+    out = ops.silu_mul(dev(mixed.reshape(23, 2 * inter).contiguous()), block=block)
+    want = torch.nn.functional.silu(gate.float()) * up.float()
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+    with pytest.raises(RuntimeError, match="run length"):
+        ops.silu_mul(dev(mixed.reshape(23, 2 * inter).contiguous()), block=7)
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(1, 64, 64), (8, 192, 320), (17, 640, 1024), (32, 128, 4096), (5, 12288, 512)])
+def test_gated_gemm_applies_the_activation(ops, tokens, inter, k):
+    """The decode GEMM with the gated epilogue equals product, rounding, then the activation kernel."""
+    g = torch.Generator().manual_seed(tokens + inter)
+    gate = (torch.randn(inter, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    up = (torch.randn(inter, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    x = (2 * torch.randn(tokens, k, generator=g)).to(torch.bfloat16)
+    w = ops.interleave_gate_up(gate, up, ops.GATE_UP_RUN).contiguous()
+    status = status_word()
+    out = ops.gated_linear(dev(x), dev(w), ops.GATE_UP_RUN, status=status)
+    assert int(status.item()) == 0 and out.shape == (tokens, inter) and out.dtype == torch.bfloat16
+    gf = (x.float() @ gate.float().t()).to(torch.bfloat16).float()
+    uf = (x.float() @ up.float().t()).to(torch.bfloat16).float()
+    want = torch.nn.functional.silu(gf) * uf
+    torch.testing.assert_close(out.float().cpu(), want, atol=3e-2, rtol=3e-2)
+    # every split count gives the same kind of answer, and the unfused pair agrees
+    for splits in (1, 2, 4, 8):
+        if splits <= (k + 63) // 64:
+            got = ops.small_m_gemm(dev(x), dev(w), splits=splits, gated=True)
+            torch.testing.assert_close(got.float().cpu(), want, atol=3e-2, rtol=3e-2)
+    unfused = ops.silu_mul(torch.nn.functional.linear(dev(x), dev(w)), block=ops.GATE_UP_RUN)
+    torch.testing.assert_close(out.float().cpu(), unfused.float().cpu(), atol=3e-2, rtol=3e-2)
+    # all gate rows first: the product and the activation kernel
+    halves = ops.gated_linear(dev(x), dev(torch.cat((gate, up))), 0)
+    torch.testing.assert_close(halves.float().cpu(), want, atol=3e-2, rtol=3e-2)
+
+
 def _qkv_reference(qkv, positions, q_w, k_w, nh, nkv, d, eps, theta):
     n = qkv.shape[0]
     x = qkv.float().view(n, nh + 2 * nkv, d)
