@@ -216,7 +216,7 @@ void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits,
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(akv::launch_small_m_gemm(x.data_ptr(), w.data_ptr(), out_ptr, out_code, parts_ptr, x.size(0), w.size(0),
                                         x.size(1), (int)splits, gated ? akv::kEpilogueGated : akv::kEpiloguePlain,
-                                        status_ptr(status), stream_of(x)),
+                                        nullptr, status_ptr(status), stream_of(x)),
                "small_m_gemm");
 }
 
@@ -243,6 +243,59 @@ CacheGeometry check_cache(const Tensor& k_cache, const Tensor& v_cache, int num_
               k_cache.size(1), " kv heads, ", k_cache.size(3), " dims], the call says [", num_kv_heads, ", ",
               head_dim, "]");
   return {k_cache.size(0), num_kv_heads, (int)k_cache.size(2), head_dim};
+}
+
+// The q/k/v projection of few tokens with per-head norm, rotation and the cache write done on the output tile
+// (heads of 128 dims, the whole head rotated or none of it).  q_out [tokens, heads * 128]; K and V go to the
+// slots of the cache pages when slots and caches are given, and are dropped otherwise.
+void small_m_gemm_qkv(const Tensor& x, const Tensor& w, Tensor& q_out, const Tensor& positions,
+                      const OptTensor& slots, const OptTensor& q_weight, const OptTensor& k_weight,
+                      const OptTensor& inv_freq, const OptTensor& k_cache, const OptTensor& v_cache,
+                      int64_t num_heads, int64_t num_kv_heads, double eps, int64_t splits, const OptTensor& status) {
+  check_cuda(x, "x");
+  check_cuda(w, "w");
+  check_cuda(q_out, "q_out");
+  AKV_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
+                q_out.scalar_type() == at::kBFloat16, "x, w and q_out must be bfloat16");
+  AKV_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1), "x must be [tokens, k] and w [features, k]");
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && w.size(0) == (num_heads + 2 * num_kv_heads) * 128,
+            "w must hold (heads + 2 kv_heads) heads of 128 rows each, got ", w.size(0), " rows");
+  AKV_CHECK(akv::small_m_gemm_supported(x.size(0), w.size(0), x.size(1)),
+            "small_m_gemm takes 1..64 tokens and a K that is a multiple of 8 and at least 64; got ", x.size(0),
+            " tokens, K = ", x.size(1));
+  AKV_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0,
+            "x and w must be 16-byte aligned");
+  const int64_t n = x.size(0), kb_total = (x.size(1) + 63) / 64;
+  AKV_CHECK((splits == 1 || splits == 2 || splits == 4 || splits == 8) && splits <= kb_total,
+            "splits must be 1, 2, 4 or 8 and at most the number of 64-element K blocks, got ", splits);
+  AKV_CHECK(q_out.is_contiguous() && q_out.numel() == n * num_heads * 128, "q_out must be [tokens, heads * 128]");
+  check_i32(positions, "positions", n);
+  akv::GemmQkv e{};
+  e.positions = positions.data_ptr<int>();
+  e.q_out = q_out.data_ptr();
+  if (slots.has_value()) {
+    check_i32(*slots, "slots", n);
+    e.slots = slots->data_ptr<int>();
+  }
+  if (q_weight.has_value()) { check_f32(*q_weight, "q_weight", 128); e.q_weight = q_weight->data_ptr<float>(); }
+  if (k_weight.has_value()) { check_f32(*k_weight, "k_weight", 128); e.k_weight = k_weight->data_ptr<float>(); }
+  if (inv_freq.has_value()) { check_f32(*inv_freq, "inv_freq", 64); e.inv_freq = inv_freq->data_ptr<float>(); }
+  AKV_CHECK(k_cache.has_value() == v_cache.has_value(), "k_cache and v_cache come together");
+  if (k_cache.has_value()) {
+    AKV_CHECK(slots.has_value(), "a cache to write needs slots");
+    const CacheGeometry g = check_cache(*k_cache, *v_cache, (int)num_kv_heads, 128, q_out);
+    e.k_cache = k_cache->data_ptr();
+    e.v_cache = v_cache->data_ptr();
+    e.num_pages = g.num_pages;
+    e.page_size = g.page_size;
+  }
+  e.num_heads = (int)num_heads;
+  e.num_kv_heads = (int)num_kv_heads;
+  e.eps = (float)eps;
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_small_m_gemm(x.data_ptr(), w.data_ptr(), nullptr, 0, nullptr, n, w.size(0), x.size(1),
+                                        (int)splits, akv::kEpilogueQkv, &e, status_ptr(status), stream_of(x)),
+               "small_m_gemm_qkv");
 }
 
 void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTensor& slots,
@@ -422,6 +475,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"), py::arg("block") = 0);
   m.def("small_m_gemm", &small_m_gemm, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("splits") = 1,
         py::arg("status") = py::none(), py::arg("gated") = false);
+  m.def("small_m_gemm_qkv", &small_m_gemm_qkv, py::arg("x"), py::arg("w"), py::arg("q_out"), py::arg("positions"),
+        py::arg("slots"), py::arg("q_weight"), py::arg("k_weight"), py::arg("inv_freq"), py::arg("k_cache"),
+        py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("eps"), py::arg("splits") = 1,
+        py::arg("status") = py::none());
   m.def("small_m_gemm_supported", &small_m_gemm_supported);
   m.def("small_m_gemm_splits", &small_m_gemm_splits);
   m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),

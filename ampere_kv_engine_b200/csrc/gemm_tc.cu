@@ -116,6 +116,7 @@ struct GemmParams {
   int kb_total;        // K blocks of 64 in all
   int splits;
   int* status;
+  GemmQkv qkv;         // kEpilogueQkv only
 };
 
 template <int BN, int kStages>
@@ -124,7 +125,8 @@ struct GemmSmem {
   static constexpr int kB = BN * kTileK * 2;
   static constexpr int kStage = kA + kB;
   static constexpr int kReduce = BN * kTileM * 4;                      // float32 partial tile, reuses the stages
-  static_assert(kReduce <= kStages * kStage, "the partial tile must fit in the stage ring");
+  static constexpr int kQkvScratch = (8 + 2 * kTileM) * 4;            // kEpilogueQkv: warp sums and normed values
+  static_assert(kReduce + kQkvScratch <= kStages * kStage, "the partial tile must fit in the stage ring");
   static constexpr int kBytes = kStages * kStage + (2 * kStages + 1) * 8 + 16 + 1024;
 };
 
@@ -180,6 +182,8 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
   bool ok = true;
+  float qkv_wd = 1.f, qkv_freq = 0.f, qkv_sn = 0.f, qkv_co = 1.f;     // kEpilogueQkv: fetched ahead of the product
+  int64_t qkv_slot = -1;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -232,6 +236,20 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   } else {
     // epilogue: warp (2..5) reads the TMEM lanes of its quarter; lane = feature, column = token
     const int quarter = warp & 3;
+    if constexpr (kEpilogue == kEpilogueQkv) {
+      // while the product runs: what the first token of this CTA's share needs besides the product (its angle's
+      // sine and cosine, its cache slot, this dim's norm weight).  None of it comes from the previous kernel.
+      const GemmQkv& e = p.qkv;
+      const int row = quarter * 32 + lane;
+      const bool is_q = tile < e.num_heads, is_k = !is_q && tile < e.num_heads + e.num_kv_heads;
+      const float* w = is_q ? e.q_weight : (is_k ? e.k_weight : nullptr);
+      qkv_wd = w != nullptr ? w[row] : 1.f;
+      qkv_freq = ((is_q || is_k) && e.inv_freq != nullptr) ? e.inv_freq[row & 63] : 0.f;
+      if (split < p.tokens) {
+        sincosf((float)e.positions[split] * qkv_freq, &qkv_sn, &qkv_co);
+        if (!is_q && e.slots != nullptr) qkv_slot = e.slots[split];
+      }
+    }
     if (!mbar_wait(acc_ready, 0)) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int row = quarter * 32 + lane;
@@ -284,6 +302,59 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             u = __bfloat162float(__float2bfloat16_rn(u));
             out[(int64_t)token * out_features + feature] = from_float<OutT>(g / (1.f + expf(-g)) * u);
           }
+        }
+      } else if constexpr (kEpilogue == kEpilogueQkv) {
+        // The tile is one head of 128 dims; a thread owns dim `row` of it.  Per token of this CTA's share: add
+        // up the splits, round as the stored product would be, norm over the head, rotate with the partner dim
+        // (row ^ 64), store to q_out or to the token's cache slot.  The four epilogue warps meet at named
+        // barrier 1.
+        const GemmQkv& e = p.qkv;
+        float* red = reinterpret_cast<float*>(smem + GemmSmem<BN, kStages>::kReduce);      // [2][4] warp sums
+        float* xch = red + 8;                                                              // [2][128] normed values
+        const int head = tile;
+        const bool is_q = head < e.num_heads, is_k = !is_q && head < e.num_heads + e.num_kv_heads;
+        const int local = is_q ? head : (is_k ? head - e.num_heads : head - e.num_heads - e.num_kv_heads);
+        const bool normed = (is_q ? e.q_weight : (is_k ? e.k_weight : nullptr)) != nullptr;
+        const bool rotate = (is_q || is_k) && e.inv_freq != nullptr;
+        int it = 0;
+        for (int token = split; token < p.tokens; token += p.splits, ++it) {
+          const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
+          float sum = 0.f;
+          for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+          float v = __bfloat162float(__float2bfloat16_rn(sum));
+          float* red_it = red + (it & 1) * 4;
+          float* xch_it = xch + (it & 1) * kTileM;
+          if (it > 0) {       // the first token's were fetched while the product ran
+            if (rotate) sincosf((float)e.positions[token] * qkv_freq, &qkv_sn, &qkv_co);
+            if (!is_q && e.slots != nullptr) qkv_slot = e.slots[token];
+          }
+          if (normed) {
+            const float ss = warp_sum(v * v);
+            if (lane == 0) red_it[warp & 3] = ss;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const float total = red_it[0] + red_it[1] + red_it[2] + red_it[3];
+            v = v * rsqrtf(total / (float)kTileM + e.eps) * qkv_wd;
+          }
+          if (rotate) {
+            xch_it[row] = v;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const float partner = xch_it[row ^ 64];
+            v = row < 64 ? v * qkv_co - partner * qkv_sn : v * qkv_co + partner * qkv_sn;
+          }
+          __nv_bfloat16* dst = nullptr;
+          if (is_q) {
+            dst = (__nv_bfloat16*)e.q_out + ((int64_t)token * e.num_heads + local) * kTileM;
+          } else if (e.slots != nullptr && e.k_cache != nullptr) {
+            const int64_t slot = qkv_slot;
+            if (slot >= e.num_pages * e.page_size) {
+              if (row == 0) set_status(p.status, kBadSlot);
+            } else if (slot >= 0) {
+              const int64_t page = slot / e.page_size, off = slot % e.page_size;
+              dst = (__nv_bfloat16*)(is_k ? e.k_cache : e.v_cache) +
+                    ((page * e.num_kv_heads + local) * e.page_size + off) * (int64_t)kTileM;
+            }
+          }
+          if (dst != nullptr) dst[row] = __float2bfloat16_rn(v);
         }
       } else {
         const int feature = tile * kTileM + row;
@@ -382,6 +453,7 @@ int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmPara
               cudaStream_t stream) {
   if constexpr (sizeof(OutT) == 2) {
     if (epilogue == kEpilogueGated) return launch_stages<BN, OutT, 4, kEpilogueGated>(w_map, x_map, p, stream);
+    if (epilogue == kEpilogueQkv) return launch_stages<BN, OutT, 4, kEpilogueQkv>(w_map, x_map, p, stream);
   }
   switch (ring_stages()) {
     case 2: return launch_stages<BN, OutT, 2, kEpiloguePlain>(w_map, x_map, p, stream);
@@ -417,10 +489,18 @@ int small_m_gemm_splits(int64_t features, int64_t k) {
 // out_dtype: akv::DType of `out` when the split partials are reduced inside the kernel; parts (float32
 // [splits, tokens, features]) is written instead when `out` is null.
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
-                        int64_t features, int64_t k, int splits, int epilogue, int* status, cudaStream_t stream) {
+                        int64_t features, int64_t k, int splits, int epilogue, const GemmQkv* qkv, int* status,
+                        cudaStream_t stream) {
   if (!small_m_gemm_supported(tokens, features, k) || splits < 1) return (int)cudaErrorInvalidValue;
+  if (epilogue == kEpilogueQkv) {
+    // the results go where qkv says; `out` only selects the in-kernel reduction and is never written
+    if (qkv == nullptr || qkv->q_out == nullptr || parts != nullptr || qkv->positions == nullptr) return (int)cudaErrorInvalidValue;
+    if (features != (int64_t)(qkv->num_heads + 2 * qkv->num_kv_heads) * kTileM) return (int)cudaErrorInvalidValue;
+    out = qkv->q_out;
+    out_dtype = kBFloat16;
+  }
   if ((out == nullptr) == (parts == nullptr)) return (int)cudaErrorInvalidValue;
-  if (epilogue != kEpiloguePlain && epilogue != kEpilogueGated) return (int)cudaErrorInvalidValue;
+  if (epilogue != kEpiloguePlain && epilogue != kEpilogueGated && epilogue != kEpilogueQkv) return (int)cudaErrorInvalidValue;
   if (epilogue == kEpilogueGated && (out == nullptr || out_dtype != kBFloat16 || features % kTileM != 0))
     return (int)cudaErrorInvalidValue;
   const int bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
@@ -430,7 +510,8 @@ int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, 
   CUtensorMap w_map, x_map;
   if (!matrix_map(w, features, k, kTileM, &w_map) || !matrix_map(x, tokens, k, bn, &x_map))
     return (int)cudaErrorInvalidValue;
-  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status};
+  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status, {}};
+  if (epilogue == kEpilogueQkv) p.qkv = *qkv;
   if (out != nullptr && out_dtype == kBFloat16) return launch_out<__nv_bfloat16>(bn, w_map, x_map, p, epilogue, stream);
   return launch_out<float>(bn, w_map, x_map, p, epilogue, stream);
 }

@@ -41,9 +41,27 @@ int small_m_gemm_splits(int64_t features, int64_t k);
 //   kEpilogueGated: w holds gate and up rows alternating in runs of 64, so that a 128-row tile has both for 64
 //   outputs; out is [tokens, features / 2] bfloat16 = silu(gate) * up, with gate and up rounded to bfloat16 first
 //   (what the unfused pair, product then launch_silu_mul, computes).
-enum GemmEpilogue : int { kEpiloguePlain = 0, kEpilogueGated = 1 };
+//   kEpilogueQkv: w holds the q, k and v projections of heads of 128 dims, one head per 128-row tile; the tile's
+//   values, rounded to bfloat16, then go through what launch_qk_norm_rope_write does (per-head RMSNorm of q and
+//   k, rotation of the whole head by position) and land in q_out / the cache pages (GemmQkv); nothing else is
+//   stored.
+enum GemmEpilogue : int { kEpiloguePlain = 0, kEpilogueGated = 1, kEpilogueQkv = 2 };
+struct GemmQkv {
+  const int32_t* positions;  // [tokens]
+  const int32_t* slots;      // [tokens] page * page_size + offset, or -1; null: K and V are not kept
+  const float* q_weight;     // [128] or null: no norm
+  const float* k_weight;
+  const float* inv_freq;     // [64] or null: no rotation
+  void* q_out;               // [tokens, num_heads * 128] bfloat16
+  void* k_cache;             // [num_pages, num_kv_heads, page_size, 128] bfloat16, or null
+  void* v_cache;
+  int num_heads, num_kv_heads, page_size;
+  int64_t num_pages;
+  float eps;
+};
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
-                        int64_t features, int64_t k, int splits, int epilogue, int* status, cudaStream_t stream);
+                        int64_t features, int64_t k, int splits, int epilogue, const GemmQkv* qkv, int* status,
+                        cudaStream_t stream);
 
 struct QkRopeWriteParams {
   const void* qkv;          // [N, (NH + 2 NKV) * D]; with qkv_parts > 0: float32 [qkv_parts, N, ...] partial sums

@@ -114,6 +114,30 @@ def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_ca
     return (q_out, k_out, v_out) if want_kv else q_out
 
 
+def project_qkv(x, w_qkv, bias, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache, *, num_heads,
+                num_kv_heads, head_dim, rotary_dim, eps, status=None):
+    """The q/k/v projection of ``x``, then per-head RMSNorm of q and k, rotation of the first ``rotary_dim`` dims
+    by position, and K/V written to their cache slots.  Returns q [tokens, heads * head_dim].
+
+    Few bfloat16 tokens with heads of 128 dims that are rotated whole: one tcgen05 kernel whose 128-row tile is
+    one head and does all of it on the tile.  Otherwise the product, then ``qk_norm_rope_write``.
+    """
+    if (bias is None and head_dim == 128 and (inv_freq is None or rotary_dim == 128) and _takes_small_m(x, w_qkv)
+            and w_qkv.shape[0] == (num_heads + 2 * num_kv_heads) * 128):
+        splits = ext().small_m_gemm_splits(w_qkv.shape[0], w_qkv.shape[1])
+        while splits not in (1, 2, 4, 8):
+            splits -= 1
+        q_out = torch.empty((x.shape[0], num_heads * 128), dtype=torch.bfloat16, device=x.device)
+        ext().small_m_gemm_qkv(x, w_qkv, q_out, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache,
+                               num_heads, num_kv_heads, float(eps), splits, status)
+        _launched()
+        return q_out
+    qkv = linear(x, w_qkv, bias, partial_ok=True, status=status)
+    return qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache,
+                              num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                              rotary_dim=rotary_dim, eps=eps, status=status)
+
+
 def kv_write(k, v, slots, k_cache, v_cache, status=None) -> None:
     ext().kv_write(k, v, slots, k_cache, v_cache, status)
     _launched()

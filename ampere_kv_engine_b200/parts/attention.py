@@ -83,19 +83,19 @@ class PagedAttention(Mixer):
 
     def forward(self, x, ctx, cache):
         group = ctx.groups[cache.group]
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv, partial_ok=True, status=ctx.status)
         slots = group.slot_mapping if cache.writes else None
         k_cache = cache.k_cache if cache.writes else None
         v_cache = cache.v_cache if cache.writes else None
         fused = self.position_encoding.fused_rotary()
         if fused is not None:
             inv_freq, rotary_dim = fused
-            q = ops.qk_norm_rope_write(
-                qkv, ctx.positions, slots, self.q_norm_weight, self.k_norm_weight, inv_freq, k_cache, v_cache,
-                num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+            q = ops.project_qkv(
+                x, self.w_qkv, self.b_qkv, ctx.positions, slots, self.q_norm_weight, self.k_norm_weight, inv_freq,
+                k_cache, v_cache, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                 rotary_dim=rotary_dim, eps=self.qk_norm_eps, status=ctx.status)
         else:
             # an encoding that is not a fused rotation: norm, encode on dense q/k, then write the pages
+            qkv = ops.linear(x, self.w_qkv, self.b_qkv, partial_ok=True, status=ctx.status)
             q, k, v = ops.qk_norm_rope_write(
                 qkv, ctx.positions, None, self.q_norm_weight, self.k_norm_weight, None, None, None,
                 num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, rotary_dim=0,

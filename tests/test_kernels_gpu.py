@@ -180,6 +180,59 @@ def test_qk_norm_rope_write(ops, dtype, nh, nkv, d, page):
     assert bool(torch.isnan(v_host.float()[untouched]).all())
 
 
+@pytest.mark.parametrize("tokens,nh,nkv,k,page", [(1, 2, 1, 64, 16), (8, 4, 2, 320, 8), (19, 3, 3, 1024, 32), (32, 8, 2, 2048, 16)])
+def test_project_qkv_on_the_gemm_tile(ops, tokens, nh, nkv, k, page):
+    """Few tokens with heads of 128 dims: the projection kernel norms, rotates and writes the cache on its output
+    tile.  It must equal the product followed by qk_norm_rope_write, and the plain reference."""
+    d, eps, theta, pages = 128, 1e-5, 50000.0, 9
+    g = torch.Generator().manual_seed(tokens + k)
+    w = (torch.randn((nh + 2 * nkv) * d, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    x = (2 * torch.randn(tokens, k, generator=g)).to(torch.bfloat16)
+    positions = torch.randint(0, 9000, (tokens,), generator=g, dtype=torch.int32)
+    q_w = 1 + 0.1 * torch.randn(d, generator=g)
+    k_w = 1 + 0.1 * torch.randn(d, generator=g)
+    slots = torch.randperm(pages * page, generator=g)[:tokens].to(torch.int32)
+    if tokens > 5:
+        slots[5] = -1
+    inv_freq = plain.rope_inverse_frequencies(d, theta)
+    results = []
+    for fused in (True, False):
+        ops.use_small_m_gemm = fused
+        try:
+            k_dev = dev(torch.full((pages, nkv, page, d), float("nan")).to(torch.bfloat16))
+            v_dev = k_dev.clone()
+            status = status_word()
+            before = ops.launch_count
+            q = ops.project_qkv(dev(x), dev(w), None, dev(positions), dev(slots), dev(q_w), dev(k_w), dev(inv_freq),
+                                k_dev, v_dev, num_heads=nh, num_kv_heads=nkv, head_dim=d, rotary_dim=d, eps=eps,
+                                status=status)
+            assert ops.launch_count - before == 1      # one kernel of this package either way (the other
+        finally:                                       # route's product is the library's)
+            ops.use_small_m_gemm = True
+        assert int(status.item()) == 0
+        results.append((q.float().cpu(), k_dev.float().cpu(), v_dev.float().cpu()))
+    qkv = (x.float() @ w.float().t()).to(torch.bfloat16)
+    q_ref, k_ref, v_ref = _qkv_reference(qkv, positions, q_w, k_w, nh, nkv, d, eps, theta)
+    for q, k_host, v_host in results:
+        torch.testing.assert_close(q.view(tokens, nh, d), q_ref, atol=3e-2, rtol=3e-2)
+        written = torch.zeros(pages, page, dtype=torch.bool)
+        for t in range(tokens):
+            s_ = int(slots[t])
+            if s_ < 0:
+                continue
+            written[s_ // page, s_ % page] = True
+            torch.testing.assert_close(k_host[s_ // page, :, s_ % page], k_ref[t], atol=3e-2, rtol=3e-2)
+            torch.testing.assert_close(v_host[s_ // page, :, s_ % page], v_ref[t], atol=3e-2, rtol=3e-2)
+        untouched = ~written[:, None, :, None].expand_as(k_host)
+        assert bool(torch.isnan(k_host[untouched]).all()) and bool(torch.isnan(v_host[untouched]).all())
+    # the two routes differ only by the order in which each adds up K
+    torch.testing.assert_close(results[0][0], results[1][0], atol=3e-2, rtol=3e-2)
+    # no norm weights, no rotation, no cache: q is the plain product
+    q = ops.project_qkv(dev(x), dev(w), None, dev(positions), None, None, None, None, None, None, num_heads=nh,
+                        num_kv_heads=nkv, head_dim=d, rotary_dim=0, eps=eps)
+    torch.testing.assert_close(q.float().cpu(), qkv[:, :nh * d].float(), atol=3e-2, rtol=3e-2)
+
+
 def test_qk_partial_rotation_and_no_rotation(ops):
     """rotary_dim < head_dim rotates pairs (j, j + rotary_dim/2) of the first rotary_dim dims only; no table = no rotation."""
     g = torch.Generator().manual_seed(4)
