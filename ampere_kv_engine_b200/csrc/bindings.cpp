@@ -171,53 +171,133 @@ void silu_mul(const Tensor& gate_up, Tensor& out, int64_t block) {
                "silu_mul");
 }
 
+// The token operand of the small-batch product: either x [tokens, k] bfloat16, or the RMS norm of a float32
+// residual stream that the kernel applies itself (hidden [tokens, k], ssq [tiles, tokens] partial sums of squares
+// left by a product with the residual epilogue, the norm's weight [k] and eps).
+struct TokenOperand {
+  const void* x = nullptr;
+  akv::GemmNormedX normed = {};
+  bool is_normed = false;
+  int64_t tokens = 0, k = 0;
+  const Tensor* anchor = nullptr;     // device and stream
+};
+
+TokenOperand token_operand(const OptTensor& x, const OptTensor& nx_hidden, const OptTensor& nx_ssq,
+                           const OptTensor& nx_weight, double nx_eps, const Tensor& w) {
+  check_cuda(w, "w");
+  AKV_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2, "w must be bfloat16 [features, k]");
+  AKV_CHECK(reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0, "w must be 16-byte aligned");
+  TokenOperand t;
+  if (x.has_value()) {
+    AKV_CHECK(!nx_hidden.has_value(), "give x or the residual stream to norm, not both");
+    check_cuda(*x, "x");
+    AKV_CHECK(x->scalar_type() == at::kBFloat16 && x->dim() == 2 && x->size(1) == w.size(1),
+              "x must be bfloat16 [tokens, k] for w [features, k]");
+    AKV_CHECK(reinterpret_cast<uintptr_t>(x->data_ptr()) % 16 == 0, "x must be 16-byte aligned");
+    t.x = x->data_ptr();
+    t.tokens = x->size(0);
+    t.anchor = &*x;
+  } else {
+    AKV_CHECK(nx_hidden.has_value() && nx_ssq.has_value() && nx_weight.has_value(),
+              "without x the product needs the residual stream, its sums of squares and the norm's weight");
+    check_cuda(*nx_hidden, "hidden");
+    AKV_CHECK(nx_hidden->scalar_type() == at::kFloat && nx_hidden->dim() == 2 && nx_hidden->size(1) == w.size(1),
+              "hidden must be float32 [tokens, k] for w [features, k]");
+    AKV_CHECK(reinterpret_cast<uintptr_t>(nx_hidden->data_ptr()) % 16 == 0, "hidden must be 16-byte aligned");
+    t.tokens = nx_hidden->size(0);
+    check_cuda(*nx_ssq, "ssq");
+    AKV_CHECK(nx_ssq->scalar_type() == at::kFloat && nx_ssq->dim() == 2 && nx_ssq->size(0) >= 1 &&
+                  nx_ssq->size(1) == t.tokens, "ssq must be float32 [tiles, tokens]");
+    check_f32(*nx_weight, "the norm's weight", w.size(1));
+    AKV_CHECK(reinterpret_cast<uintptr_t>(nx_weight->data_ptr()) % 16 == 0, "the norm's weight must be 16-byte aligned");
+    t.is_normed = true;
+    t.normed.hidden = nx_hidden->data_ptr<float>();
+    t.normed.ssq = nx_ssq->data_ptr<float>();
+    t.normed.weight = nx_weight->data_ptr<float>();
+    t.normed.ssq_tiles = (int)nx_ssq->size(0);
+    t.normed.eps = (float)nx_eps;
+    t.anchor = &*nx_hidden;
+  }
+  t.k = w.size(1);
+  AKV_CHECK(w.device() == t.anchor->device(), "w and the token operand must be on the same device");
+  AKV_CHECK(akv::small_m_gemm_supported(t.tokens, w.size(0), t.k),
+            "small_m_gemm takes 1..64 tokens and a K that is a multiple of 8 and at least 64; got ", t.tokens,
+            " tokens, K = ", t.k);
+  return t;
+}
+
+void check_cluster_splits(int64_t splits, int64_t k) {
+  AKV_CHECK((splits == 1 || splits == 2 || splits == 4 || splits == 8) && splits <= (k + 63) / 64,
+            "splits must be 1, 2, 4 or 8 and at most the number of 64-element K blocks, got ", splits);
+}
+
 // x @ w^T for few tokens on the tcgen05 tensor cores.  `out` is either [tokens, features] (float32 or bfloat16:
 // the K splits are added up inside the kernel) or a 3-D float32 [splits, tokens, features] that receives every
-// split's partial sum as it is.
-void small_m_gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t splits, const OptTensor& status,
-                  bool gated) {
-  check_cuda(x, "x");
-  check_cuda(w, "w");
+// split's partial sum as it is.  gated: w holds gate and up rows in alternating runs of 64 and out is
+// silu(gate) * up, [tokens, features / 2] bfloat16.
+void small_m_gemm(const OptTensor& x, const Tensor& w, Tensor& out, int64_t splits, const OptTensor& status,
+                  bool gated, const OptTensor& nx_hidden, const OptTensor& nx_ssq, const OptTensor& nx_weight,
+                  double nx_eps) {
+  const TokenOperand t = token_operand(x, nx_hidden, nx_ssq, nx_weight, nx_eps, w);
   check_cuda(out, "out");
-  AKV_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "x and w must be bfloat16");
-  AKV_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1), "x must be [tokens, k] and w [features, k]");
-  AKV_CHECK(akv::small_m_gemm_supported(x.size(0), w.size(0), x.size(1)),
-            "small_m_gemm takes 1..64 tokens and a K that is a multiple of 8 and at least 64; got ", x.size(0),
-            " tokens, K = ", x.size(1));
-  AKV_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0,
-            "x and w must be 16-byte aligned");
-  const int64_t kb_total = (x.size(1) + 63) / 64;
+  AKV_CHECK(out.device() == w.device(), "out and w must be on the same device");
   void* out_ptr = nullptr;
   float* parts_ptr = nullptr;
   int out_code = 0;
   if (out.dim() == 3) {
-    AKV_CHECK(out.scalar_type() == at::kFloat && out.size(1) == x.size(0) && out.size(2) == w.size(0),
+    AKV_CHECK(out.scalar_type() == at::kFloat && out.size(1) == t.tokens && out.size(2) == w.size(0),
               "a 3-D out must be float32 [splits, tokens, features]");
     splits = out.size(0);
-    AKV_CHECK(splits >= 1 && splits <= kb_total, "splits must be between 1 and the number of 64-element K blocks");
+    AKV_CHECK(splits >= 1 && splits <= (t.k + 63) / 64, "splits must be between 1 and the number of 64-element K blocks");
+    AKV_CHECK(!gated && !t.is_normed, "partial sums come from the plain product of a given x only");
     parts_ptr = out.data_ptr<float>();
-    AKV_CHECK(!gated, "the gated epilogue writes a 2-D bfloat16 out");
   } else {
     if (gated) {
       AKV_CHECK(w.size(0) % 128 == 0 && out.scalar_type() == at::kBFloat16,
                 "the gated epilogue takes a weight of gate and up rows in alternating runs of 64 (rows a multiple "
                 "of 128) and a bfloat16 out");
-      AKV_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) * 2 == w.size(0),
+      AKV_CHECK(out.dim() == 2 && out.size(0) == t.tokens && out.size(1) * 2 == w.size(0),
                 "a gated out must be [tokens, features / 2]");
     } else {
-      AKV_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == w.size(0),
+      AKV_CHECK(out.dim() == 2 && out.size(0) == t.tokens && out.size(1) == w.size(0),
                 "out must be [tokens, features]");
     }
-    AKV_CHECK((splits == 1 || splits == 2 || splits == 4 || splits == 8) && splits <= kb_total,
-              "splits must be 1, 2, 4 or 8 and at most the number of 64-element K blocks, got ", splits);
+    check_cluster_splits(splits, t.k);
     out_code = dtype_code(out, "out");
     out_ptr = out.data_ptr();
   }
-  c10::cuda::CUDAGuard guard(x.device());
-  check_launch(akv::launch_small_m_gemm(x.data_ptr(), w.data_ptr(), out_ptr, out_code, parts_ptr, x.size(0), w.size(0),
-                                        x.size(1), (int)splits, gated ? akv::kEpilogueGated : akv::kEpiloguePlain,
-                                        nullptr, status_ptr(status), stream_of(x)),
+  akv::GemmFusion f;
+  f.epilogue = gated ? akv::kEpilogueGated : akv::kEpiloguePlain;
+  f.normed_x = t.is_normed;
+  f.normed = t.normed;
+  c10::cuda::CUDAGuard guard(w.device());
+  check_launch(akv::launch_small_m_gemm(t.x, w.data_ptr(), out_ptr, out_code, parts_ptr, t.tokens, w.size(0), t.k,
+                                        (int)splits, &f, status_ptr(status), stream_of(*t.anchor)),
                "small_m_gemm");
+}
+
+// The product added to the float32 residual stream in place: hidden [tokens, features] += bfloat16(x @ w^T), and
+// ssq [ceil(features / 128), tokens] receives each 128-feature tile's sum of squares of the new values.
+void small_m_gemm_residual(const Tensor& x, const Tensor& w, Tensor& hidden, Tensor& ssq, int64_t splits,
+                           const OptTensor& status) {
+  const TokenOperand t = token_operand(x, OptTensor(), OptTensor(), OptTensor(), 0.0, w);
+  check_cuda(hidden, "hidden");
+  check_cuda(ssq, "ssq");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2 && hidden.size(0) == t.tokens &&
+                hidden.size(1) == w.size(0) && hidden.device() == w.device(),
+            "hidden must be float32 [tokens, features] on w's device");
+  AKV_CHECK(ssq.scalar_type() == at::kFloat && ssq.dim() == 2 && ssq.size(0) == (w.size(0) + 127) / 128 &&
+                ssq.size(1) == t.tokens && ssq.device() == w.device(),
+            "ssq must be float32 [ceil(features / 128), tokens] on w's device");
+  check_cluster_splits(splits, t.k);
+  akv::GemmFusion f;
+  f.epilogue = akv::kEpilogueResidual;
+  f.residual.hidden = hidden.data_ptr<float>();
+  f.residual.ssq = ssq.data_ptr<float>();
+  c10::cuda::CUDAGuard guard(w.device());
+  check_launch(akv::launch_small_m_gemm(t.x, w.data_ptr(), nullptr, 0, nullptr, t.tokens, w.size(0), t.k, (int)splits,
+                                        &f, status_ptr(status), stream_of(x)),
+               "small_m_gemm_residual");
 }
 
 bool small_m_gemm_supported(int64_t tokens, int64_t features, int64_t k) {
@@ -248,26 +328,20 @@ CacheGeometry check_cache(const Tensor& k_cache, const Tensor& v_cache, int num_
 // The q/k/v projection of few tokens with per-head norm, rotation and the cache write done on the output tile
 // (heads of 128 dims, the whole head rotated or none of it).  q_out [tokens, heads * 128]; K and V go to the
 // slots of the cache pages when slots and caches are given, and are dropped otherwise.
-void small_m_gemm_qkv(const Tensor& x, const Tensor& w, Tensor& q_out, const Tensor& positions,
+void small_m_gemm_qkv(const OptTensor& x, const Tensor& w, Tensor& q_out, const Tensor& positions,
                       const OptTensor& slots, const OptTensor& q_weight, const OptTensor& k_weight,
                       const OptTensor& inv_freq, const OptTensor& k_cache, const OptTensor& v_cache,
-                      int64_t num_heads, int64_t num_kv_heads, double eps, int64_t splits, const OptTensor& status) {
-  check_cuda(x, "x");
-  check_cuda(w, "w");
+                      int64_t num_heads, int64_t num_kv_heads, double eps, int64_t splits, const OptTensor& status,
+                      const OptTensor& nx_hidden, const OptTensor& nx_ssq, const OptTensor& nx_weight,
+                      double nx_eps) {
+  const TokenOperand t = token_operand(x, nx_hidden, nx_ssq, nx_weight, nx_eps, w);
   check_cuda(q_out, "q_out");
-  AKV_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
-                q_out.scalar_type() == at::kBFloat16, "x, w and q_out must be bfloat16");
-  AKV_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1), "x must be [tokens, k] and w [features, k]");
+  AKV_CHECK(q_out.scalar_type() == at::kBFloat16 && q_out.device() == w.device(),
+            "q_out must be bfloat16 on w's device");
   AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && w.size(0) == (num_heads + 2 * num_kv_heads) * 128,
             "w must hold (heads + 2 kv_heads) heads of 128 rows each, got ", w.size(0), " rows");
-  AKV_CHECK(akv::small_m_gemm_supported(x.size(0), w.size(0), x.size(1)),
-            "small_m_gemm takes 1..64 tokens and a K that is a multiple of 8 and at least 64; got ", x.size(0),
-            " tokens, K = ", x.size(1));
-  AKV_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0,
-            "x and w must be 16-byte aligned");
-  const int64_t n = x.size(0), kb_total = (x.size(1) + 63) / 64;
-  AKV_CHECK((splits == 1 || splits == 2 || splits == 4 || splits == 8) && splits <= kb_total,
-            "splits must be 1, 2, 4 or 8 and at most the number of 64-element K blocks, got ", splits);
+  const int64_t n = t.tokens;
+  check_cluster_splits(splits, t.k);
   AKV_CHECK(q_out.is_contiguous() && q_out.numel() == n * num_heads * 128, "q_out must be [tokens, heads * 128]");
   check_i32(positions, "positions", n);
   akv::GemmQkv e{};
@@ -292,9 +366,14 @@ void small_m_gemm_qkv(const Tensor& x, const Tensor& w, Tensor& q_out, const Ten
   e.num_heads = (int)num_heads;
   e.num_kv_heads = (int)num_kv_heads;
   e.eps = (float)eps;
-  c10::cuda::CUDAGuard guard(x.device());
-  check_launch(akv::launch_small_m_gemm(x.data_ptr(), w.data_ptr(), nullptr, 0, nullptr, n, w.size(0), x.size(1),
-                                        (int)splits, akv::kEpilogueQkv, &e, status_ptr(status), stream_of(x)),
+  akv::GemmFusion f;
+  f.epilogue = akv::kEpilogueQkv;
+  f.qkv = e;
+  f.normed_x = t.is_normed;
+  f.normed = t.normed;
+  c10::cuda::CUDAGuard guard(w.device());
+  check_launch(akv::launch_small_m_gemm(t.x, w.data_ptr(), nullptr, 0, nullptr, n, w.size(0), t.k, (int)splits, &f,
+                                        status_ptr(status), stream_of(*t.anchor)),
                "small_m_gemm_qkv");
 }
 
@@ -474,11 +553,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"), py::arg("block") = 0);
   m.def("small_m_gemm", &small_m_gemm, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("splits") = 1,
-        py::arg("status") = py::none(), py::arg("gated") = false);
+        py::arg("status") = py::none(), py::arg("gated") = false, py::arg("nx_hidden") = py::none(),
+        py::arg("nx_ssq") = py::none(), py::arg("nx_weight") = py::none(), py::arg("nx_eps") = 0.0);
+  m.def("small_m_gemm_residual", &small_m_gemm_residual, py::arg("x"), py::arg("w"), py::arg("hidden"),
+        py::arg("ssq"), py::arg("splits") = 1, py::arg("status") = py::none());
   m.def("small_m_gemm_qkv", &small_m_gemm_qkv, py::arg("x"), py::arg("w"), py::arg("q_out"), py::arg("positions"),
         py::arg("slots"), py::arg("q_weight"), py::arg("k_weight"), py::arg("inv_freq"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("eps"), py::arg("splits") = 1,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("nx_hidden") = py::none(), py::arg("nx_ssq") = py::none(),
+        py::arg("nx_weight") = py::none(), py::arg("nx_eps") = 0.0);
   m.def("small_m_gemm_supported", &small_m_gemm_supported);
   m.def("small_m_gemm_splits", &small_m_gemm_splits);
   m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),

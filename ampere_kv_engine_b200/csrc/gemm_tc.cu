@@ -116,7 +116,9 @@ struct GemmParams {
   int kb_total;        // K blocks of 64 in all
   int splits;
   int* status;
-  GemmQkv qkv;         // kEpilogueQkv only
+  GemmQkv qkv;            // kEpilogueQkv only
+  GemmResidual residual;  // kEpilogueResidual only
+  GemmNormedX normed;     // kNormedX only
 };
 
 template <int BN, int kStages>
@@ -127,7 +129,8 @@ struct GemmSmem {
   static constexpr int kReduce = BN * kTileM * 4;                      // float32 partial tile, reuses the stages
   static constexpr int kQkvScratch = (8 + 2 * kTileM) * 4;            // kEpilogueQkv: warp sums and normed values
   static_assert(kReduce + kQkvScratch <= kStages * kStage, "the partial tile must fit in the stage ring");
-  static constexpr int kBytes = kStages * kStage + (2 * kStages + 1) * 8 + 16 + 1024;
+  static constexpr int kBars = (2 * kStages + 1) * 8 + 16;             // barriers, TMEM base
+  static constexpr int kBytes = kStages * kStage + kBars + 64 * 4 + 1024;   // + inverse RMS per token (kNormedX)
 };
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -143,7 +146,11 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-template <int BN, typename OutT, int kStages, int kEpilogue>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, typename OutT, int kStages, int kEpilogue, bool kNormedX>
 __global__ void __launch_bounds__(192)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                     GemmParams p) {
@@ -153,6 +160,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   uint64_t* empty = full + kStages;
   uint64_t* acc_ready = empty + kStages;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  float* inv_rms = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(acc_ready) + 8 + 16);     // [64], kNormedX
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, split = blockIdx.y;
   constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
@@ -165,7 +173,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], kNormedX ? 2 : 1);     // the TMA issuer, and the warp that writes the token tile
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_ready, 1);
@@ -184,20 +192,24 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   bool ok = true;
   float qkv_wd = 1.f, qkv_freq = 0.f, qkv_sn = 0.f, qkv_co = 1.f;     // kEpilogueQkv: fetched ahead of the product
   int64_t qkv_slot = -1;
+  float res_old = 0.f;                                                 // kEpilogueResidual: likewise
 
   if (warp == 0) {
     if (lane == 0) {
       // The weights do not depend on the kernel before this one: fill the ring's weight halves first, then wait
-      // for that kernel and fetch the activations.
+      // for that kernel and fetch the activations.  (kNormedX: warps 2-5 make the token tiles.)
+      constexpr uint32_t kTxBytes = kNormedX ? GemmSmem<BN, kStages>::kA : GemmSmem<BN, kStages>::kStage;
       const int ahead = min(num_kb, kStages);
       for (int kb = 0; kb < ahead; ++kb) {
-        mbar_expect_tx(&full[kb], GemmSmem<BN, kStages>::kStage);
+        mbar_expect_tx(&full[kb], kTxBytes);
         tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage, &w_map, (kb_begin + kb) * kTileK, tile * kTileM, &full[kb]);
       }
-      pdl_wait();
-      for (int kb = 0; kb < ahead; ++kb)
-        tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA, &x_map, (kb_begin + kb) * kTileK, 0,
-                    &full[kb]);
+      if constexpr (!kNormedX) {
+        pdl_wait();
+        for (int kb = 0; kb < ahead; ++kb)
+          tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA, &x_map, (kb_begin + kb) * kTileK, 0,
+                      &full[kb]);
+      }
       for (int kb = ahead; kb < num_kb; ++kb) {
         const int s = kb % kStages;
         if (!mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
@@ -205,10 +217,10 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           break;
         }
         uint8_t* stage = smem + s * GemmSmem<BN, kStages>::kStage;
-        mbar_expect_tx(&full[s], GemmSmem<BN, kStages>::kStage);
+        mbar_expect_tx(&full[s], kTxBytes);
         const int k0 = (kb_begin + kb) * kTileK;
         tma_load_2d(stage, &w_map, k0, tile * kTileM, &full[s]);
-        tma_load_2d(stage + GemmSmem<BN, kStages>::kA, &x_map, k0, 0, &full[s]);
+        if constexpr (!kNormedX) tma_load_2d(stage + GemmSmem<BN, kStages>::kA, &x_map, k0, 0, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -249,6 +261,57 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         sincosf((float)e.positions[split] * qkv_freq, &qkv_sn, &qkv_co);
         if (!is_q && e.slots != nullptr) qkv_slot = e.slots[split];
       }
+    }
+    if constexpr (kNormedX) {
+      // The token operand is the RMS norm of the residual stream, made here: x = hidden * inv_rms * weight,
+      // rounded to bfloat16 and laid out as the TMA would (rows of 128 bytes, 16-byte chunk c of row r at
+      // c ^ (r & 7)).  Warp q makes the K blocks kb = q, q + 4, ...: four blocks are under way at a time.
+      const GemmNormedX& nx = p.normed;
+      pdl_wait();      // hidden and its sums of squares come from the kernels before this one
+      const int t = quarter * 32 + lane;
+      if (t < p.tokens) {
+        float ss = 0.f;
+        for (int i = 0; i < nx.ssq_tiles; ++i) ss += nx.ssq[(int64_t)i * p.tokens + t];
+        inv_rms[t] = rsqrtf(ss / (float)p.k + nx.eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int kb = quarter; kb < num_kb && ok; kb += 4) {
+        const int s = kb % kStages;
+        if (kb >= kStages && !mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+          ok = false;
+          break;
+        }
+        uint8_t* x_tile = smem + s * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA;
+        for (int task = lane; task < p.tokens * 8; task += 32) {
+          const int r = task >> 3, c = task & 7;
+          const int k0 = (kb_begin + kb) * kTileK + c * 8;
+          uint4 packed = make_uint4(0u, 0u, 0u, 0u);       // past the end of K: zeros (the weights' are zeros too)
+          if (k0 < p.k) {
+            float h[8], w[8];
+            load8<float>(nx.hidden + (int64_t)r * p.k + k0, h);
+            load8<float>(nx.weight + k0, w);
+            const float inv = inv_rms[r];
+            uint32_t u[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(h[2 * e] * inv * w[2 * e], h[2 * e + 1] * inv * w[2 * e + 1]);
+              u[e] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            packed = make_uint4(u[0], u[1], u[2], u[3]);
+          }
+          *reinterpret_cast<uint4*>(x_tile + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+      }
+    }
+    if constexpr (kEpilogue == kEpilogueResidual) {
+      // the residual stream's old value for the first token of this CTA's share, fetched while the product runs
+      if constexpr (!kNormedX) pdl_wait();
+      const int feature = tile * kTileM + quarter * 32 + lane;
+      if (split < p.tokens && feature < p.features)
+        res_old = p.residual.hidden[(int64_t)split * p.features + feature];
     }
     if (!mbar_wait(acc_ready, 0)) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -356,6 +419,28 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           }
           if (dst != nullptr) dst[row] = __float2bfloat16_rn(v);
         }
+      } else if constexpr (kEpilogue == kEpilogueResidual) {
+        // hidden += the tile (rounded as the stored product would be); the new values' squares, summed over the
+        // tile's features, are this tile's share of each token's mean square.
+        float* red = reinterpret_cast<float*>(smem + GemmSmem<BN, kStages>::kReduce);      // [2][4] warp sums
+        const int feature = tile * kTileM + row;
+        int it = 0;
+        for (int token = split; token < p.tokens; token += p.splits, ++it) {
+          const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
+          float sum = 0.f;
+          for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+          float h = 0.f;
+          if (feature < p.features) {
+            float* cell = p.residual.hidden + (int64_t)token * p.features + feature;
+            h = (it > 0 ? *cell : res_old) + __bfloat162float(__float2bfloat16_rn(sum));
+            *cell = h;
+          }
+          const float ss = warp_sum(h * h);
+          float* red_it = red + (it & 1) * 4;
+          if (lane == 0) red_it[warp & 3] = ss;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (row == 0) p.residual.ssq[(int64_t)tile * p.tokens + token] = red_it[0] + red_it[1] + red_it[2] + red_it[3];
+        }
       } else {
         const int feature = tile * kTileM + row;
         if (feature < p.features) {
@@ -423,9 +508,9 @@ bool matrix_map(const void* base, int64_t rows, int64_t cols, int box_rows, CUte
   return true;
 }
 
-template <int BN, typename OutT, int kStages, int kEpilogue>
+template <int BN, typename OutT, int kStages, int kEpilogue, bool kNormedX>
 int launch_stages(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = small_m_gemm_kernel<BN, OutT, kStages, kEpilogue>;
+  auto kernel = small_m_gemm_kernel<BN, OutT, kStages, kEpilogue, kNormedX>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, kStages>::kBytes);
@@ -438,7 +523,7 @@ int launch_stages(const CUtensorMap& w_map, const CUtensorMap& x_map, const Gemm
 }
 
 // Stages of the TMA ring.  Four stages of 18-24 KB let three (two at 64 tokens) CTAs share an SM.
-// AKV_GEMM_STAGES=2|4|8 in the environment overrides it for the plain epilogue (for measurements).
+// AKV_GEMM_STAGES=2|4|8 in the environment overrides it for the plain product (for measurements).
 int ring_stages() {
   static const int stages = [] {
     const char* v = getenv("AKV_GEMM_STAGES");
@@ -448,26 +533,36 @@ int ring_stages() {
   return stages;
 }
 
-template <int BN, typename OutT>
-int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue,
+template <int BN, bool kNormedX>
+int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue, bool bf16_out,
               cudaStream_t stream) {
-  if constexpr (sizeof(OutT) == 2) {
-    if (epilogue == kEpilogueGated) return launch_stages<BN, OutT, 4, kEpilogueGated>(w_map, x_map, p, stream);
-    if (epilogue == kEpilogueQkv) return launch_stages<BN, OutT, 4, kEpilogueQkv>(w_map, x_map, p, stream);
+  switch (epilogue) {
+    case kEpilogueGated: return launch_stages<BN, __nv_bfloat16, 4, kEpilogueGated, kNormedX>(w_map, x_map, p, stream);
+    case kEpilogueQkv: return launch_stages<BN, __nv_bfloat16, 4, kEpilogueQkv, kNormedX>(w_map, x_map, p, stream);
+    case kEpilogueResidual:
+      if constexpr (kNormedX) return (int)cudaErrorInvalidValue;
+      else return launch_stages<BN, float, 4, kEpilogueResidual, false>(w_map, x_map, p, stream);
+    default: break;
   }
-  switch (ring_stages()) {
-    case 2: return launch_stages<BN, OutT, 2, kEpiloguePlain>(w_map, x_map, p, stream);
-    case 8: return launch_stages<BN, OutT, 8, kEpiloguePlain>(w_map, x_map, p, stream);
-    default: return launch_stages<BN, OutT, 4, kEpiloguePlain>(w_map, x_map, p, stream);
+  if constexpr (!kNormedX) {
+    const int stages = ring_stages();
+    if (stages == 2)
+      return bf16_out ? launch_stages<BN, __nv_bfloat16, 2, kEpiloguePlain, false>(w_map, x_map, p, stream)
+                      : launch_stages<BN, float, 2, kEpiloguePlain, false>(w_map, x_map, p, stream);
+    if (stages == 8)
+      return bf16_out ? launch_stages<BN, __nv_bfloat16, 8, kEpiloguePlain, false>(w_map, x_map, p, stream)
+                      : launch_stages<BN, float, 8, kEpiloguePlain, false>(w_map, x_map, p, stream);
   }
+  return bf16_out ? launch_stages<BN, __nv_bfloat16, 4, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream)
+                  : launch_stages<BN, float, 4, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream);
 }
 
-template <typename OutT>
-int launch_out(int bn, const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue,
-               cudaStream_t stream) {
-  if (bn == 16) return launch_bn<16, OutT>(w_map, x_map, p, epilogue, stream);
-  if (bn == 32) return launch_bn<32, OutT>(w_map, x_map, p, epilogue, stream);
-  return launch_bn<64, OutT>(w_map, x_map, p, epilogue, stream);
+template <bool kNormedX>
+int launch_tokens(int bn, const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue,
+                  bool bf16_out, cudaStream_t stream) {
+  if (bn == 16) return launch_bn<16, kNormedX>(w_map, x_map, p, epilogue, bf16_out, stream);
+  if (bn == 32) return launch_bn<32, kNormedX>(w_map, x_map, p, epilogue, bf16_out, stream);
+  return launch_bn<64, kNormedX>(w_map, x_map, p, epilogue, bf16_out, stream);
 }
 
 }  // namespace
@@ -487,33 +582,50 @@ int small_m_gemm_splits(int64_t features, int64_t k) {
 }
 
 // out_dtype: akv::DType of `out` when the split partials are reduced inside the kernel; parts (float32
-// [splits, tokens, features]) is written instead when `out` is null.
+// [splits, tokens, features]) is written instead when `out` is null.  `fusion` (null: none) names what else the
+// kernel does: an epilogue on the output tile, a token operand made from the residual stream.
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
-                        int64_t features, int64_t k, int splits, int epilogue, const GemmQkv* qkv, int* status,
+                        int64_t features, int64_t k, int splits, const GemmFusion* fusion, int* status,
                         cudaStream_t stream) {
   if (!small_m_gemm_supported(tokens, features, k) || splits < 1) return (int)cudaErrorInvalidValue;
-  if (epilogue == kEpilogueQkv) {
+  const GemmFusion plain;
+  const GemmFusion& f = fusion != nullptr ? *fusion : plain;
+  if (f.epilogue == kEpilogueQkv) {
     // the results go where qkv says; `out` only selects the in-kernel reduction and is never written
-    if (qkv == nullptr || qkv->q_out == nullptr || parts != nullptr || qkv->positions == nullptr) return (int)cudaErrorInvalidValue;
-    if (features != (int64_t)(qkv->num_heads + 2 * qkv->num_kv_heads) * kTileM) return (int)cudaErrorInvalidValue;
-    out = qkv->q_out;
+    if (f.qkv.q_out == nullptr || parts != nullptr || f.qkv.positions == nullptr) return (int)cudaErrorInvalidValue;
+    if (features != (int64_t)(f.qkv.num_heads + 2 * f.qkv.num_kv_heads) * kTileM) return (int)cudaErrorInvalidValue;
+    out = f.qkv.q_out;
     out_dtype = kBFloat16;
+  } else if (f.epilogue == kEpilogueResidual) {
+    if (f.residual.hidden == nullptr || f.residual.ssq == nullptr || parts != nullptr || f.normed_x)
+      return (int)cudaErrorInvalidValue;
+    out = f.residual.hidden;
+    out_dtype = kFloat32;
+  } else if (f.epilogue == kEpilogueGated) {
+    if (out == nullptr || out_dtype != kBFloat16 || features % kTileM != 0) return (int)cudaErrorInvalidValue;
+  } else if (f.epilogue != kEpiloguePlain) {
+    return (int)cudaErrorInvalidValue;
   }
   if ((out == nullptr) == (parts == nullptr)) return (int)cudaErrorInvalidValue;
-  if (epilogue != kEpiloguePlain && epilogue != kEpilogueGated && epilogue != kEpilogueQkv) return (int)cudaErrorInvalidValue;
-  if (epilogue == kEpilogueGated && (out == nullptr || out_dtype != kBFloat16 || features % kTileM != 0))
+  if (f.normed_x) {
+    if (x != nullptr || f.normed.hidden == nullptr || f.normed.ssq == nullptr || f.normed.weight == nullptr ||
+        f.normed.ssq_tiles < 1 || parts != nullptr)
+      return (int)cudaErrorInvalidValue;
+  } else if (x == nullptr) {
     return (int)cudaErrorInvalidValue;
+  }
   const int bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
   const int kb_total = (int)((k + kTileK - 1) / kTileK);
   if (splits > kb_total) return (int)cudaErrorInvalidValue;
   if (out != nullptr && splits != 1 && splits != 2 && splits != 4 && splits != 8) return (int)cudaErrorInvalidValue;
   CUtensorMap w_map, x_map;
-  if (!matrix_map(w, features, k, kTileM, &w_map) || !matrix_map(x, tokens, k, bn, &x_map))
-    return (int)cudaErrorInvalidValue;
-  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status, {}};
-  if (epilogue == kEpilogueQkv) p.qkv = *qkv;
-  if (out != nullptr && out_dtype == kBFloat16) return launch_out<__nv_bfloat16>(bn, w_map, x_map, p, epilogue, stream);
-  return launch_out<float>(bn, w_map, x_map, p, epilogue, stream);
+  if (!matrix_map(w, features, k, kTileM, &w_map)) return (int)cudaErrorInvalidValue;
+  if (f.normed_x) x_map = w_map;      // unused
+  else if (!matrix_map(x, tokens, k, bn, &x_map)) return (int)cudaErrorInvalidValue;
+  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status, f.qkv, f.residual, f.normed};
+  const bool bf16_out = out != nullptr && out_dtype == kBFloat16;
+  if (f.normed_x) return launch_tokens<true>(bn, w_map, x_map, p, f.epilogue, bf16_out, stream);
+  return launch_tokens<false>(bn, w_map, x_map, p, f.epilogue, bf16_out, stream);
 }
 
 }  // namespace akv

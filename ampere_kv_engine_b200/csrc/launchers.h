@@ -45,7 +45,10 @@ int small_m_gemm_splits(int64_t features, int64_t k);
 //   values, rounded to bfloat16, then go through what launch_qk_norm_rope_write does (per-head RMSNorm of q and
 //   k, rotation of the whole head by position) and land in q_out / the cache pages (GemmQkv); nothing else is
 //   stored.
-enum GemmEpilogue : int { kEpiloguePlain = 0, kEpilogueGated = 1, kEpilogueQkv = 2 };
+//   kEpilogueResidual: the tile, rounded to bfloat16, is added to the float32 residual stream in place
+//   (GemmResidual::hidden [tokens, features]), and the sum of squares of the new values over the tile's 128
+//   features goes to ssq [tiles, tokens]: the next product can then apply the RMS norm itself (GemmNormedX).
+enum GemmEpilogue : int { kEpiloguePlain = 0, kEpilogueGated = 1, kEpilogueQkv = 2, kEpilogueResidual = 3 };
 struct GemmQkv {
   const int32_t* positions;  // [tokens]
   const int32_t* slots;      // [tokens] page * page_size + offset, or -1; null: K and V are not kept
@@ -59,8 +62,29 @@ struct GemmQkv {
   int64_t num_pages;
   float eps;
 };
+struct GemmResidual {
+  float* hidden;             // [tokens, features] float32, updated in place
+  float* ssq;                // [ceil(features / 128), tokens] float32, written
+};
+// The token operand made inside the kernel instead of read from x: x[t, k] = hidden[t, k] * inv_rms[t] * weight[k]
+// rounded to bfloat16, with inv_rms[t] = rsqrt(sum over tiles of ssq[tile, t] / k + eps): the RMS norm of
+// launch_add_rmsnorm applied to a residual stream whose sums of squares a kEpilogueResidual product left behind.
+struct GemmNormedX {
+  const float* hidden;       // [tokens, k] float32
+  const float* ssq;          // [ssq_tiles, tokens]
+  const float* weight;       // [k]
+  int ssq_tiles;
+  float eps;
+};
+struct GemmFusion {
+  int epilogue = kEpiloguePlain;
+  GemmQkv qkv = {};
+  GemmResidual residual = {};
+  bool normed_x = false;     // x is null and normed says how to make it
+  GemmNormedX normed = {};
+};
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
-                        int64_t features, int64_t k, int splits, int epilogue, const GemmQkv* qkv, int* status,
+                        int64_t features, int64_t k, int splits, const GemmFusion* fusion, int* status,
                         cudaStream_t stream);
 
 struct QkRopeWriteParams {

@@ -90,8 +90,11 @@ def gated_linear(x: torch.Tensor, gate_up: torch.Tensor, block: int, status: tor
     """``silu(x @ gate.T) * (x @ up.T)`` with gate and up rows stored in alternating runs of ``block`` (0: all gate
     rows first).  Few bfloat16 tokens and ``block == GATE_UP_RUN``: one tcgen05 kernel that applies the activation
     to its output tile; otherwise the product and the activation kernel."""
-    if block == GATE_UP_RUN and _takes_small_m(x, gate_up) and gate_up.shape[0] % 128 == 0:
-        return small_m_gemm(x, gate_up, status=status, gated=True)
+    x, normed, small = _operand(x, gate_up)
+    if block == GATE_UP_RUN and small and gate_up.shape[0] % 128 == 0:
+        return small_m_gemm(x, gate_up, status=status, gated=True, normed=normed)
+    if normed:
+        return silu_mul(small_m_gemm(None, gate_up, status=status, normed=normed), torch.bfloat16, block)
     return silu_mul(linear(x, gate_up, partial_ok=True, status=status), x.dtype, block)
 
 
@@ -122,16 +125,17 @@ def project_qkv(x, w_qkv, bias, positions, slots, q_weight, k_weight, inv_freq, 
     Few bfloat16 tokens with heads of 128 dims that are rotated whole: one tcgen05 kernel whose 128-row tile is
     one head and does all of it on the tile.  Otherwise the product, then ``qk_norm_rope_write``.
     """
-    if (bias is None and head_dim == 128 and (inv_freq is None or rotary_dim == 128) and _takes_small_m(x, w_qkv)
-            and w_qkv.shape[0] == (num_heads + 2 * num_kv_heads) * 128):
-        splits = ext().small_m_gemm_splits(w_qkv.shape[0], w_qkv.shape[1])
-        while splits not in (1, 2, 4, 8):
-            splits -= 1
-        q_out = torch.empty((x.shape[0], num_heads * 128), dtype=torch.bfloat16, device=x.device)
-        ext().small_m_gemm_qkv(x, w_qkv, q_out, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache,
-                               num_heads, num_kv_heads, float(eps), splits, status)
-        _launched()
-        return q_out
+    on_tile = (bias is None and head_dim == 128 and (inv_freq is None or rotary_dim == 128)
+               and w_qkv.shape[0] == (num_heads + 2 * num_kv_heads) * 128)
+    if on_tile:
+        x, normed, small = _operand(x, w_qkv)
+        if small:
+            q_out = torch.empty((positions.shape[0], num_heads * 128), dtype=torch.bfloat16, device=w_qkv.device)
+            ext().small_m_gemm_qkv(x, w_qkv, q_out, positions, slots, q_weight, k_weight, inv_freq, k_cache,
+                                   v_cache, num_heads, num_kv_heads, float(eps), _cluster_splits(w_qkv), status,
+                                   **normed)
+            _launched()
+            return q_out
     qkv = linear(x, w_qkv, bias, partial_ok=True, status=status)
     return qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, inv_freq, k_cache, v_cache,
                               num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
@@ -204,6 +208,50 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     return tokens
 
 
+class Summed:
+    """What a product leaves behind when it has added its result to the residual stream itself
+    (``linear_into_residual``): ``hidden`` holds the sum already, and ``ssq`` [tiles, tokens] the sums of squares
+    of its new values per 128-feature tile, from which the next RMS norm needs no pass over ``hidden``."""
+
+    def __init__(self, hidden: torch.Tensor, ssq: torch.Tensor):
+        self.hidden, self.ssq = hidden, ssq
+
+
+class LazyNorm:
+    """An RMS norm that is not computed yet: ``hidden * rsqrt(mean(hidden^2) + eps) * weight`` with the sums of
+    squares already known (``Summed``).  ``linear``, ``gated_linear`` and ``project_qkv`` take it in place of a
+    tensor and let the small-batch product kernel apply it to its token operand; ``materialize`` runs the norm
+    kernel."""
+
+    def __init__(self, summed: Summed, weight: torch.Tensor, eps: float, dtype: torch.dtype, status=None):
+        self.hidden, self.ssq, self.weight, self.eps, self.dtype, self.status = (
+            summed.hidden, summed.ssq, weight, float(eps), dtype, status)
+
+    @property
+    def shape(self):
+        return self.hidden.shape
+
+    def materialize(self) -> torch.Tensor:
+        return add_rmsnorm(self.hidden, None, self.weight, self.eps, self.dtype, status=self.status)
+
+
+def _operand(x, weight: torch.Tensor):
+    """(tensor or None, normed-x keyword arguments of the extension, fused?) for a token operand that may be a
+    ``LazyNorm``.  A lazy norm that the small-batch kernel cannot take is materialized."""
+    if not isinstance(x, LazyNorm):
+        return x, {}, _takes_small_m(x, weight)
+    h = x.hidden
+    fused = (use_small_m_gemm and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and h.is_cuda
+             and h.shape[0] <= SMALL_M_LIMIT and h.is_contiguous() and weight.is_contiguous()
+             and h.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.weight.data_ptr() % 16 == 0
+             and h.shape[1] == weight.shape[1]
+             and ext().small_m_gemm_supported(h.shape[0], weight.shape[0], weight.shape[1]))
+    if not fused:
+        t = x.materialize()
+        return t, {}, _takes_small_m(t, weight)
+    return None, {"nx_hidden": h, "nx_ssq": x.ssq, "nx_weight": x.weight, "nx_eps": x.eps}, True
+
+
 #: products of at most this many bfloat16 tokens go through the package's own tcgen05 kernel (the kernel takes
 #: up to 64; measured on B200 the library is faster from 33 tokens on)
 SMALL_M_LIMIT = 32
@@ -212,31 +260,55 @@ use_small_m_gemm = True
 prefer_partials = False
 
 
-def small_m_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+def _cluster_splits(weight: torch.Tensor) -> int:
+    splits = min(ext().small_m_gemm_splits(weight.shape[0], weight.shape[1]), (weight.shape[1] + 63) // 64)
+    while splits not in (1, 2, 4, 8):
+        splits -= 1
+    return splits
+
+
+def small_m_gemm(x: torch.Tensor | None, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                  splits: int | None = None, parts: bool = False, status: torch.Tensor | None = None,
-                 gated: bool = False) -> torch.Tensor:
+                 gated: bool = False, normed: dict | None = None) -> torch.Tensor:
     """``x @ weight.T`` for 1..64 bfloat16 tokens on the tcgen05 tensor cores, K cut into ``splits`` ranges.
 
     Default: [tokens, features] in ``out_dtype`` (float32 or bfloat16); the splits (1, 2, 4 or 8 CTAs of a
     cluster) add their float32 partial tiles up through distributed shared memory.  ``parts=True``: the float32
     partial sums themselves, [splits, tokens, features], for a consumer kernel that adds them up.
     ``gated=True``: ``weight`` holds gate and up rows in alternating runs of 64 and the result is
-    ``silu(gate) * up``, [tokens, features / 2] bfloat16.
+    ``silu(gate) * up``, [tokens, features / 2] bfloat16.  ``normed`` (with ``x`` None): the kernel makes its token
+    operand from a residual stream and its sums of squares (``LazyNorm``).
     """
+    normed = normed or {}
+    tokens = x.shape[0] if x is not None else normed["nx_hidden"].shape[0]
     kb_total = (weight.shape[1] + 63) // 64
     if splits is None:
         splits = ext().small_m_gemm_splits(weight.shape[0], weight.shape[1])
     splits = max(1, min(int(splits), kb_total))
     if parts:
-        out = torch.empty((splits, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        out = torch.empty((splits, tokens, weight.shape[0]), dtype=torch.float32, device=weight.device)
     else:
         while splits not in (1, 2, 4, 8):
             splits -= 1
-        out = torch.empty((x.shape[0], weight.shape[0] // 2 if gated else weight.shape[0]),
-                          dtype=torch.bfloat16 if gated else out_dtype, device=x.device)
-    ext().small_m_gemm(x, weight, out, splits, status, gated)
+        out = torch.empty((tokens, weight.shape[0] // 2 if gated else weight.shape[0]),
+                          dtype=torch.bfloat16 if gated else out_dtype, device=weight.device)
+    ext().small_m_gemm(x, weight, out, splits, status, gated, **normed)
     _launched()
     return out
+
+
+def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor,
+                         status: torch.Tensor | None = None) -> Summed | None:
+    """``hidden += bfloat16(x @ weight.T)`` inside the small-batch product kernel, which also leaves the sums of
+    squares of the new ``hidden`` for the next norm.  None when that kernel does not take the sizes: the caller
+    then computes the product and hands it to the norm as a pending delta."""
+    if not (_takes_small_m(x, weight) and hidden.dtype == torch.float32 and hidden.is_contiguous()
+            and hidden.shape == (x.shape[0], weight.shape[0])):
+        return None
+    ssq = torch.empty(((weight.shape[0] + 127) // 128, x.shape[0]), dtype=torch.float32, device=x.device)
+    ext().small_m_gemm_residual(x, weight, hidden, ssq, _cluster_splits(weight), status)
+    _launched()
+    return Summed(hidden, ssq)
 
 
 def _takes_small_m(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -255,11 +327,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     GEMM, as in the reference.  With ``partial_ok`` the result may be a 3-D float32 stack
     ``[parts, tokens, features]`` of split-K partial sums, for a consumer kernel that adds them up;
     ``out_dtype=torch.float32`` keeps the accumulator's precision in the result (used for the logits).
+    ``x`` may be a ``LazyNorm``.
     """
-    if bias is None and _takes_small_m(x, weight):
-        if partial_ok and prefer_partials:
+    if isinstance(x, LazyNorm) and bias is not None:
+        x = x.materialize()
+    x, normed, small = _operand(x, weight)
+    if bias is None and small:
+        if partial_ok and prefer_partials and not normed:
             return small_m_gemm(x, weight, parts=True, status=status)
-        return small_m_gemm(x, weight, out_dtype=out_dtype or x.dtype, status=status)
+        return small_m_gemm(x, weight, out_dtype=out_dtype or torch.bfloat16, status=status, normed=normed)
     if out_dtype is not None and out_dtype != x.dtype:
         out = torch.mm(x, weight.t(), out_dtype=out_dtype)
         if bias is not None:

@@ -13,7 +13,7 @@ import torch
 
 from ..config.spec import ModelSpec, PartSpec
 from ..parts import attention, block, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheSpec, ParamSpec, build_part)
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, CacheSpec, ParamSpec, build_part)
 from ..parts.embedding import LinearHead, TokenEmbedding
 
 
@@ -100,5 +100,5 @@ class DecoderModel:
             hidden, delta = self.blocks[entry.layer].forward(hidden, delta, ctx, cache_views[pos])
         if ctx.num_logit_rows == 0:
             return None
-        normed = self.final_norm.forward(hidden, delta, ctx, rows=ctx.logit_rows)
+        normed = Block.run_norm(self.final_norm, hidden, delta, ctx, rows=ctx.logit_rows)
         return self.head.forward(normed)

@@ -24,7 +24,8 @@ class PagedAttention(Mixer):
     ``scale`` (None = head_dim ** -0.5), ``position_encoding`` (a PartSpec)."""
 
     graph_safe = True
-
+    takes_lazy_norm = True
+    adds_residual = True
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
@@ -81,7 +82,7 @@ class PagedAttention(Mixer):
             self.q_norm_weight = tensors["q_norm.weight"]
             self.k_norm_weight = tensors["k_norm.weight"]
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, residual=None):
         group = ctx.groups[cache.group]
         slots = group.slot_mapping if cache.writes else None
         k_cache = cache.k_cache if cache.writes else None
@@ -113,4 +114,8 @@ class PagedAttention(Mixer):
             ctx.tile_nq, num_tiles=ctx.num_tiles, q_tile=ctx.q_tile, num_splits=splits,
             num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, window=self.window or 0, scale=self.scale,
             status=ctx.status)
+        if residual is not None and self.b_o is None:
+            summed = ops.linear_into_residual(out, self.w_o, residual, status=ctx.status)
+            if summed is not None:
+                return summed
         return ops.linear(out, self.w_o, self.b_o, partial_ok=True, status=ctx.status)

@@ -18,6 +18,7 @@ from typing import Any, Callable
 import torch
 
 from ..config.spec import PartSpec
+from ..kernels import ops
 
 
 @dataclass(frozen=True)
@@ -87,6 +88,12 @@ class Norm(Part):
         (a split-K product) that are to be added together."""
         raise NotImplementedError
 
+    #: True when ``forward`` also takes a ``Summed`` as ``delta`` (the branch's product kernel has already added
+    #: its result to ``hidden`` and left the sums of squares) and a keyword ``lazy``: with ``lazy=True`` it may
+    #: return a ``LazyNorm`` for a consumer with ``takes_lazy_norm``.  A norm without it is handed ``delta=None``
+    #: in that case, which means the same thing.
+    takes_summed = False
+
 
 class PositionEncoding(Part):
     """How positions enter a mixer.  ``fused_rotary()`` returns ``(inv_freq, rotary_dim)`` when
@@ -102,6 +109,13 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: ``forward`` accepts a ``LazyNorm`` as ``x`` (it hands it to ``ops.linear`` / ``ops.project_qkv``, which let
+    #: the small-batch product kernel apply the norm).
+    takes_lazy_norm = False
+    #: ``forward`` accepts a keyword ``residual`` (the float32 residual stream): it may then add its output there
+    #: itself and return a ``Summed`` instead of the output.
+    adds_residual = False
+
     def cache_spec(self) -> CacheSpec:
         return CacheSpec()
 
@@ -113,6 +127,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_lazy_norm = False     # as for Mixer
+    adds_residual = False
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 
@@ -128,8 +145,26 @@ class Block:
 
     def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx, cache
                 ) -> tuple[torch.Tensor, torch.Tensor | None]:
-        """Takes the residual stream and a not-yet-added branch output; returns the same pair."""
+        """Takes the residual stream and a not-yet-added branch output; returns the same pair.  The branch output
+        may be a ``Summed``: already added by the kernel that made it."""
         raise NotImplementedError
+
+    @staticmethod
+    def run_norm(norm: Norm, hidden, delta, ctx, consumer=None, rows=None):
+        """``norm`` over ``hidden`` (+ ``delta``), lazily if ``delta`` is a ``Summed`` and both the norm and the
+        consumer of its result know how."""
+        if isinstance(delta, ops.Summed):
+            if not norm.takes_summed:
+                return norm.forward(hidden, None, ctx, rows=rows)
+            return norm.forward(hidden, delta, ctx, rows=rows, lazy=bool(getattr(consumer, "takes_lazy_norm", False)))
+        return norm.forward(hidden, delta, ctx, rows=rows)
+
+    @staticmethod
+    def run_branch(part, hidden, *args):
+        """``part.forward(*args)``, with the residual stream offered to a part that can add to it itself."""
+        if part.adds_residual:
+            return part.forward(*args, residual=hidden)
+        return part.forward(*args)
 
 
 class Registry:

@@ -2,7 +2,9 @@
 
 ``prenorm``: ``h += mixer(norm1(h)); h += feed_forward(norm2(h))`` (ampere_kv/runner.py:117-121
 and 156-179).  The residual stream is float32; each branch output is handed to the next norm
-as a pending ``delta`` so that the sum and the norm are one kernel.
+as a pending ``delta`` so that the sum and the norm are one kernel.  On decode steps the branch's
+last product may add to the stream itself and the next product apply the norm (``Summed``,
+``LazyNorm``): then no kernel stands between the two products.
 """
 
 from __future__ import annotations
@@ -13,7 +15,7 @@ from .base import Block, register_block
 @register_block("prenorm")
 class PreNormBlock(Block):
     def forward(self, hidden, delta, ctx, cache):
-        x = self.mixer_norm.forward(hidden, delta, ctx)
-        attn = self.mixer.forward(x, ctx, cache)
-        x = self.feed_forward_norm.forward(hidden, attn, ctx)
-        return hidden, self.feed_forward.forward(x, ctx)
+        x = self.run_norm(self.mixer_norm, hidden, delta, ctx, consumer=self.mixer)
+        attn = self.run_branch(self.mixer, hidden, x, ctx, cache)
+        x = self.run_norm(self.feed_forward_norm, hidden, attn, ctx, consumer=self.feed_forward)
+        return hidden, self.run_branch(self.feed_forward, hidden, x, ctx)

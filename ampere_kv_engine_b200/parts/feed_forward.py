@@ -21,7 +21,8 @@ class GatedMLP(FeedForward):
     """params: ``intermediate_size``, ``activation`` (only ``"silu"``)."""
 
     graph_safe = True
-
+    takes_lazy_norm = True
+    adds_residual = True
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
@@ -49,7 +50,11 @@ class GatedMLP(FeedForward):
             self.gate_up = torch.cat((gate, up), dim=0).contiguous()
         self.down = tensors["down_proj.weight"].contiguous()
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, residual=None):
         status = getattr(ctx, "status", None)
         act = ops.gated_linear(x, self.gate_up, self.run, status=status)
+        if residual is not None:
+            summed = ops.linear_into_residual(act, self.down, residual, status=status)
+            if summed is not None:
+                return summed
         return ops.linear(act, self.down, partial_ok=True, status=status)

@@ -34,6 +34,12 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.weight = tensors["weight"]
 
-    def forward(self, hidden, delta, ctx, rows=None):
-        return ops.add_rmsnorm(hidden, delta, self.weight, self.eps, self.dtype, rows=rows,
-                               status=getattr(ctx, "status", None))
+    takes_summed = True
+
+    def forward(self, hidden, delta, ctx, rows=None, lazy=False):
+        status = getattr(ctx, "status", None)
+        if isinstance(delta, ops.Summed):
+            if lazy and rows is None and self.size == hidden.shape[1]:
+                return ops.LazyNorm(delta, self.weight, self.eps, self.dtype, status)
+            delta = None      # hidden holds the sum already
+        return ops.add_rmsnorm(hidden, delta, self.weight, self.eps, self.dtype, rows=rows, status=status)

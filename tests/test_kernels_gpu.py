@@ -233,6 +233,77 @@ def test_project_qkv_on_the_gemm_tile(ops, tokens, nh, nkv, k, page):
     torch.testing.assert_close(q.float().cpu(), qkv[:, :nh * d].float(), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("tokens,hidden_size,k", [(1, 64, 64), (8, 96, 160), (19, 4096, 512), (32, 1000, 1024)])
+def test_product_adds_to_the_residual_and_the_next_applies_the_norm(ops, tokens, hidden_size, k):
+    """A decode branch ends in a product that adds to the float32 residual stream itself and leaves per-tile sums
+    of squares; the next product makes its token operand from them (the RMS norm inside the kernel).  Both must
+    equal the unfused kernels: product, add + norm, product."""
+    g = torch.Generator().manual_seed(tokens + hidden_size)
+    eps = 1e-5
+    x = torch.randn(tokens, k, generator=g).to(torch.bfloat16)
+    w_out = (torch.randn(hidden_size, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    hidden = 3 * torch.randn(tokens, hidden_size, generator=g)
+    norm_w = 1 + 0.1 * torch.randn(hidden_size, generator=g)
+    h_dev = dev(hidden.clone())
+    status = status_word()
+    summed = ops.linear_into_residual(dev(x), dev(w_out), h_dev, status=status)
+    assert summed is not None and summed.hidden is h_dev and int(status.item()) == 0
+    delta = (x.float() @ w_out.float().t()).to(torch.bfloat16).float()
+    want_hidden = hidden + delta
+    # the product's float32 sums differ from the host's in their last bits, and a bfloat16 rounding may flip
+    torch.testing.assert_close(h_dev.cpu(), want_hidden, atol=2e-2, rtol=2e-2)
+    got_hidden = h_dev.cpu()
+    assert summed.ssq.shape == ((hidden_size + 127) // 128, tokens)
+    torch.testing.assert_close(summed.ssq.sum(0).cpu(), got_hidden.square().sum(-1), atol=1e-3, rtol=1e-5)
+    for tile in range(summed.ssq.shape[0]):
+        torch.testing.assert_close(summed.ssq[tile].cpu(), got_hidden[:, tile * 128:(tile + 1) * 128].square().sum(-1),
+                                   atol=1e-3, rtol=1e-5)
+
+    lazy = ops.LazyNorm(summed, dev(norm_w), eps, torch.bfloat16, status)
+    normed = plain.rms_norm(got_hidden, norm_w, eps).to(torch.bfloat16)
+    torch.testing.assert_close(lazy.materialize().float().cpu(), normed.float(), **tol(torch.bfloat16))
+    if hidden_size % 8:
+        return
+    # plain product of the lazy norm, in both output types
+    w_next = (torch.randn(200, hidden_size, generator=g) * hidden_size ** -0.5).to(torch.bfloat16)
+    want = normed.float() @ w_next.float().t()
+    torch.testing.assert_close(ops.linear(lazy, dev(w_next), out_dtype=torch.float32, status=status).cpu(), want,
+                               atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(ops.linear(lazy, dev(w_next), status=status).float().cpu(), want, atol=4e-2, rtol=4e-2)
+    # gated product
+    gate = (torch.randn(128, hidden_size, generator=g) * hidden_size ** -0.5).to(torch.bfloat16)
+    up = (torch.randn(128, hidden_size, generator=g) * hidden_size ** -0.5).to(torch.bfloat16)
+    gu = ops.interleave_gate_up(gate, up, ops.GATE_UP_RUN).contiguous()
+    gf = (normed.float() @ gate.float().t()).to(torch.bfloat16).float()
+    uf = (normed.float() @ up.float().t()).to(torch.bfloat16).float()
+    torch.testing.assert_close(ops.gated_linear(lazy, dev(gu), ops.GATE_UP_RUN, status=status).float().cpu(),
+                               torch.nn.functional.silu(gf) * uf, atol=4e-2, rtol=4e-2)
+    torch.testing.assert_close(ops.gated_linear(lazy, dev(torch.cat((gate, up))), 0, status=status).float().cpu(),
+                               torch.nn.functional.silu(gf) * uf, atol=4e-2, rtol=4e-2)
+    # q/k/v projection with norm, rotation and cache write on the tile
+    nh, nkv, d, page, pages = 2, 1, 128, 16, 6
+    w_qkv = (torch.randn((nh + 2 * nkv) * d, hidden_size, generator=g) * hidden_size ** -0.5).to(torch.bfloat16)
+    positions = torch.randint(0, 5000, (tokens,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, generator=g)[:tokens].to(torch.int32)
+    q_w, k_w = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    inv_freq = plain.rope_inverse_frequencies(d, 10000.0)
+    k_dev = dev(torch.full((pages, nkv, page, d), float("nan")).to(torch.bfloat16))
+    v_dev = k_dev.clone()
+    q = ops.project_qkv(lazy, dev(w_qkv), None, dev(positions), dev(slots), dev(q_w), dev(k_w), dev(inv_freq), k_dev,
+                        v_dev, num_heads=nh, num_kv_heads=nkv, head_dim=d, rotary_dim=d, eps=eps, status=status)
+    qkv = (normed.float() @ w_qkv.float().t()).to(torch.bfloat16)
+    q_ref, k_ref, v_ref = _qkv_reference(qkv, positions, q_w, k_w, nh, nkv, d, eps, 10000.0)
+    torch.testing.assert_close(q.float().cpu().view(tokens, nh, d), q_ref, atol=4e-2, rtol=4e-2)
+    for t_ in range(tokens):
+        s_ = int(slots[t_])
+        torch.testing.assert_close(k_dev.float().cpu()[s_ // page, :, s_ % page], k_ref[t_], atol=4e-2, rtol=4e-2)
+        torch.testing.assert_close(v_dev.float().cpu()[s_ // page, :, s_ % page], v_ref[t_], atol=4e-2, rtol=4e-2)
+    assert int(status.item()) == 0
+    # more tokens than the small-batch kernel takes, or float32: the caller keeps the unfused route
+    big = dev(torch.zeros(ops.SMALL_M_LIMIT + 1, k, dtype=torch.bfloat16))
+    assert ops.linear_into_residual(big, dev(w_out), dev(torch.zeros(ops.SMALL_M_LIMIT + 1, hidden_size))) is None
+
+
 def test_qk_partial_rotation_and_no_rotation(ops):
     """rotary_dim < head_dim rotates pairs (j, j + rotary_dim/2) of the first rotary_dim dims only; no table = no rotation."""
     g = torch.Generator().manual_seed(4)
