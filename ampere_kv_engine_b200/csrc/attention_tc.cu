@@ -703,7 +703,6 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();      // q and this step's K/V pages come from the previous kernels
 
   bool ok = true;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
@@ -713,7 +712,17 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
 
   if (is_producer) {
     TableWindow window{p.block_table + (int64_t)seq * p.table_width, p.table_width, -1, -1};
-    for (int b = 0; b < num_blocks; ++b) {
+    // Keys before this step's tokens were written by earlier steps: their blocks are fetched while the previous
+    // kernel (which writes this step's K and V) still runs, as far as the ring has room.
+    const int first_new = ctx - q_len;
+    int b = 0;
+    if (tp.use_tma) {
+      for (; b < num_blocks && b < STAGES && min(range_lo + (b + 1) * KT, range_hi) <= first_new; ++b)
+        issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + b * Layout::kStage,
+                           &full[b], 0, 1);
+    }
+    pdl_wait();      // this step's K/V pages come from the previous kernels
+    for (; b < num_blocks; ++b) {
       const int s = b % STAGES;
       if (b >= STAGES && !mbar_wait(&empty[s], ((b / STAGES) - 1) & 1)) {
         ok = false;
@@ -726,6 +735,7 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
         issue_block_cp<D, KT>(tp, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage, &full[s]);
     }
   } else {
+    pdl_wait();      // q comes from the previous kernel
     // query fragments: rows are the heads of the group (row < G), all D/16 k-steps
     const int row_a = lane >> 2, row_b = row_a + 8;
     uint32_t q_frag[D / 16][4];
@@ -1024,10 +1034,12 @@ int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& 
 }
 
 // Shape of the decode kernel's CTAs: (TMA ring stages of 16 KB at head size 128, consumer warps).  One CTA
-// streams pages at 13-15 GB/s whatever its ring depth (measured on B200), so bandwidth comes from CTAs per SM.
-// Few CTAs in flight (small batches): 2 stages x 2 warps, the smallest CTA, which also shares an SM best with the
-// next kernel's early CTAs; enough CTAs to fill the GPU: 3 stages x 4 warps.  Measured: batch 8 step 3.73 ms vs
-// 3.94 ms, batch 64 kernel 59.7 us vs 64.9 us.  AKV_ATTN_CONFIG=2|3|4|6 forces (2,2) | (3,4) | (2,4) | (3,2).
+// streams pages at 13-15 GB/s whatever its ring depth (measured on B200), so bandwidth comes from CTAs per SM,
+// and a cluster's CTAs must all fit at once: rings of 4 or more stages (64 KB and up) made the batch-8 kernel
+// 25 us instead of 15 us.  3 stages x 4 warps is the default: since the producer fetches the blocks of old keys
+// before it waits for the previous kernel, the third stage pays (measured per step: batch 8 3.49 ms vs 3.53 ms
+// with 2 x 2, batch 1 3.18 vs 3.27 ms, batch 64 5.61 vs 5.80 ms).  AKV_ATTN_CONFIG=2|3|4|6 forces
+// (2,2) | (3,4) | (2,4) | (3,2).
 int decode_config(int64_t ctas) {
   static const int forced = [] {
     const char* v = getenv("AKV_ATTN_CONFIG");
@@ -1035,7 +1047,8 @@ int decode_config(int64_t ctas) {
     return (n == 2 || n == 3 || n == 4 || n == 6) ? n : 0;
   }();
   if (forced) return forced;
-  return ctas >= 148 * 4 ? 3 : 2;
+  (void)ctas;
+  return 3;
 }
 
 }  // namespace
