@@ -89,14 +89,23 @@ Tensor smoke_add(const Tensor& a, const Tensor& b) {
   return out;
 }
 
-void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const OptTensor& status) {
+void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const OptTensor& status,
+               const OptTensor& sampled) {
   check_cuda(table, "table");
   AKV_CHECK(table.dim() == 2, "table must be [vocab, hidden]");
   const int64_t n = ids.numel(), h = table.size(1);
   check_i32(ids, "ids");
   check_f32(hidden, "hidden", n * h);
+  const int* sampled_ptr = nullptr;
+  int64_t num_sampled = 0;
+  if (sampled.has_value()) {
+    check_i32(*sampled, "sampled");
+    sampled_ptr = sampled->data_ptr<int>();
+    num_sampled = sampled->numel();
+  }
   c10::cuda::CUDAGuard guard(table.device());
-  check_launch(akv::launch_embedding(ids.data_ptr<int>(), table.data_ptr(), hidden.data_ptr<float>(), n, h,
+  check_launch(akv::launch_embedding(ids.data_ptr<int>(), sampled_ptr, num_sampled, table.data_ptr(),
+                                     hidden.data_ptr<float>(), n, h,
                                      table.size(0), dtype_code(table, "table"), status_ptr(status),
                                      stream_of(table)),
                "embedding");
@@ -548,7 +557,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the engine";
   namespace py = pybind11;
   m.def("smoke_add", &smoke_add, "a + b on the device (toolchain check)");
-  m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("hidden"), py::arg("status") = py::none());
+  m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("hidden"), py::arg("status") = py::none(),
+        py::arg("sampled") = py::none());
   m.def("add_rmsnorm", &add_rmsnorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
         py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"), py::arg("block") = 0);

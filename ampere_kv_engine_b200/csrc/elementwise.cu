@@ -36,13 +36,15 @@ int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cuda
 }
 
 template <typename T>
-__global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ hidden, int64_t hidden_size, int64_t vocab,
-                                 int* status) {
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ sampled,
+                                 int64_t num_sampled, const T* __restrict__ table, float* __restrict__ hidden,
+                                 int64_t hidden_size, int64_t vocab, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t token = blockIdx.x;
   int64_t id = ids[token];
+  // -(r + 1): the token that the previous step chose in its row r, which the host has not read yet
+  if (id < 0 && sampled != nullptr && -id - 1 < num_sampled) id = sampled[-id - 1];
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) set_status(status, kBadToken);
     id = 0;
@@ -52,15 +54,18 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
   for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) dst[i] = to_float<T>(row[i]);
 }
 
-int launch_embedding(const int32_t* ids, const void* table, float* hidden, int64_t num_tokens,
-                     int64_t hidden_size, int64_t vocab, int dtype, int* status, cudaStream_t stream) {
+int launch_embedding(const int32_t* ids, const int32_t* sampled, int64_t num_sampled, const void* table,
+                     float* hidden, int64_t num_tokens, int64_t hidden_size, int64_t vocab, int dtype, int* status,
+                     cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   const int threads = (int)(hidden_size >= 1024 ? 256 : (hidden_size >= 128 ? 128 : 32));
   if (dtype == kBFloat16)
     return (int)launch_chain(embedding_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(threads), 0, stream,
-                             dim3(1, 1, 1), ids, (const __nv_bfloat16*)table, hidden, hidden_size, vocab, status);
+                             dim3(1, 1, 1), ids, sampled, num_sampled, (const __nv_bfloat16*)table, hidden, hidden_size,
+                             vocab, status);
   return (int)launch_chain(embedding_kernel<float>, dim3((unsigned)num_tokens), dim3(threads), 0, stream,
-                           dim3(1, 1, 1), ids, (const float*)table, hidden, hidden_size, vocab, status);
+                           dim3(1, 1, 1), ids, sampled, num_sampled, (const float*)table, hidden, hidden_size, vocab,
+                           status);
 }
 
 // ---------------------------------------------------------------------------------------------------------

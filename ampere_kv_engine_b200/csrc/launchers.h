@@ -14,9 +14,11 @@ namespace akv {
 
 int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream);
 
-// hidden[n, :] = float(table[ids[n], :])
-int launch_embedding(const int32_t* ids, const void* table, float* hidden, int64_t num_tokens,
-                     int64_t hidden_size, int64_t vocab, int dtype, int* status, cudaStream_t stream);
+// hidden[n, :] = float(table[ids[n], :]).  With `sampled` (may be null), an id of -(r + 1) stands for sampled[r]:
+// the token the previous step chose in its row r, still on the device.
+int launch_embedding(const int32_t* ids, const int32_t* sampled, int64_t num_sampled, const void* table,
+                     float* hidden, int64_t num_tokens, int64_t hidden_size, int64_t vocab, int dtype, int* status,
+                     cudaStream_t stream);
 
 // hidden += delta (if delta); out = rmsnorm(hidden) * weight.  With `rows` (num_rows entries)
 // only those rows are read, hidden is left untouched and out is [num_rows, hidden_size].

@@ -26,6 +26,9 @@ class SeqStep:
     seq: SequenceCache
     tokens: list[int]
     want: list[int] = field(default_factory=list)
+    #: set when the entry's single token is the one the previous step chose in its row ``source`` and the host
+    #: has not read it yet: the embedding takes it from the device (``tokens`` is then a placeholder)
+    source: int | None = None
 
 
 @dataclass
@@ -56,6 +59,7 @@ class StepContext:
     max_context: int                # longest ctx_lens entry (host value)
     groups: list[GroupBatch]
     status: torch.Tensor | None     # int32[1] the kernels report bad indices in
+    sampled: torch.Tensor | None = None   # int32 tokens the previous step chose (for entries with a ``source``)
     # host copies, for parts that loop over sequences themselves
     q_lens_host: list[int] = field(default_factory=list)
     ctx_lens_host: list[int] = field(default_factory=list)
@@ -116,7 +120,7 @@ def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout
         host[off[index]:off[index] + len(values)] = values
 
     host[off[0]:off[0] + layout.num_tokens] = 0
-    put(0, [t for e in entries for t in e.tokens])
+    put(0, [-(e.source + 1) if e.source is not None else t for e in entries for t in e.tokens])
     host[off[1]:off[1] + layout.num_tokens] = 0
     put(1, np.concatenate([np.arange(s, c, dtype=np.int64) for s, c in zip(starts, ctx_lens)]))
     put(2, cu)
@@ -156,7 +160,7 @@ def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout
 
 def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_context: int,
                  status: torch.Tensor | None, q_lens: list[int], ctx_lens: list[int], state_slots: list[int],
-                 h2d_bytes: int) -> StepContext:
+                 h2d_bytes: int, sampled: torch.Tensor | None = None) -> StepContext:
     """Views into the device copy ``dev`` of a filled index buffer."""
     off = layout.offsets
 
@@ -173,8 +177,8 @@ def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_
         state_slots=view(4, layout.num_seqs), logit_rows=view(5, layout.num_logit_rows),
         num_logit_rows=layout.num_logit_rows, tile_seq=view(6, layout.num_tiles), tile_q0=view(7, layout.num_tiles),
         tile_nq=view(8, layout.num_tiles), num_tiles=layout.num_tiles, q_tile=tile_rows, max_context=max_context,
-        groups=groups, status=status, q_lens_host=q_lens, ctx_lens_host=ctx_lens, state_slots_host=state_slots,
-        h2d_bytes=h2d_bytes)
+        groups=groups, status=status, sampled=sampled, q_lens_host=q_lens, ctx_lens_host=ctx_lens,
+        state_slots_host=state_slots, h2d_bytes=h2d_bytes)
 
 
 def validate_entries(entries: list[SeqStep]) -> None:
@@ -183,6 +187,9 @@ def validate_entries(entries: list[SeqStep]) -> None:
     for e in entries:
         if not e.tokens:
             raise ValueError("every entry of a step needs at least one token")
+        if e.source is not None and (len(e.tokens) != 1 or e.source < 0):
+            raise ValueError(f"request {e.seq.request_id!r}: a token taken from the previous step's choices is "
+                             f"the entry's only token")
         for w in e.want:
             if not 0 <= w < len(e.tokens):
                 raise ValueError(f"request {e.seq.request_id!r}: wanted place {w} is outside its "
@@ -197,7 +204,8 @@ def exact_layout(manager: CacheManager, entries: list[SeqStep], tile_rows: int) 
 
 
 def build_context(manager: CacheManager, entries: list[SeqStep], device: torch.device,
-                  status: torch.Tensor | None = None, q_tile: int | None = None) -> StepContext:
+                  status: torch.Tensor | None = None, q_tile: int | None = None,
+                  sampled: torch.Tensor | None = None) -> StepContext:
     """Lay out the step exactly (no padding) and copy it to the device in one transfer.  Every entry's pages
     must already be reserved for its new tokens."""
     validate_entries(entries)
@@ -211,4 +219,5 @@ def build_context(manager: CacheManager, entries: list[SeqStep], device: torch.d
         staged = staged.pin_memory()
     dev = staged.to(device, non_blocking=True)
     return make_context(layout, dev, tile_rows=tile_rows, max_context=max(ctx_lens), status=status, q_lens=q_lens,
-                        ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries], h2d_bytes=int(host.nbytes))
+                        ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries], h2d_bytes=int(host.nbytes),
+                        sampled=sampled)

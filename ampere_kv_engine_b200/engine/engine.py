@@ -67,6 +67,12 @@ class Engine:
         self.admission = admission
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self._stream_counter = 0
+        # pinned landing places of the chosen tokens (+ the status word); two, since one step may be in flight
+        # while the one before it is read
+        self._readback = [torch.zeros(max_seqs + 2, dtype=torch.int32) for _ in range(3)]
+        if self.device.type == "cuda":
+            self._readback = [t.pin_memory() for t in self._readback]
+        self._readback_turn = 0
 
     # ------------------------------------------------------------------ construction
 
@@ -91,13 +97,43 @@ class Engine:
     # ------------------------------------------------------------------ executor interface (for the scheduler)
 
     def execute(self, entries: list[SeqStep], wanted: list[Request]) -> list[int]:
+        """Run the batch and return the chosen token of every wanted request (blocks until the device is done)."""
+        return self.collect(self.launch(entries, wanted, [len(r.output_ids) for r in wanted]))
+
+    def launch(self, entries: list[SeqStep], wanted: list[Request], steps: list[int]):
+        """Enqueue the batch and the choice of its tokens without waiting for either.  ``steps``: the index of the
+        token being chosen within each wanted request (the sampler's draw depends on it).  The chosen tokens stay
+        on the device (``runner.sampled``, row i for ``wanted[i]``), where the next step's entries with a
+        ``source`` find them, and travel to a pinned host buffer that :meth:`collect` reads."""
         logits = self.runner.step(entries)
         if logits is None:
+            return None
+        tokens = self.sampler.sample(logits, [r.sampling for r in wanted], steps)
+        count = tokens.shape[0]
+        self.runner.sampled[:count].copy_(tokens)
+        slot = self._readback[self._readback_turn]
+        self._readback_turn = (self._readback_turn + 1) % len(self._readback)
+        # one read-back: the tokens and the kernels' status word
+        if self.device.type == "cuda":
+            slot[:count].copy_(tokens, non_blocking=True)
+            slot[count:count + 1].copy_(self.runner.status, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        else:
+            slot[:count].copy_(tokens)
+            slot[count:count + 1].copy_(self.runner.status)
+            done = None
+        return slot, count, done
+
+    def collect(self, handle) -> list[int]:
+        """The tokens of a launched batch, once the device has them."""
+        if handle is None:
             self.runner.raise_on_status()
             return []
-        tokens = self.sampler.sample(logits, [r.sampling for r in wanted], [len(r.output_ids) for r in wanted])
-        packed = torch.cat((tokens, self.runner.status))     # one read-back: the tokens and the kernels' status word
-        host = packed.tolist()
+        slot, count, done = handle
+        if done is not None:
+            done.synchronize()
+        host = slot[:count + 1].tolist()
         if host[-1]:
             self.runner.raise_on_status()
         return host[:-1]

@@ -24,6 +24,17 @@ A request alone in the engine that still cannot be backed is finished with reaso
 The scheduler is host logic only.  It talks to an *executor* with three members:
 ``manager`` (the :class:`CacheManager`), ``execute(entries, requests) -> list[int]`` (run the
 batch, choose a token for every entry that wants one, in order) and ``vocab_size``.
+
+An executor that also has ``launch(entries, requests, steps) -> handle`` and
+``collect(handle) -> list[int]`` is driven one round ahead: round k + 1 is laid out and queued
+on the device before round k's tokens are read, so the host's work hides behind the device's.
+A request whose newest token is still on the device contributes an entry with a ``source``
+(the row of that token among round k's choices) instead of a token id.  What the host cannot
+know a round early is an EOS: a request that turns out to have ended in round k has one
+speculative token computed in round k + 1, which is dropped (its pages go back as always; the
+device runs rounds in order, so nobody else sees those pages before round k + 1 is through).
+A request that ends by its token limit is not scheduled speculatively.  When pages run short
+the round in flight is read first, so preemption decides with everything known.
 """
 
 from __future__ import annotations
@@ -55,6 +66,7 @@ class Request:
         self.budget: list[int] = []         # pages per group reserved at admission (budget policy)
         self.preemptions = 0
         self.admit_order = -1
+        self.inflight_row: int | None = None    # row of this request's newest token in the round not yet read
 
     @property
     def tokens(self) -> list[int]:
@@ -81,7 +93,8 @@ class StepStats:
 
 class Scheduler:
     def __init__(self, executor, *, max_batch_tokens: int = 2048, max_seqs: int = 256,
-                 eos_token_ids=(), admission: str = "budget", max_context: int | None = None):
+                 eos_token_ids=(), admission: str = "budget", max_context: int | None = None,
+                 lookahead: bool | None = None):
         if max_batch_tokens < 1 or max_seqs < 1:
             raise ValueError("max_batch_tokens and max_seqs must be positive")
         if admission not in ("budget", "optimistic"):
@@ -99,6 +112,11 @@ class Scheduler:
         self.reserved = [0] * len(self.manager.groups)
         self._admitted = 0
         self.preemptions = 0
+        can_look_ahead = hasattr(executor, "launch") and hasattr(executor, "collect")
+        #: queue each round before the previous round's tokens are read (None: whenever the executor can)
+        self.lookahead = can_look_ahead if lookahead is None else bool(lookahead) and can_look_ahead
+        self._inflight = None       # (handle, wanted requests) of the queued round whose tokens are not read yet
+        self.dropped_tokens = 0     # speculative tokens of requests that had already ended
 
     # ------------------------------------------------------------------ public
 
@@ -132,7 +150,7 @@ class Scheduler:
             request.stop_reason = request.stop_reason or "cancelled"
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.prefilling or self.running)
+        return bool(self.waiting or self.prefilling or self.running or self._inflight is not None)
 
     def step(self, now: float | None = None) -> tuple[list[Request], StepStats]:
         """One round.  Returns the requests that finished in it (each exactly once) and what ran."""
@@ -141,6 +159,24 @@ class Scheduler:
         self._admit()
         stats = StepStats()
         entries, owners = self._build_batch(stats, finished)
+        if self.lookahead:
+            launched = None
+            if entries:
+                wanted = [r for r, e in zip(owners, entries) if e.want]
+                steps = [len(r.output_ids) + (r.inflight_row is not None) for r in wanted]
+                launched = (self.executor.launch(entries, wanted, steps), wanted)
+                for request in owners:      # the whole prompt is in the cache (or on its way): it decodes from now on
+                    if request.status == PREFILLING and request.computed >= len(request.tokens):
+                        self.prefilling.remove(request)
+                        request.status = RUNNING
+                        self.running.append(request)
+            self._collect(finished)         # the round before, now that this one is queued behind it
+            if launched is not None:
+                self._inflight = launched
+                for row, request in enumerate(launched[1]):
+                    request.inflight_row = row
+            stats.free_pages = self.manager.free_pages()
+            return finished, stats
         if entries:
             wanted = [r for r, e in zip(owners, entries) if e.want]
             tokens = self.executor.execute(entries, wanted)
@@ -194,6 +230,26 @@ class Scheduler:
                 self.reserved = [r + b for r, b in zip(self.reserved, request.budget)]
             self.prefilling.append(request)
 
+    def _collect(self, finished: list[Request]) -> None:
+        """Read the tokens of the round in flight, if any, and do what ``step`` does after a round."""
+        if self._inflight is None:
+            return
+        handle, wanted = self._inflight
+        self._inflight = None
+        tokens = self.executor.collect(handle)
+        if len(tokens) != len(wanted):
+            raise RuntimeError("the executor returned a token count that does not match the batch")
+        for request, token in zip(wanted, tokens):
+            request.inflight_row = None
+            if request.status == FINISHED or request.stop_reason:
+                self.dropped_tokens += 1        # it had ended before this round ran
+                continue
+            self._commit(request, int(token))
+        for request in wanted:
+            if request.stop_reason and request.status != FINISHED:
+                self._retire(request)
+                finished.append(request)
+
     def _plan(self) -> list[tuple[Request, int, int]]:
         """(request, first token index, count) for this round under the token budget."""
         plan = []
@@ -201,6 +257,8 @@ class Scheduler:
         for request in self.running:
             if budget <= 0:
                 break
+            if request.inflight_row is not None and len(request.output_ids) + 1 >= request.max_new_tokens:
+                continue        # the token in flight is its last
             plan.append((request, request.computed, 1))
             budget -= 1
         for request in self.prefilling:
@@ -224,6 +282,9 @@ class Scheduler:
                     need[gi] += n
             if all(n <= g.pool.num_free for n, g in zip(need, self.manager.groups)):
                 break
+            if self._inflight is not None:
+                self._collect(finished)     # decide with everything known: requests may just have ended
+                continue
             live = self._live()
             victim = max(live, key=lambda r: r.admit_order)
             if len(live) == 1:
@@ -235,9 +296,13 @@ class Scheduler:
                 stats.preempted += 1
         entries, owners = [], []
         for request, start, count in plan:
-            tokens = request.tokens[start:start + count]
-            last = start + count == len(request.tokens)
-            entries.append(SeqStep(request.seq, tokens, [count - 1] if last else []))
+            if request.inflight_row is not None:
+                # its next token is the one the round in flight chooses
+                entries.append(SeqStep(request.seq, [0], [0], source=request.inflight_row))
+            else:
+                tokens = request.tokens[start:start + count]
+                last = start + count == len(request.tokens)
+                entries.append(SeqStep(request.seq, tokens, [count - 1] if last else []))
             owners.append(request)
             if request.status == RUNNING:
                 stats.decode_tokens += count

@@ -80,6 +80,8 @@ class ModelRunner:
                                     max_seqs=max_seqs, dtype=kv_dtype, device=self.device)
         self.views = self.manager.layer_views()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        #: the tokens the last step chose, kept on the device: an entry with a ``source`` reads its token here
+        self.sampled = torch.zeros(max(1, max_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.last_h2d_bytes = 0
         #: decode-only steps are replayed as CUDA graphs (one per batch-size and table-width bucket)
@@ -117,7 +119,7 @@ class ModelRunner:
             if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= _SEQ_BUCKETS[-1]:
                 logits = self._decode_step_captured(entries)
             else:
-                ctx = build_context(self.manager, entries, self.device, status=self.status)
+                ctx = build_context(self.manager, entries, self.device, status=self.status, sampled=self.sampled)
                 self.last_h2d_bytes = ctx.h2d_bytes
                 logits = self.model.forward(ctx, self.views)
         except BaseException:
@@ -144,7 +146,7 @@ class ModelRunner:
     def _decode_step_captured(self, entries: list[SeqStep]) -> torch.Tensor | None:
         layout = self._decode_layout(entries)
         captured = self._captured.get(layout.key())
-        full = [SeqStep(e.seq, e.tokens, [0]) for e in entries]
+        full = [SeqStep(e.seq, e.tokens, [0], e.source) for e in entries]
         if captured is None:
             captured = self._capture(layout, full)
         else:
@@ -171,7 +173,7 @@ class ModelRunner:
         max_context = max(layout.widths) * self.manager.page_size
         ctx = make_context(layout, dev, tile_rows=1, max_context=max_context, status=self.status,
                            q_lens=q_lens, ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries],
-                           h2d_bytes=int(layout.total * 4))
+                           h2d_bytes=int(layout.total * 4), sampled=self.sampled)
         # one eager run first (library handles and workspaces come into being outside the capture); it writes the
         # same cache slots the captured run writes again
         self.model.forward(ctx, self.views)

@@ -39,10 +39,12 @@ def smoke_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return ext().smoke_add(a, b)
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
-    """float32 residual stream [tokens, hidden] gathered from ``table`` rows."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor | None = None,
+              sampled: torch.Tensor | None = None) -> torch.Tensor:
+    """float32 residual stream [tokens, hidden] gathered from ``table`` rows.  With ``sampled`` (int32, on the
+    device) an id of ``-(r + 1)`` stands for ``sampled[r]``: the token the previous step chose in its row r."""
     hidden = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
-    ext().embedding(ids, table, hidden, status)
+    ext().embedding(ids, table, hidden, status, sampled)
     _launched()
     return hidden
 

@@ -31,7 +31,8 @@ class TokenEmbedding(Part):
         self.weight = tensors["weight"].contiguous()
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.embedding(token_ids, self.weight, status=getattr(ctx, "status", None))
+        return ops.embedding(token_ids, self.weight, status=getattr(ctx, "status", None),
+                             sampled=getattr(ctx, "sampled", None))
 
 
 class LinearHead(Part):

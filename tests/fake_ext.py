@@ -18,8 +18,11 @@ class FakeExt:
     def smoke_add(self, a, b):
         return a + b
 
-    def embedding(self, ids, table, hidden, status=None):
-        hidden.copy_(table[ids.long()].float())
+    def embedding(self, ids, table, hidden, status=None, sampled=None):
+        ids = ids.long()
+        if sampled is not None:
+            ids = torch.where(ids < 0, sampled.long()[(-ids - 1).clamp(min=0)], ids)
+        hidden.copy_(table[ids].float())
 
     def add_rmsnorm(self, hidden, delta, weight, out, rows, eps, status=None):
         if delta is not None and delta.dim() == 3:

@@ -96,6 +96,35 @@ def test_temperature_sampling_reproducible_and_batch_independent():
         ids.append(token)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rounds_queued_ahead_choose_the_same_tokens(dtype):
+    """The scheduler queues a round before it has read the tokens of the one before (they reach the next round's
+    embedding on the device).  Round by round or ahead: the same tokens, also across an EOS, whose speculative
+    successor is dropped."""
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = tiny.CONFIGS["B"]
+    engine = Engine.from_pretrained(model_folder("B"), dtype=dtype, page_size=page, num_pages=64, max_batch_tokens=40)
+    prompts = prompts_for("B", (3, 50, 64, 21), seed=11)
+    free_run = engine.generate(prompts, max_new_tokens=20, temperature=0.7, seed=5, ignore_eos=True)
+    eos = free_run[1][6]
+    results = {}
+    for ahead in (False, True):
+        scheduler = engine.new_scheduler(lookahead=ahead, eos_token_ids=(eos,))
+        from ampere_kv_engine_b200.sampling.sampler import SamplingParams
+        requests = [scheduler.submit(i, p, 20, sampling=SamplingParams(0.7, 5, stream=i)) for i, p in enumerate(prompts)]
+        while scheduler.has_work():
+            scheduler.step()
+        results[ahead] = [r.output_ids for r in requests]
+        assert all(r.stop_reason in ("eos", "length") for r in requests)
+        if ahead:
+            assert scheduler.dropped_tokens >= 1
+        assert engine.manager.free_pages() == [64] * len(engine.manager.groups)
+    assert results[True] == results[False]
+    for run, full in zip(results[True], free_run):
+        cut = full.index(eos) + 1 if eos in full else len(full)
+        assert run == full[:cut]
+
+
 def test_requests_wait_for_pages_and_all_finish():
     """Pages for two requests at a time only: the others wait in arrival order; all finish with the tokens they
     get when run alone; every page comes back."""

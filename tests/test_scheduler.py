@@ -221,3 +221,92 @@ def test_stats_report_what_ran():
     _, st = s.step(now=0.0)
     assert (st.prefill_tokens, st.decode_tokens, st.num_seqs, st.batch_tokens) == (19, 1, 2, 20)
     assert st.free_pages == ex.manager.free_pages()
+
+
+class AheadExecutor(StubExecutor):
+    """The stub with ``launch`` / ``collect``: a round's tokens become readable only at ``collect``, and an entry
+    with a ``source`` takes its token from the previous round's choices, as the device does."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.sampled: list[int] = []
+        self.launched = self.collected = 0
+
+    def launch(self, entries, wanted, steps):
+        assert self.launched - self.collected <= 1, "at most one round may be unread when the next is queued"
+        assert len(steps) == len(wanted)
+        resolved = []
+        for e in entries:
+            if e.source is not None:
+                assert e.tokens == [0] and e.want == [0]
+                e = type(e)(e.seq, [self.sampled[e.source]], e.want)
+            resolved.append(e)
+        tokens = StubExecutor.execute(self, resolved, wanted)
+        self.sampled = list(tokens)
+        self.launched += 1
+        return list(tokens)
+
+    def collect(self, handle):
+        self.collected += 1
+        return handle
+
+
+def test_lookahead_gives_the_same_tokens_and_frees_everything():
+    prompts = [prompt(10), prompt(33, 3), prompt(5, 9), prompt(47, 1)]
+    limits = [5, 1, 12, 2]
+    outs = {}
+    for ahead in (False, True):
+        ex = AheadExecutor(pages=64)
+        s = Scheduler(ex, max_batch_tokens=24, lookahead=ahead)
+        assert s.lookahead is ahead
+        reqs = [s.submit(i, p, n) for i, (p, n) in enumerate(zip(prompts, limits))]
+        done = drive(s)
+        assert sorted(r.request_id for r in done) == [0, 1, 2, 3]
+        assert all(r.status == FINISHED and r.stop_reason == "length" for r in reqs)
+        outs[ahead] = [r.output_ids for r in reqs]
+        assert ex.manager.free_pages() == [64] and ex.launched == ex.collected
+        assert s.dropped_tokens == 0           # a token limit is known a round early: nothing speculative
+    assert outs[True] == outs[False] == [expected_output(p, n) for p, n in zip(prompts, limits)]
+
+
+def test_lookahead_drops_the_token_computed_past_an_eos():
+    p = prompt(10)
+    chain = expected_output(p, 6)
+    eos = chain[3]
+    assert eos not in chain[:3]
+    ex = AheadExecutor(pages=64)
+    s = Scheduler(ex, eos_token_ids=[eos], lookahead=True)
+    a = s.submit("a", p, 10)
+    b = s.submit("b", prompt(12, 5), 10, ignore_eos=True)
+    drive(s)
+    assert a.output_ids == chain[:4] and a.stop_reason == "eos"
+    assert len(b.output_ids) == 10 and b.output_ids == expected_output(prompt(12, 5), 10)
+    assert s.dropped_tokens == 1               # the round queued before the EOS was read
+    assert ex.manager.free_pages() == [64]
+    # the stub saw one token more of "a" than it kept: the speculative one
+    assert len(ex.fed["a"]) == len(p) + 4
+
+
+def test_lookahead_reads_the_round_in_flight_before_it_preempts():
+    ex = AheadExecutor(pages=6, page=16)
+    s = Scheduler(ex, admission="optimistic", max_batch_tokens=64, lookahead=True)
+    a = s.submit("a", prompt(40), 30)
+    b = s.submit("b", prompt(40, 2), 30)
+    drive(s)
+    assert s.preemptions >= 1
+    assert a.output_ids == expected_output(prompt(40), 30)
+    assert b.output_ids == expected_output(prompt(40, 2), 30)
+    assert ex.manager.free_pages() == [6]
+
+
+def test_lookahead_cancel_and_empty_rounds():
+    ex = AheadExecutor(pages=64)
+    s = Scheduler(ex, lookahead=True)
+    a = s.submit("a", prompt(8), 50, ignore_eos=True)
+    for _ in range(5):
+        s.step(now=0.0)
+    s.cancel(a)
+    done = drive(s)
+    assert [r.request_id for r in done] == ["a"] and a.stop_reason == "cancelled"
+    assert not s.has_work() and ex.manager.free_pages() == [64] and ex.launched == ex.collected
+    assert a.output_ids == expected_output(prompt(8), len(a.output_ids))
