@@ -139,9 +139,11 @@ __global__ void qk_norm_rope_write_kernel(QkRopeWriteParams p) {
   }
 }
 
-// Fast path (head size a multiple of 4, the whole head rotated or none of it, one input tensor): 8 warps = 8
-// heads of one token per block, the token's cos/sin table computed once per block in shared memory, every lane
-// owns two adjacent elements of the low half and their partners in the high half (4- or 8-byte accesses).
+// Fast path (head size a multiple of 4, the whole head rotated or none of it, one input tensor): a block of 8 warps
+// takes 24 heads of one token, three per warp, whose loads are all issued before the first is used (a warp with
+// one head's 256 bytes in flight left the kernel latency-bound: 45 us for 2,048 tokens of 48 heads).  The token's
+// cos/sin table is computed once per block in shared memory; every lane owns two adjacent elements of the low
+// half and their partners in the high half (4- or 8-byte accesses).
 template <typename T>
 struct Pair;
 template <>
@@ -167,9 +169,12 @@ struct Pair<__nv_bfloat16> {
 };
 
 constexpr int kFastWarps = 8;
+constexpr int kHeadsPerWarp = 3;      // loads of three heads are in flight per warp before any is used
 constexpr int kMaxUnitsPerLane = 4;   // head_dim <= 512
 
-template <typename T>
+// UPL: units of 4 elements per lane, 1 for heads up to 128 dims, 2 up to 256, 4 up to 512 (fewer registers, more
+// warps per SM).
+template <typename T, int UPL>
 __global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_write_fast_kernel(QkRopeWriteParams p) {
   extern __shared__ float cs[];   // [2][half]: cos, sin of this token's angles
   pdl_launch_dependents();
@@ -180,6 +185,34 @@ __global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_write_fast_kerne
   if (token >= p.num_tokens) return;
   const int D = p.head_dim, half = D / 2, units = D / 4;
   const bool rotary = p.inv_freq != nullptr && p.rotary_dim == D;
+  // the token's cache slot, once
+  int64_t slot = -1;
+  if (p.slots != nullptr && p.k_cache != nullptr) {
+    slot = p.slots[token];
+    if (slot >= p.num_pages * p.page_size) {
+      if (threadIdx.x == 0) set_status(p.status, kBadSlot);
+      slot = -1;
+    }
+  }
+  const int first_head = (blockIdx.x * kFastWarps + warp) * kHeadsPerWarp;
+  float lo[kHeadsPerWarp][UPL][2], hi[kHeadsPerWarp][UPL][2];
+  // 1. every load of this warp's heads, before anything waits for one
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerWarp; ++hh) {
+    const int head = first_head + hh;
+    if (head < total_heads) {
+      const T* src = (const T*)p.qkv + (token * total_heads + head) * (int64_t)D;
+#pragma unroll
+      for (int c = 0; c < UPL; ++c) {
+        const int u = c * 32 + lane;
+        if (u < units) {
+          Pair<T>::load(src + 2 * u, lo[hh][c][0], lo[hh][c][1]);
+          Pair<T>::load(src + half + 2 * u, hi[hh][c][0], hi[hh][c][1]);
+        }
+      }
+    }
+  }
+  // the token's cos/sin table, while the loads are under way
   if (rotary) {
     const float pos = (float)p.positions[token];
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
@@ -190,82 +223,75 @@ __global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_write_fast_kerne
     }
     __syncthreads();
   }
-  const int head = blockIdx.x * kFastWarps + warp;
-  if (head >= total_heads) return;
-  const T* src = (const T*)p.qkv + (token * total_heads + head) * (int64_t)D;
-  const bool is_q = head < p.num_heads;
-  const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
-  const int local = is_q ? head : (is_k ? head - p.num_heads : head - p.num_heads - p.num_kv_heads);
-  T* dense_out = nullptr;
-  if (is_q) dense_out = (T*)p.q_out + (token * p.num_heads + local) * (int64_t)D;
-  else if (is_k && p.k_out) dense_out = (T*)p.k_out + (token * p.num_kv_heads + local) * (int64_t)D;
-  else if (!is_k && p.v_out) dense_out = (T*)p.v_out + (token * p.num_kv_heads + local) * (int64_t)D;
-  T* cache_out = nullptr;
-  if (!is_q && p.slots != nullptr && p.k_cache != nullptr) {
-    const int64_t slot = p.slots[token];
-    if (slot >= 0) {
-      if (slot >= p.num_pages * p.page_size) {
-        if (lane == 0) set_status(p.status, kBadSlot);
-      } else {
-        const int64_t page = slot / p.page_size, off = slot % p.page_size;
-        T* base = (T*)(is_k ? p.k_cache : p.v_cache);
-        cache_out = base + ((page * p.num_kv_heads + local) * p.page_size + off) * (int64_t)D;
+  // 2. norm, rotation, stores, head by head
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerWarp; ++hh) {
+    const int head = first_head + hh;
+    if (head >= total_heads) break;
+    const bool is_q = head < p.num_heads;
+    const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
+    const int local = is_q ? head : (is_k ? head - p.num_heads : head - p.num_heads - p.num_kv_heads);
+    T* dense_out = nullptr;
+    if (is_q) dense_out = (T*)p.q_out + (token * p.num_heads + local) * (int64_t)D;
+    else if (is_k && p.k_out) dense_out = (T*)p.k_out + (token * p.num_kv_heads + local) * (int64_t)D;
+    else if (!is_k && p.v_out) dense_out = (T*)p.v_out + (token * p.num_kv_heads + local) * (int64_t)D;
+    T* cache_out = nullptr;
+    if (!is_q && slot >= 0) {
+      const int64_t page = slot / p.page_size, off = slot % p.page_size;
+      T* base = (T*)(is_k ? p.k_cache : p.v_cache);
+      cache_out = base + ((page * p.num_kv_heads + local) * p.page_size + off) * (int64_t)D;
+    }
+    const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < UPL; ++c) {
+        const int u = c * 32 + lane;
+        if (u < units)
+          ss += lo[hh][c][0] * lo[hh][c][0] + lo[hh][c][1] * lo[hh][c][1] + hi[hh][c][0] * hi[hh][c][0] +
+                hi[hh][c][1] * hi[hh][c][1];
       }
-    }
-  }
-  float lo[kMaxUnitsPerLane][2], hi[kMaxUnitsPerLane][2];
-  float ss = 0.f;
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + p.eps);
 #pragma unroll
-  for (int c = 0; c < kMaxUnitsPerLane; ++c) {
-    const int u = c * 32 + lane;
-    if (u < units) {
-      Pair<T>::load(src + 2 * u, lo[c][0], lo[c][1]);
-      Pair<T>::load(src + half + 2 * u, hi[c][0], hi[c][1]);
-      ss += lo[c][0] * lo[c][0] + lo[c][1] * lo[c][1] + hi[c][0] * hi[c][0] + hi[c][1] * hi[c][1];
-    }
-  }
-  const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
-  if (w != nullptr) {
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)D + p.eps);
+      for (int c = 0; c < UPL; ++c) {
+        const int u = c * 32 + lane;
+        if (u < units) {
 #pragma unroll
-    for (int c = 0; c < kMaxUnitsPerLane; ++c) {
-      const int u = c * 32 + lane;
-      if (u < units) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          lo[c][e] = lo[c][e] * inv * w[2 * u + e];
-          hi[c][e] = hi[c][e] * inv * w[half + 2 * u + e];
+          for (int e = 0; e < 2; ++e) {
+            lo[hh][c][e] = lo[hh][c][e] * inv * w[2 * u + e];
+            hi[hh][c][e] = hi[hh][c][e] * inv * w[half + 2 * u + e];
+          }
         }
       }
     }
-  }
-  if (rotary && (is_q || is_k)) {
+    if (rotary && (is_q || is_k)) {
 #pragma unroll
-    for (int c = 0; c < kMaxUnitsPerLane; ++c) {
-      const int u = c * 32 + lane;
-      if (u < units) {
+      for (int c = 0; c < UPL; ++c) {
+        const int u = c * 32 + lane;
+        if (u < units) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float co = cs[2 * u + e], sn = cs[half + 2 * u + e];
-          const float a = lo[c][e], b = hi[c][e];
-          lo[c][e] = a * co - b * sn;
-          hi[c][e] = b * co + a * sn;
+          for (int e = 0; e < 2; ++e) {
+            const float co = cs[2 * u + e], sn = cs[half + 2 * u + e];
+            const float a = lo[hh][c][e], b = hi[hh][c][e];
+            lo[hh][c][e] = a * co - b * sn;
+            hi[hh][c][e] = b * co + a * sn;
+          }
         }
       }
     }
-  }
 #pragma unroll
-  for (int c = 0; c < kMaxUnitsPerLane; ++c) {
-    const int u = c * 32 + lane;
-    if (u < units) {
-      if (dense_out) {
-        Pair<T>::store(dense_out + 2 * u, lo[c][0], lo[c][1]);
-        Pair<T>::store(dense_out + half + 2 * u, hi[c][0], hi[c][1]);
-      }
-      if (cache_out) {
-        Pair<T>::store(cache_out + 2 * u, lo[c][0], lo[c][1]);
-        Pair<T>::store(cache_out + half + 2 * u, hi[c][0], hi[c][1]);
+    for (int c = 0; c < UPL; ++c) {
+      const int u = c * 32 + lane;
+      if (u < units) {
+        if (dense_out) {
+          Pair<T>::store(dense_out + 2 * u, lo[hh][c][0], lo[hh][c][1]);
+          Pair<T>::store(dense_out + half + 2 * u, hi[hh][c][0], hi[hh][c][1]);
+        }
+        if (cache_out) {
+          Pair<T>::store(cache_out + 2 * u, lo[hh][c][0], lo[hh][c][1]);
+          Pair<T>::store(cache_out + half + 2 * u, hi[hh][c][0], hi[hh][c][1]);
+        }
       }
     }
   }
@@ -283,13 +309,21 @@ int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
   if (p.qkv_parts == 0 && p.head_dim % 4 == 0 && whole_or_none && p.head_dim / 4 <= 32 * kMaxUnitsPerLane) {
     QkRopeWriteParams q = p;
     if (q.rotary_dim != q.head_dim) q.inv_freq = nullptr;
-    dim3 fast_grid((unsigned)((total_heads + kFastWarps - 1) / kFastWarps), (unsigned)ny, (unsigned)nz);
+    const int per_block = kFastWarps * kHeadsPerWarp;
+    dim3 fast_grid((unsigned)((total_heads + per_block - 1) / per_block), (unsigned)ny, (unsigned)nz);
     const size_t table = q.inv_freq ? (size_t)p.head_dim * sizeof(float) : 0;
-    if (p.dtype == kBFloat16)
-      return (int)launch_chain(qk_norm_rope_write_fast_kernel<__nv_bfloat16>, fast_grid, dim3(kFastWarps * 32), table,
-                               stream, dim3(1, 1, 1), q);
-    return (int)launch_chain(qk_norm_rope_write_fast_kernel<float>, fast_grid, dim3(kFastWarps * 32), table, stream,
-                             dim3(1, 1, 1), q);
+    const dim3 block(kFastWarps * 32), one(1, 1, 1);
+#define AKV_QK_FAST(T, UPL) \
+  return (int)launch_chain(qk_norm_rope_write_fast_kernel<T, UPL>, fast_grid, block, table, stream, one, q)
+    if (p.dtype == kBFloat16) {
+      if (p.head_dim <= 128) AKV_QK_FAST(__nv_bfloat16, 1);
+      if (p.head_dim <= 256) AKV_QK_FAST(__nv_bfloat16, 2);
+      AKV_QK_FAST(__nv_bfloat16, 4);
+    }
+    if (p.head_dim <= 128) AKV_QK_FAST(float, 1);
+    if (p.head_dim <= 256) AKV_QK_FAST(float, 2);
+    AKV_QK_FAST(float, 4);
+#undef AKV_QK_FAST
   }
   dim3 grid((unsigned)((total_heads + warps - 1) / warps), (unsigned)ny, (unsigned)nz);
   const size_t smem = (p.rotary_dim != p.head_dim && p.inv_freq) ? (size_t)warps * p.head_dim * sizeof(float) : 0;

@@ -39,6 +39,26 @@ def timed(fn, calls: int, warmup: int = 3) -> float:
     return start.elapsed_time(stop) * 1000.0 / calls
 
 
+def timed_graph(fn, calls: int, warmup: int = 3) -> float:
+    """Mean microseconds per call of ``fn(i)`` with the calls captured in one CUDA graph: the figure for kernels
+    so short that launching them one by one from Python would measure the host."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(calls):
+            fn(warmup + i)
+    graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1000.0 / calls
+
+
 def copies_for(nbytes: int) -> int:
     return max(2, (2 * L2_BYTES + nbytes - 1) // nbytes + 1)
 
@@ -126,12 +146,12 @@ def bench_rowwise(args) -> dict:
     hidden = [torch.randn(n, h, generator=g, device="cuda") for _ in range(copies)]
     delta = [torch.randn(n, h, generator=g, device="cuda").to(torch.bfloat16) for _ in range(copies)]
     weight = torch.ones(h, device="cuda")
-    out = {"norm_us": timed(lambda i: ops.add_rmsnorm(hidden[i % copies], delta[i % copies], weight, 1e-6,
+    out = {"norm_us": timed_graph(lambda i: ops.add_rmsnorm(hidden[i % copies], delta[i % copies], weight, 1e-6,
                                                       torch.bfloat16), args.calls)}
     out["norm_gbs"] = round(n * h * (4 + 2 + 4 + 2) / out["norm_us"] / 1e3, 1)
     gate_up = [torch.randn(n, 2 * inter, generator=g, device="cuda").to(torch.bfloat16)
                for _ in range(copies_for(n * inter * 6))]
-    out["silu_mul_us"] = timed(lambda i: ops.silu_mul(gate_up[i % len(gate_up)]), args.calls)
+    out["silu_mul_us"] = timed_graph(lambda i: ops.silu_mul(gate_up[i % len(gate_up)]), args.calls)
     out["silu_mul_gbs"] = round(n * inter * 6 / out["silu_mul_us"] / 1e3, 1)
     heads, kv, d = args.heads, args.kv_heads, args.head_dim
     qkv = [torch.randn(n, (heads + 2 * kv) * d, generator=g, device="cuda").to(torch.bfloat16)
@@ -142,7 +162,7 @@ def bench_rowwise(args) -> dict:
     positions = torch.arange(n, device="cuda", dtype=torch.int32)
     ones = torch.ones(d, device="cuda")
     inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2).float() / d))).cuda()
-    out["qk_rope_write_us"] = timed(lambda i: ops.qk_norm_rope_write(
+    out["qk_rope_write_us"] = timed_graph(lambda i: ops.qk_norm_rope_write(
         qkv[i % len(qkv)], positions, positions, ones, ones, inv_freq, k_cache, v_cache, num_heads=heads,
         num_kv_heads=kv, head_dim=d, rotary_dim=d, eps=1e-6), args.calls)
     out["qk_rope_write_gbs"] = round(n * (heads + 2 * kv) * d * 4 / out["qk_rope_write_us"] / 1e3, 1)
