@@ -1,6 +1,6 @@
 """Times one kernel at a time on the GPU, with CUDA events, on inputs larger than L2.
 
-    python -m ampere_kv_engine_b200.kernels.microbench gemm --tokens 8 --features 24576 --k 4096
+    python -m ampere_kv_engine_b200.kernels.microbench gemm --tokens 8 --features 24576 --k 4096 [--gated]
     python -m ampere_kv_engine_b200.kernels.microbench decode-attention --batch 64 --context 1152
     python -m ampere_kv_engine_b200.kernels.microbench prefill-attention --tokens 2048
     python -m ampere_kv_engine_b200.kernels.microbench norm --tokens 2048
@@ -71,7 +71,14 @@ def bench_gemm(args) -> dict:
     x = torch.randn(args.tokens, args.k, generator=g, device="cuda", dtype=torch.bfloat16)
     out = {}
     small = args.tokens <= 64
-    if small:
+    if small and args.gated:
+        # the weight read as gate and up rows in alternating runs of 64; the kernel applies SiLU-mul to its tile
+        out["tcgen05_us"] = timed(lambda i: ops.small_m_gemm(x, weights[i % n], gated=True), args.calls)
+        full = (x.float() @ weights[0].float().t()).to(torch.bfloat16).float().view(args.tokens, -1, 2, 64)
+        ref = (torch.nn.functional.silu(full[:, :, 0]) * full[:, :, 1]).reshape(args.tokens, -1)
+        got = ops.small_m_gemm(x, weights[0], gated=True).float()
+        out["max_abs_error"] = float((got - ref).abs().max())
+    elif small:
         out["tcgen05_us"] = timed(lambda i: ops.small_m_gemm(x, weights[i % n]), args.calls)
         ref = x.float() @ weights[0].float().t()
         got = ops.small_m_gemm(x, weights[0], out_dtype=torch.float32)
@@ -185,6 +192,7 @@ def main(argv=None) -> int:
     parser.add_argument("--intermediate", type=int, default=12288)
     parser.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0 = the engine's choice)")
     parser.add_argument("--with-general", action="store_true", help="also time the general attention kernel on prompts")
+    parser.add_argument("--gated", action="store_true", help="gemm: the SiLU-mul epilogue (gate/up rows in runs of 64)")
     parser.add_argument("--calls", type=int, default=50)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
