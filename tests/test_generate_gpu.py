@@ -22,7 +22,7 @@ def prompts_for(name, lengths, seed=7):
     return [torch.randint(0, tiny.CONFIGS[name][0]["vocab_size"], (n,), generator=g).tolist() for n in lengths]
 
 
-@pytest.mark.parametrize("name,lengths", [("A", (5, 17, 33)), ("B", (1, 31, 64, 130))])
+@pytest.mark.parametrize("name,lengths", [("A", (5, 17, 33)), ("B", (1, 31, 64, 130)), ("C", (3, 40, 70))])
 def test_greedy_generation_equals_plain(name, lengths):
     from ampere_kv_engine_b200.engine.engine import Engine
     raw, page = tiny.CONFIGS[name]
@@ -36,14 +36,17 @@ def test_greedy_generation_equals_plain(name, lengths):
     engine.manager.check_invariants()
 
 
-def test_bfloat16_greedy_generation_close_to_plain():
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_bfloat16_greedy_generation_close_to_plain(name):
     """bfloat16 may pick another token where two logits are within rounding; every pick must still be
-    (nearly) the best token of the plain model given the same history."""
+    (nearly) the best token of the plain model given the same history.  (C: the decode steps run the fused
+    kernels: norm on the GEMM's token operand, rotation and cache write, SiLU-mul and the residual sum on its
+    output tile.)"""
     from ampere_kv_engine_b200.engine.engine import Engine
-    raw, page = tiny.CONFIGS["A"]
-    folder = model_folder("A")
+    raw, page = tiny.CONFIGS[name]
+    folder = model_folder(name)
     engine = Engine.from_pretrained(folder, dtype="bfloat16", page_size=page, num_pages=40)
-    prompts = prompts_for("A", (5, 17, 33))
+    prompts = prompts_for(name, (5, 17, 33))
     got = engine.generate(prompts, max_new_tokens=8, ignore_eos=True)
     w = plain_weights(folder, "bfloat16")
     for prompt, out in zip(prompts, got):

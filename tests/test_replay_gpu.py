@@ -1,5 +1,5 @@
 """bin/trace_run on the GPU, as a user runs it (a subprocess fed JSON lines), in float32 and in bfloat16,
-for both tiny configurations: each request alone and whole; most of it in one step and the last 32 tokens
+for both tiny configurations and a small one with the benchmark model's head shape: each request alone and whole; most of it in one step and the last 32 tokens
 one by one; in portions of changing size down to two tokens; and mixed, up to four live requests with so
 few pages that they are used again.  Every written row is compared with the plain implementation."""
 
@@ -13,7 +13,7 @@ from models_util import model_folder, plain_logits
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": (5, 17, 33, 130), "B": (1, 31, 64, 130)}
+LENGTHS = {"A": (5, 17, 33, 130), "B": (1, 31, 64, 130), "C": (3, 40, 64, 130)}
 MODES = ("whole", "last32", "portions", "mixed")
 MAX_TOKENS = 64 * 6
 
@@ -36,7 +36,7 @@ def _run(name: str, dtype: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("mode", MODES)
 def test_replay_matches_plain(name, dtype, mode):
     combined, spans, outputs, expected = _run(name, dtype)

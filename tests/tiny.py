@@ -50,7 +50,33 @@ TINY_B = {
 }
 PAGE_B = 32
 
-CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B)}
+# A third, small configuration with the head shape of the benchmark model (head_dim 128, groups of four q-heads,
+# an intermediate size that is a multiple of 64): the sizes at which the tcgen05 attention kernel and the fused
+# epilogues of the decode GEMM run.  Layer 1 sees a window of 48 keys.
+SMALL_C = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 2,
+    "hidden_size": 512,
+    "num_attention_heads": 8,
+    "num_key_value_heads": 2,
+    "head_dim": 128,
+    "intermediate_size": 1152,
+    "vocab_size": 1536,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 1024,
+    "tie_word_embeddings": False,
+    "hidden_act": "silu",
+    "attention_bias": False,
+    "use_sliding_window": True,
+    "sliding_window": 48,
+    "max_window_layers": 1,
+    "eos_token_id": 2,
+}
+PAGE_C = 16
+
+CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "C": (SMALL_C, PAGE_C)}
 
 
 def config(name: str) -> dict:
