@@ -171,7 +171,8 @@ def main() -> int:
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     max_batch = 64 if not args.no_points else args.batch
-    pool_tokens = max(max_batch * (PROMPT_LEN + GEN_LEN + 64), args.batch * CONTEXT // 4, PREFILL_TOKENS + 64)
+    pool_tokens = max(max_batch * (PROMPT_LEN + GEN_LEN + 64), args.batch * (CONTEXT + 64) if not args.no_points else 0,
+                      PREFILL_TOKENS + 64)
     engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", device=device, page_size=PAGE_SIZE,
                                 max_tokens=pool_tokens, max_seqs=max_batch + 2, max_batch_tokens=PREFILL_TOKENS)
     runner = engine.runner
@@ -191,12 +192,17 @@ def main() -> int:
         torch.cuda.synchronize()
         return start.elapsed_time(stop) / steps
 
-    def decode_point(batch, steps, warmup):
-        """ms per decode step of ``batch`` requests that each hold a 1,024-token prompt."""
-        seqs = [runner.open(f"d{batch}-{i}") for i in range(batch)]
-        per_step = max(1, PREFILL_TOKENS // PROMPT_LEN)
-        for i in range(0, batch, per_step):
-            runner.step([SeqStep(s, synthetic(PROMPT_LEN), []) for s in seqs[i:i + per_step]])
+    def decode_point(batch, steps, warmup, prompt_len=PROMPT_LEN):
+        """ms per decode step of ``batch`` requests that each hold a ``prompt_len``-token prompt."""
+        seqs = [runner.open(f"d{batch}-{prompt_len}-{i}") for i in range(batch)]
+        if prompt_len <= PREFILL_TOKENS:
+            per_step = max(1, PREFILL_TOKENS // prompt_len)
+            for i in range(0, batch, per_step):
+                runner.step([SeqStep(s, synthetic(prompt_len), []) for s in seqs[i:i + per_step]])
+        else:
+            for s in seqs:       # long prompts go in portions of the prefill budget
+                for start in range(0, prompt_len, PREFILL_TOKENS):
+                    runner.step([SeqStep(s, synthetic(min(PREFILL_TOKENS, prompt_len - start)), [])])
         greedy = [SamplingParams()] * batch
         zeros = [0] * batch
 
@@ -268,6 +274,12 @@ def main() -> int:
         for b in (1, 64):
             p_ms, _, _ = decode_point(b, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = round(b / (p_ms / 1000), 2)
+        # the same batch at the end of the configuration's 8,192-token context, with its own roofline fraction
+        long_steps = max(8, args.steps // 2)
+        p_ms, long_ctx, _ = decode_point(args.batch, long_steps, args.warmup, CONTEXT - GEN_LEN)
+        points[f"decode_b{args.batch}_ctx{CONTEXT}"] = round(args.batch / (p_ms / 1000), 2)
+        points[f"decode_b{args.batch}_ctx{CONTEXT}_hbm_frac"] = round(
+            decode_bytes(cfg, args.layers, args.batch, long_ctx) / (p_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)
 
     line = {
         "metric": "decode tok/s at batch 8 (Qwen3-8B shape, B200); prefill and batch 1/64 alongside",
