@@ -271,24 +271,23 @@ __device__ __forceinline__ void issue_block(const TcParams& tp, const CUtensorMa
       }
     }
   }
-  if (lane == 0) {
-    mbar_expect_tx(bar, bytes);
+  // One copy per lane (lane = box * 2H + copy), issued side by side: one thread issuing a block's copies in turn
+  // spends about 150 ns on each, which capped a CTA at 13-15 GB/s.
+  if (lane == 0) mbar_expect_tx(bar, bytes);
+  __syncwarp();
+  const int my_box = lane / (2 * H), c = lane % (2 * H);
+  int my_page = -1;
 #pragma unroll
-    for (int b = 0; b < KT / 8; ++b) {
-      if (b < boxes && page_of[b] >= 0) {
-        const int key = key0 + b * rows;
-        const int y = (page_of[b] * p.num_kv_heads + kvh) * P + key % P;
-#pragma unroll
-        for (int c = 0; c < 2 * H; ++c) {
-          if ((b * 2 * H + c) % num_producers != producer) continue;
-          const int h = c >> 1;
-          if (c & 1)
-            tma_load_2d(stage + KT * D * 2 + h * KT * 128 + b * rows * 128, v_map, h * 64, y, bar);
-          else
-            tma_load_2d(stage + h * KT * 128 + b * rows * 128, k_map, h * 64, y, bar);
-        }
-      }
-    }
+  for (int b = 0; b < KT / 8; ++b)
+    if (b == my_box && b < boxes) my_page = page_of[b];
+  if (my_page >= 0 && lane % num_producers == producer) {
+    const int key = key0 + my_box * rows;
+    const int y = (my_page * p.num_kv_heads + kvh) * P + key % P;
+    const int h = c >> 1;
+    if (c & 1)
+      tma_load_2d(stage + KT * D * 2 + h * KT * 128 + my_box * rows * 128, v_map, h * 64, y, bar);
+    else
+      tma_load_2d(stage + h * KT * 128 + my_box * rows * 128, k_map, h * 64, y, bar);
   }
 }
 
@@ -1033,22 +1032,21 @@ int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& 
   return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
 }
 
-// Shape of the decode kernel's CTAs: (TMA ring stages of 16 KB at head size 128, consumer warps).  One CTA
-// streams pages at 13-15 GB/s whatever its ring depth (measured on B200), so bandwidth comes from CTAs per SM,
-// and a cluster's CTAs must all fit at once: rings of 4 or more stages (64 KB and up) made the batch-8 kernel
-// 25 us instead of 15 us.  3 stages x 4 warps is the default: since the producer fetches the blocks of old keys
-// before it waits for the previous kernel, the third stage pays (measured per step: batch 8 3.49 ms vs 3.53 ms
-// with 2 x 2, batch 1 3.18 vs 3.27 ms, batch 64 5.61 vs 5.80 ms).  AKV_ATTN_CONFIG=2|3|4|6 forces
-// (2,2) | (3,4) | (2,4) | (3,2).
-int decode_config(int64_t ctas) {
+// Shape of the decode kernel's CTAs: (TMA ring stages of 16 KB at head size 128, consumer warps).  Bandwidth comes
+// from CTAs per SM, and a cluster's CTAs must all fit at once: rings of 4 or more stages (64 KB and up) made the
+// batch-8 kernel 25 us instead of 15 us.  Three stages pay since the producer fetches the blocks of old keys
+// before it waits for the previous kernel.  CTAs that walk many key blocks do best with two consumer warps (more
+// CTAs per SM by registers), short walks with four (the block is done sooner).  Measured per step with
+// (3,4) | (3,2): batch 8 at 1,064 keys 3.48 | 3.49 ms, batch 64 5.56 | 5.47 ms, batch 8 at 8,192 keys
+// 4.88 | 4.81 ms; (2,2) is 1-4 % behind everywhere.  AKV_ATTN_CONFIG=2|3|4|6 forces (2,2) | (3,4) | (2,4) | (3,2).
+int decode_config(int64_t blocks_per_cta) {
   static const int forced = [] {
     const char* v = getenv("AKV_ATTN_CONFIG");
     const int n = v ? atoi(v) : 0;
     return (n == 2 || n == 3 || n == 4 || n == 6) ? n : 0;
   }();
   if (forced) return forced;
-  (void)ctas;
-  return 3;
+  return blocks_per_cta >= 16 ? 6 : 3;
 }
 
 }  // namespace
@@ -1091,7 +1089,9 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
                  : launch_coop<128, ST, false, W>(p, box_rows, k_map, v_map, stream);                         \
   return merge ? launch_coop<64, ST, true, W>(p, box_rows, k_map, v_map, stream)                              \
                : launch_coop<64, ST, false, W>(p, box_rows, k_map, v_map, stream);
-    switch (decode_config((int64_t)p.num_tiles * p.num_kv_heads * p.num_splits)) {
+    // an upper bound of the 32-key blocks a CTA walks: the block table's width over the splits
+    const int64_t bound_keys = p.window > 0 ? (int64_t)p.window : (int64_t)p.table_width * p.page_size;
+    switch (decode_config(bound_keys / (p.num_splits > 0 ? p.num_splits : 1) / 32)) {
       case 2: AKV_COOP(2, 2)
       case 4: AKV_COOP(2, 4)
       case 6: AKV_COOP(3, 2)

@@ -242,41 +242,44 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
     for (int b = 0; b < num_blocks && ok; ++b) {
       const int s = b % kStagesKV;
-      if (b >= kStagesKV && !bar_wait(&kv_empty[s], ((b / kStagesKV) - 1) & 1)) {
-        ok = false;
-        break;
+      if (b >= kStagesKV) {
+        const bool freed = bar_wait(&kv_empty[s], ((b / kStagesKV) - 1) & 1);
+        if (!__all_sync(0xffffffffu, freed)) {      // the warp decides together: it votes below
+          ok = false;
+          break;
+        }
       }
+      // One copy per lane: lane = 4 * box + kind, kind = K low half, K high half, V low half, V high half.  The
+      // lanes look their pages up and issue their copies side by side; one thread doing the block's up to
+      // sixteen look-ups and copies in turn took longer than the tensor cores need for the block.
+      uint8_t* k_dst = kv_smem + s * FaSmem::kStage;
+      uint8_t* v_dst = k_dst + FaSmem::kK;
+      const int key0 = lo + b * kKeys;
+      const int boxes = kKeys / fp.box_rows;
+      const int x = lane >> 2, kind = lane & 3;
+      const int key = key0 + x * fp.box_rows;
+      const bool mine = x < boxes && key < hi;
+      int y = -1;
+      if (mine) {
+        const int logical = key / P;
+        int page = logical < p.table_width ? table[logical] : -1;
+        if (page < 0 || page >= p.num_pages) {
+          set_status(p.status, kBadPage);
+          page = 0;     // keep the byte count honest; the result is flagged
+        }
+        y = (page * p.num_kv_heads + kvh) * P + key % P;
+      }
+      const uint32_t valid_boxes = __popc(__ballot_sync(0xffffffffu, mine && kind == 0));
       if (lane == 0) {
-        uint8_t* k_dst = kv_smem + s * FaSmem::kStage;
-        uint8_t* v_dst = k_dst + FaSmem::kK;
-        const int key0 = lo + b * kKeys;
-        const int boxes = kKeys / fp.box_rows;
-        uint32_t bytes = 0;
-        for (int x = 0; x < boxes; ++x)
-          if (key0 + x * fp.box_rows < hi) bytes += (uint32_t)fp.box_rows * 256u;
+        const uint32_t bytes = valid_boxes * (uint32_t)fp.box_rows * 256u;
         bar_expect_tx(&k_full[s], bytes);
         bar_expect_tx(&v_full[s], bytes);
-        // all K boxes first: the scores need them first
-        int y_of[kKeys / 16];
-        for (int x = 0; x < boxes; ++x) {
-          const int key = key0 + x * fp.box_rows;
-          y_of[x] = -1;
-          if (key >= hi) continue;
-          const int logical = key / P;
-          int page = logical < p.table_width ? table[logical] : -1;
-          if (page < 0 || page >= p.num_pages) {
-            set_status(p.status, kBadPage);
-            page = 0;     // keep the byte count honest; the result is flagged
-          }
-          y_of[x] = (page * p.num_kv_heads + kvh) * P + key % P;
-          tma_2d(k_dst + x * fp.box_rows * 128, &k_map, 0, y_of[x], &k_full[s]);
-          tma_2d(k_dst + kKeys * 128 + x * fp.box_rows * 128, &k_map, 64, y_of[x], &k_full[s]);
-        }
-        for (int x = 0; x < boxes; ++x) {
-          if (y_of[x] < 0) continue;
-          tma_2d(v_dst + x * fp.box_rows * 128, &v_map, 0, y_of[x], &v_full[s]);
-          tma_2d(v_dst + kKeys * 128 + x * fp.box_rows * 128, &v_map, 64, y_of[x], &v_full[s]);
-        }
+      }
+      __syncwarp();
+      if (mine) {
+        const uint32_t off = (uint32_t)(kind & 1) * (kKeys * 128) + (uint32_t)x * fp.box_rows * 128;
+        if (kind < 2) tma_2d(k_dst + off, &k_map, (kind & 1) * 64, y, &k_full[s]);
+        else tma_2d(v_dst + off, &v_map, (kind & 1) * 64, y, &v_full[s]);
       }
     }
   } else if (warp == 5) {
