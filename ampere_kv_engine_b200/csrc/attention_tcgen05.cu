@@ -240,8 +240,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       tma_3d(q_smem + kRows * 128, &q_map, 64, kvh * G, q0, q_full);
     }
     const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
+    // One copy per lane: lane = 4 * box + kind, kind = K low half, K high half, V low half, V high half.  The
+    // lanes look their pages up and issue their copies side by side; one thread doing the block's up to
+    // sixteen look-ups and copies in turn took longer than the tensor cores need for the block.  The look-up
+    // of a block is started one block early, so that its latency hides behind the wait for the stage.
+    const int boxes = kKeys / fp.box_rows;
+    const int x = lane >> 2, kind = lane & 3;
+    auto row_of = [&](int blk) -> int {       // first cache row of this lane's box in block blk, -1: no box
+      const int key = lo + blk * kKeys + x * fp.box_rows;
+      if (blk >= num_blocks || x >= boxes || key >= hi) return -1;
+      const int logical = key / P;
+      int page = logical < p.table_width ? table[logical] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        set_status(p.status, kBadPage);
+        page = 0;     // keep the byte count honest; the result is flagged
+      }
+      return (page * p.num_kv_heads + kvh) * P + key % P;
+    };
+    int y_next = row_of(0);
     for (int b = 0; b < num_blocks && ok; ++b) {
       const int s = b % kStagesKV;
+      const int y = y_next;
+      y_next = row_of(b + 1);
       if (b >= kStagesKV) {
         const bool freed = bar_wait(&kv_empty[s], ((b / kStagesKV) - 1) & 1);
         if (!__all_sync(0xffffffffu, freed)) {      // the warp decides together: it votes below
@@ -249,26 +269,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           break;
         }
       }
-      // One copy per lane: lane = 4 * box + kind, kind = K low half, K high half, V low half, V high half.  The
-      // lanes look their pages up and issue their copies side by side; one thread doing the block's up to
-      // sixteen look-ups and copies in turn took longer than the tensor cores need for the block.
       uint8_t* k_dst = kv_smem + s * FaSmem::kStage;
       uint8_t* v_dst = k_dst + FaSmem::kK;
-      const int key0 = lo + b * kKeys;
-      const int boxes = kKeys / fp.box_rows;
-      const int x = lane >> 2, kind = lane & 3;
-      const int key = key0 + x * fp.box_rows;
-      const bool mine = x < boxes && key < hi;
-      int y = -1;
-      if (mine) {
-        const int logical = key / P;
-        int page = logical < p.table_width ? table[logical] : -1;
-        if (page < 0 || page >= p.num_pages) {
-          set_status(p.status, kBadPage);
-          page = 0;     // keep the byte count honest; the result is flagged
-        }
-        y = (page * p.num_kv_heads + kvh) * P + key % P;
-      }
+      const bool mine = y >= 0;
       const uint32_t valid_boxes = __popc(__ballot_sync(0xffffffffu, mine && kind == 0));
       if (lane == 0) {
         const uint32_t bytes = valid_boxes * (uint32_t)fp.box_rows * 256u;
@@ -346,26 +349,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         tmem_ld32_nowait(lane_base + (b & 1) * 64 + 32, raw[1]);
         tmem_wait_ld();
       }
-      float sc[kKeys];
-      // most blocks lie wholly below the diagonal, inside the window and inside the sequence: no masks there
+      // Unscaled scores stay where the load put them; masked keys become -inf.  Most blocks lie wholly below the
+      // diagonal, inside the window and inside the sequence: no masks there.  The maximum is taken along four
+      // independent chains (one chain of 64 dependent maxima was a quarter of the block's time).
       const bool plain = ok && nvalid == kKeys && key0 + kKeys - 1 <= tile_pos &&
                          (p.window <= 0 || key0 > tile_pos + nq - 1 - p.window);
-      float bmax = -CUDART_INF_F;
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (plain && live) {
 #pragma unroll
-        for (int j = 0; j < kKeys; ++j) {
-          sc[j] = __uint_as_float(raw[j >> 5][j & 31]) * scale_log2;
-          bmax = fmaxf(bmax, sc[j]);
-        }
+        for (int j = 0; j < kKeys; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
       } else {
 #pragma unroll
         for (int j = 0; j < kKeys; ++j) {
           const int key = key0 + j;
           const bool visible = ok && live && j < nvalid && key <= pos && (p.window <= 0 || key > pos - p.window);
-          sc[j] = visible ? __uint_as_float(raw[j >> 5][j & 31]) * scale_log2 : -CUDART_INF_F;
-          bmax = fmaxf(bmax, sc[j]);
+          if (!visible) raw[j >> 5][j & 31] = 0xff800000u;     // -inf
+          mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
         }
       }
+      const float bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;     // the scale is positive
       // raise the reference maximum only when it pays; then O (in TMEM) and l are rescaled
       const bool raise = bmax > m_ref + kRescaleThreshold || (m_ref == -CUDART_INF_F && bmax > -CUDART_INF_F);
       if (__any_sync(0xffffffffu, raise)) {
@@ -396,19 +398,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       // seen no key yet subtracts 0, so that 2^(-inf - 0) = 0 and not 2^(-inf + inf).
       const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;
       uint8_t* p_row = p_smem + (b & 1) * FaSmem::kP + row * 128;
+      float part[4] = {0.f, 0.f, 0.f, 0.f};     // four chains for the row sum as well
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t packed[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float pa = ex2(sc[c * 8 + 2 * e] - m_sub);        // 2^(-inf) = 0 for masked keys
-          const float pb = ex2(sc[c * 8 + 2 * e + 1] - m_sub);
-          l += pa + pb;
+          const int j = c * 8 + 2 * e;
+          // 2^(score * scale - m): one multiply-add; -inf stays -inf and gives 0
+          const float pa = ex2(fmaf(__uint_as_float(raw[j >> 5][j & 31]), scale_log2, -m_sub));
+          const float pb = ex2(fmaf(__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31]), scale_log2, -m_sub));
+          part[e] += pa + pb;
           __nv_bfloat162 h = __floats2bfloat162_rn(pa, pb);
           packed[e] = *reinterpret_cast<uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
+      l += (part[0] + part[1]) + (part[2] + part[3]);
       if (nvalid < kKeys) {
         // V rows of keys past the end may hold anything (a page's tail, or nothing was loaded): zero them, or
         // 0 * NaN would poison the product.  V has to have landed first.
@@ -536,6 +542,7 @@ bool attention_tcgen05_supported(const PagedAttentionParams& p) {
     return v != nullptr && v[0] == 'm';
   }();
   if (disabled || p.dtype != kBFloat16 || p.head_dim != kD || p.q_tile <= 1) return false;
+  if (!(p.scale > 0.f)) return false;      // the kernel takes the maximum before it scales
   if (p.num_heads % p.num_kv_heads) return false;
   const int G = p.num_heads / p.num_kv_heads;
   if (G != 2 && G != 4 && G != 8) return false;
