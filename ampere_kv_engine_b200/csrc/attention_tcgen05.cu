@@ -37,7 +37,6 @@ namespace {
 constexpr int kD = 128;             // head size
 constexpr int kRows = 128;          // query rows per CTA
 constexpr int kKeys = 64;           // keys per block
-constexpr int kStagesKV = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
 
@@ -107,6 +106,17 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
       "}\n" ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand read from tensor memory (lane = row, a 32-bit column = two consecutive K elements).
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t id,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(id), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bar))
                : "memory");
@@ -120,13 +130,13 @@ struct FaParams {
 
 // Shared memory: Q [2 halves][128 rows][128 B] | K/V ring: per stage K [2][64][128 B], V [2][64][128 B] |
 // P [2 buffers][128 rows][128 B] | barriers | TMEM base.
-struct FaSmem {
+template <int kStagesKV>
+struct FaSmemT {
   static constexpr int kQ = 2 * kRows * 128;
   static constexpr int kK = 2 * kKeys * 128;
   static constexpr int kStage = 2 * kK;
-  static constexpr int kP = kRows * 128;
   static constexpr int kBars = (1 + 3 * kStagesKV + 2 + 2 + 2) * 8;
-  static constexpr int kBytes = kQ + kStagesKV * kStage + 2 * kP + kBars + 16 + 1024;
+  static constexpr int kBytes = kQ + kStagesKV * kStage + kBars + 16 + 1024;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -159,16 +169,20 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 
 constexpr float kRescaleThreshold = 8.f;     // log2 units
 
-__global__ void __launch_bounds__(192, 1)
+// kStagesKV = 2: 96 KB of shared memory and at most 168 registers, two CTAs per SM (each takes half of the SM's
+// tensor memory): one CTA's softmax fills the other's waits.  kStagesKV = 4: one CTA per SM with a deeper K/V ring,
+// for launches with fewer CTAs than SMs.
+template <int kStagesKV>
+__global__ void __launch_bounds__(192, kStagesKV <= 2 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                          const __grid_constant__ CUtensorMap v_map, FaParams fp) {
+  using FaSmem = FaSmemT<kStagesKV>;
   const PagedAttentionParams& p = fp.p;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;
   uint8_t* kv_smem = smem + FaSmem::kQ;
-  uint8_t* p_smem = kv_smem + kStagesKV * FaSmem::kStage;       // two buffers
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(p_smem + 2 * FaSmem::kP);
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(kv_smem + kStagesKV * FaSmem::kStage);
   uint64_t* k_full = q_full + 1;                 // [stages]
   uint64_t* v_full = k_full + kStagesKV;         // [stages]
   uint64_t* kv_empty = v_full + kStagesKV;       // [stages]
@@ -289,7 +303,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t id_s = idesc(kKeys, false), id_o = idesc(kD, true);
-      const uint32_t q_addr = s_addr(q_smem), p_addr = s_addr(p_smem);
+      const uint32_t q_addr = s_addr(q_smem);
       auto issue_scores = [&](int b) -> bool {
         const int s = b % kStagesKV;
         if (!bar_wait(&k_full[s], (b / kStagesKV) & 1)) return false;
@@ -316,12 +330,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         if (!bar_wait(&v_full[s], (b / kStagesKV) & 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t v_addr = s_addr(kv_smem + s * FaSmem::kStage) + FaSmem::kK;
-        const uint32_t pb = p_addr + (b & 1) * FaSmem::kP;
+        const uint32_t p_tmem = tmem + (b & 1) * 64;      // P lies over the first half of the block's scores
 #pragma unroll
         for (int t = 0; t < kKeys / 16; ++t) {
-          // A = P: 16 keys = 32 bytes along the row; B = V: 16 keys = 16 rows of 128 bytes
-          umma(tmem + 128, desc_k_major(pb + t * 32), desc_mn_major(v_addr + t * 16 * 128, kKeys * 128), id_o,
-               (b > 0 || t > 0) ? 1u : 0u);
+          // A = P from tensor memory: 16 keys = 8 columns; B = V: 16 keys = 16 rows of 128 bytes
+          umma_a_tmem(tmem + 128, p_tmem + t * 8, desc_mn_major(v_addr + t * 16 * 128, kKeys * 128), id_o,
+                      (b > 0 || t > 0) ? 1u : 0u);
         }
         umma_commit(&pv_done[b & 1]);
         umma_commit(&kv_empty[s]);
@@ -394,25 +408,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           m_ref = bmax;
         }
       }
-      // P row: 64 bfloat16 = 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7).  A row that has
-      // seen no key yet subtracts 0, so that 2^(-inf - 0) = 0 and not 2^(-inf + inf).
+      // A row that has seen no key yet subtracts 0, so that 2^(-inf - 0) = 0 and not 2^(-inf + inf).
       const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;
-      uint8_t* p_row = p_smem + (b & 1) * FaSmem::kP + row * 128;
+      // P as bfloat16 pairs, one 32-bit column per pair, written over the first 32 score columns of this
+      // thread's lane (its 64 scores are in registers by now): P V reads its A operand from tensor memory
+      uint32_t packed[32];
       float part[4] = {0.f, 0.f, 0.f, 0.f};     // four chains for the row sum as well
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = c * 8 + 2 * e;
-          // 2^(score * scale - m): one multiply-add; -inf stays -inf and gives 0
-          const float pa = ex2(fmaf(__uint_as_float(raw[j >> 5][j & 31]), scale_log2, -m_sub));
-          const float pb = ex2(fmaf(__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31]), scale_log2, -m_sub));
-          part[e] += pa + pb;
-          __nv_bfloat162 h = __floats2bfloat162_rn(pa, pb);
-          packed[e] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int j = 0; j < kKeys; j += 2) {
+        // 2^(score * scale - m): one multiply-add; -inf stays -inf and gives 0
+        const float pa = ex2(fmaf(__uint_as_float(raw[j >> 5][j & 31]), scale_log2, -m_sub));
+        const float pb = ex2(fmaf(__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31]), scale_log2, -m_sub));
+        part[(j >> 1) & 3] += pa + pb;
+        __nv_bfloat162 h = __floats2bfloat162_rn(pa, pb);
+        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      if (ok) {
+        tmem_st32(lane_base + (b & 1) * 64, packed);
+        tmem_wait_st();
       }
       l += (part[0] + part[1]) + (part[2] + part[3]);
       if (nvalid < kKeys) {
@@ -424,9 +437,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           const int r = nvalid + (i >> 4), c = i & 15;
           *reinterpret_cast<uint4*>(v_area + (c >> 3) * (kKeys * 128) + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        // generic-proxy writes must be visible to the tensor core's async-proxy reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      // generic-proxy writes (P, zeroed V rows) must be visible to the tensor core's async-proxy reads
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       bar_arrive(&p_ready[b & 1]);
     }
@@ -553,6 +566,23 @@ bool attention_tcgen05_supported(const PagedAttentionParams& p) {
   return encode_fn() != nullptr;
 }
 
+namespace {
+template <int kStagesKV>
+int launch_stages(const CUtensorMap& q_map, const CUtensorMap& k_map, const CUtensorMap& v_map, const FaParams& fp,
+                  dim3 grid, cudaStream_t stream) {
+  auto kernel = attention_tcgen05_kernel<kStagesKV>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           FaSmemT<kStagesKV>::kBytes);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  return (int)launch_chain(kernel, grid, dim3(192), FaSmemT<kStagesKV>::kBytes, stream, dim3(1, 1, 1), q_map, k_map,
+                           v_map, fp);
+}
+}  // namespace
+
 int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream) {
   const int G = p.num_heads / p.num_kv_heads;
   const int tq = kRows / G;
@@ -563,17 +593,26 @@ int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream)
   if (!q_map_for(p.q, p.num_tokens, p.num_heads, G, tq, &q_map) || !cache_map(p.k_cache, rows, box_rows, &k_map) ||
       !cache_map(p.v_cache, rows, box_rows, &v_map))
     return (int)cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           FaSmem::kBytes);
-    if (err != cudaSuccess) return (int)err;
-    configured = true;
-  }
   FaParams fp{p, tq, subtiles, box_rows};
   const dim3 grid((unsigned)(p.num_tiles * subtiles), (unsigned)p.num_kv_heads, 1u);
-  return (int)launch_chain(attention_tcgen05_kernel, grid, dim3(192), FaSmem::kBytes, stream, dim3(1, 1, 1), q_map,
-                           k_map, v_map, fp);
+  // more CTAs than SMs: two per SM, two K/V stages each; fewer: one per SM with four stages.  Measured:
+  // a 2,048-token prompt (512 CTAs) 86 us with two per SM against 101 us with one; a 512-token portion after
+  // 7,680 keys (128 CTAs) 160 us with the deep ring against 191 us with the shallow one.
+  static const int forced = [] {
+    const char* v = getenv("AKV_PROMPT_STAGES");
+    const int n = v ? atoi(v) : 0;
+    return (n == 2 || n == 4) ? n : 0;
+  }();
+  static const int sms = [] {
+    int device = 0, count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      count = 148;
+    return count;
+  }();
+  const bool shallow = forced ? forced == 2 : (int64_t)grid.x * grid.y > sms;
+  if (shallow) return launch_stages<2>(q_map, k_map, v_map, fp, grid, stream);
+  return launch_stages<4>(q_map, k_map, v_map, fp, grid, stream);
 }
 
 }  // namespace akv
