@@ -203,7 +203,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   constexpr uint32_t kTmemCols = 256;            // S: columns 0-63 and 64-127, O: columns 128-255
 
   pdl_launch_dependents();
-  const int batch_tile = blockIdx.x / fp.subtiles, sub = blockIdx.x - batch_tile * fp.subtiles;
+  // CTAs start in index order and a sequence's later tiles see more keys: walk the tiles backwards, longest first
+  const int slot = blockIdx.x / fp.subtiles, sub = blockIdx.x - slot * fp.subtiles;
+  const int batch_tile = (int)(gridDim.x / fp.subtiles) - 1 - slot;
   const int seq = p.tile_seq[batch_tile];
   const int q0 = p.tile_q0[batch_tile] + fp.tq * sub;
   const int nq = min(fp.tq, p.tile_nq[batch_tile] - fp.tq * sub);
