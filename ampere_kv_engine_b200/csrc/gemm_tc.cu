@@ -265,7 +265,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     if constexpr (kNormedX) {
       // The token operand is the RMS norm of the residual stream, made here: x = hidden * inv_rms * weight,
       // rounded to bfloat16 and laid out as the TMA would (rows of 128 bytes, 16-byte chunk c of row r at
-      // c ^ (r & 7)).  Warp q makes the K blocks kb = q, q + 4, ...: four blocks are under way at a time.
+      // c ^ (r & 7)).  Warp q makes the K blocks kb = q, q + 4, ...: up to four blocks are under way at a time.
       const GemmNormedX& nx = p.normed;
       pdl_wait();      // hidden and its sums of squares come from the kernels before this one
       const int t = quarter * 32 + lane;
@@ -275,7 +275,10 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         inv_rms[t] = rsqrtf(ss / (float)p.k + nx.eps);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int kb = quarter; kb < num_kb && ok; kb += 4) {
+      // A stage must always be written by the same warp, so that the warp sees each of the stage's "empty" phases
+      // in turn (a parity wait two phases late answers wrongly): with three stages three warps work.
+      constexpr int kXWarps = kStages < 4 ? kStages : 4;
+      for (int kb = quarter; quarter < kXWarps && kb < num_kb && ok; kb += kXWarps) {
         const int s = kb % kStages;
         if (kb >= kStages && !mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
           ok = false;
@@ -522,13 +525,13 @@ int launch_stages(const CUtensorMap& w_map, const CUtensorMap& x_map, const Gemm
   return (int)launch_chain(kernel, grid, dim3(192), GemmSmem<BN, kStages>::kBytes, stream, cluster, w_map, x_map, p);
 }
 
-// Stages of the TMA ring.  Four stages of 18-24 KB let three (two at 64 tokens) CTAs share an SM.
-// AKV_GEMM_STAGES=2|4|8 in the environment overrides it for the plain product (for measurements).
+// Stages of the TMA ring of the plain product when AKV_GEMM_STAGES=2|3|4|8 is set in the environment (for
+// measurements); 0: the default of the token count.
 int ring_stages() {
   static const int stages = [] {
     const char* v = getenv("AKV_GEMM_STAGES");
-    const int n = v ? atoi(v) : 4;
-    return (n == 2 || n == 8) ? n : 4;
+    const int n = v ? atoi(v) : 0;
+    return (n == 2 || n == 3 || n == 4 || n == 8) ? n : 0;
   }();
   return stages;
 }
@@ -536,12 +539,17 @@ int ring_stages() {
 template <int BN, bool kNormedX>
 int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmParams& p, int epilogue, bool bf16_out,
               cudaStream_t stream) {
+  // 16 tokens: four stages of 18 KB; 32 and 64 tokens: three stages of 20 and 24 KB.  Either way three CTAs share
+  // an SM (with four stages of 20 KB only two did, and the wide projections took 27 % longer).
+  constexpr int kDefault = BN == 16 ? 4 : 3;
   switch (epilogue) {
-    case kEpilogueGated: return launch_stages<BN, __nv_bfloat16, 4, kEpilogueGated, kNormedX>(w_map, x_map, p, stream);
-    case kEpilogueQkv: return launch_stages<BN, __nv_bfloat16, 4, kEpilogueQkv, kNormedX>(w_map, x_map, p, stream);
+    case kEpilogueGated:
+      return launch_stages<BN, __nv_bfloat16, kDefault, kEpilogueGated, kNormedX>(w_map, x_map, p, stream);
+    case kEpilogueQkv:
+      return launch_stages<BN, __nv_bfloat16, kDefault, kEpilogueQkv, kNormedX>(w_map, x_map, p, stream);
     case kEpilogueResidual:
       if constexpr (kNormedX) return (int)cudaErrorInvalidValue;
-      else return launch_stages<BN, float, 4, kEpilogueResidual, false>(w_map, x_map, p, stream);
+      else return launch_stages<BN, float, kDefault, kEpilogueResidual, false>(w_map, x_map, p, stream);
     default: break;
   }
   if constexpr (!kNormedX) {
@@ -552,9 +560,14 @@ int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmPara
     if (stages == 8)
       return bf16_out ? launch_stages<BN, __nv_bfloat16, 8, kEpiloguePlain, false>(w_map, x_map, p, stream)
                       : launch_stages<BN, float, 8, kEpiloguePlain, false>(w_map, x_map, p, stream);
+    if (stages == 3 || stages == 4) {
+      if (stages == 7 - kDefault)      // the other of 3 and 4
+        return bf16_out ? launch_stages<BN, __nv_bfloat16, 7 - kDefault, kEpiloguePlain, false>(w_map, x_map, p, stream)
+                        : launch_stages<BN, float, 7 - kDefault, kEpiloguePlain, false>(w_map, x_map, p, stream);
+    }
   }
-  return bf16_out ? launch_stages<BN, __nv_bfloat16, 4, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream)
-                  : launch_stages<BN, float, 4, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream);
+  return bf16_out ? launch_stages<BN, __nv_bfloat16, kDefault, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream)
+                  : launch_stages<BN, float, kDefault, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream);
 }
 
 template <bool kNormedX>

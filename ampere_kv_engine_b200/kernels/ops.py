@@ -258,6 +258,11 @@ def _operand(x, weight: torch.Tensor):
 #: up to 64; measured on B200 the library is faster from 33 tokens on)
 SMALL_M_LIMIT = 32
 use_small_m_gemm = True
+#: up to this many tokens a decode branch adds to the residual stream inside its last product and the next product
+#: applies the norm to its own token operand.  Every CTA of that product re-reads the float32 stream for its K
+#: range, which grows with the tokens: measured per decode step on B200, the pair saves 94 us at 4 tokens and 37 us
+#: at 8, and costs 30 us at 12, 160 us at 16 and 1.3 ms at 32.
+LAZY_NORM_LIMIT = 8
 #: hand split-K partial sums to the consuming kernel instead of adding them up inside the product kernel
 prefer_partials = False
 
@@ -304,8 +309,8 @@ def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Te
     """``hidden += bfloat16(x @ weight.T)`` inside the small-batch product kernel, which also leaves the sums of
     squares of the new ``hidden`` for the next norm.  None when that kernel does not take the sizes: the caller
     then computes the product and hands it to the norm as a pending delta."""
-    if not (_takes_small_m(x, weight) and hidden.dtype == torch.float32 and hidden.is_contiguous()
-            and hidden.shape == (x.shape[0], weight.shape[0])):
+    if not (x.shape[0] <= LAZY_NORM_LIMIT and _takes_small_m(x, weight) and hidden.dtype == torch.float32
+            and hidden.is_contiguous() and hidden.shape == (x.shape[0], weight.shape[0])):
         return None
     ssq = torch.empty(((weight.shape[0] + 127) // 128, x.shape[0]), dtype=torch.float32, device=x.device)
     ext().small_m_gemm_residual(x, weight, hidden, ssq, _cluster_splits(weight), status)
