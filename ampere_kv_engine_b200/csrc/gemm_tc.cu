@@ -195,21 +195,24 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   float res_old = 0.f;                                                 // kEpilogueResidual: likewise
 
   if (warp == 0) {
+    // The weights do not depend on the kernel before this one: fill the ring's weight halves first, then wait
+    // for that kernel and fetch the activations.  (kNormedX: warps 2-5 make the token tiles.)  The first copies
+    // are issued by one lane per stage, side by side: a thread spends about 100 ns on each copy it issues, and
+    // the activation copies come after the wait, where that time is not hidden.
+    constexpr uint32_t kTxBytes = kNormedX ? GemmSmem<BN, kStages>::kA : GemmSmem<BN, kStages>::kStage;
+    const int ahead = min(num_kb, kStages);
+    if (lane < ahead) {
+      mbar_expect_tx(&full[lane], kTxBytes);
+      tma_load_2d(smem + lane * GemmSmem<BN, kStages>::kStage, &w_map, (kb_begin + lane) * kTileK, tile * kTileM, &full[lane]);
+    }
+    if constexpr (!kNormedX) {
+      pdl_wait();
+      if (lane < ahead)
+        tma_load_2d(smem + lane * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA, &x_map,
+                    (kb_begin + lane) * kTileK, 0, &full[lane]);
+    }
+    __syncwarp();
     if (lane == 0) {
-      // The weights do not depend on the kernel before this one: fill the ring's weight halves first, then wait
-      // for that kernel and fetch the activations.  (kNormedX: warps 2-5 make the token tiles.)
-      constexpr uint32_t kTxBytes = kNormedX ? GemmSmem<BN, kStages>::kA : GemmSmem<BN, kStages>::kStage;
-      const int ahead = min(num_kb, kStages);
-      for (int kb = 0; kb < ahead; ++kb) {
-        mbar_expect_tx(&full[kb], kTxBytes);
-        tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage, &w_map, (kb_begin + kb) * kTileK, tile * kTileM, &full[kb]);
-      }
-      if constexpr (!kNormedX) {
-        pdl_wait();
-        for (int kb = 0; kb < ahead; ++kb)
-          tma_load_2d(smem + kb * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA, &x_map, (kb_begin + kb) * kTileK, 0,
-                      &full[kb]);
-      }
       for (int kb = ahead; kb < num_kb; ++kb) {
         const int s = kb % kStages;
         if (!mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
