@@ -470,6 +470,50 @@ def test_tcgen05_prompt_attention_repeats_and_rescales(ops):
     torch.testing.assert_close(case.run(ops, 0, 1, kernel="mma"), want, **tol(dtype))
 
 
+def _last_rows_reference(case, window=0):
+    """The plain attention formula for the last q_len positions of each sequence only (float64), for contexts too
+    long for the whole-sequence form: query i sees key j iff j <= i (and j > i - window)."""
+    outs = []
+    group = case.nh // case.nkv
+    for s, (n, c) in enumerate(zip(case.q_lens, case.ctx_lens)):
+        q = case.q_seq[s].double()                                            # [n, NH, D]
+        k = case.k_seq[s].double().repeat_interleave(group, dim=1)            # [c, NH, D]
+        v = case.v_seq[s].double().repeat_interleave(group, dim=1)
+        scores = torch.einsum("thd,shd->hts", q, k) * case.d ** -0.5
+        i = torch.arange(c - n, c)[:, None]
+        j = torch.arange(c)[None, :]
+        visible = j <= i
+        if window:
+            visible &= j > i - window
+        probs = torch.softmax(scores.masked_fill(~visible[None], -torch.inf), dim=-1)
+        outs.append(torch.einsum("hts,shd->thd", probs, v).reshape(n, -1).float())
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("window", [0, 3000])
+def test_attention_over_thousands_of_keys(ops, window):
+    """Contexts of several thousand keys, where the K/V rings of the tensor-core kernels wrap hundreds of times:
+    prompt portions after a long history (tcgen05 and mma.sync kernels), and decoded tokens with every way of
+    splitting the keys.  One far key is made to matter in the longest sequence."""
+    dtype = torch.bfloat16
+    case = PagedCase(dtype, 8, 2, 128, 16, q_lens=[200, 37, 64], ctx_lens=[6000, 4100, 2500], seed=41, q_tile=32)
+    far = 77
+    for kv in range(2):
+        direction = torch.nn.functional.normalize(case.k_seq[0][far, kv].float(), dim=0)
+        case.k_seq[0][far, kv] = (7.0 * direction).to(dtype)
+        for h in range(4 * kv, 4 * kv + 4):
+            case.q_seq[0][:, h] = (case.q_seq[0][:, h].float() + 20.0 * direction).to(dtype)
+    case.rewrite_cache()
+    want = _last_rows_reference(case, window)
+    for kernel in ("auto", "mma"):
+        torch.testing.assert_close(case.run(ops, window, 1, kernel=kernel), want, **tol(dtype))
+    decode = PagedCase(dtype, 8, 2, 128, 16, q_lens=[1, 1, 1, 1], ctx_lens=[6000, 4100, 1, 2500], seed=42)
+    want = _last_rows_reference(decode, window)
+    for splits in (1, 2, 4, 8):
+        torch.testing.assert_close(decode.run(ops, window, splits), want, **tol(dtype))
+    torch.testing.assert_close(decode.run(ops, window, 5, kernel="general"), want, **tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_paged_attention_decode_batch_and_scale(ops, dtype):
     case = PagedCase(dtype, 8, 2, 64, 16, q_lens=[1] * 7, ctx_lens=[1, 15, 16, 17, 300, 64, 65], seed=9)
