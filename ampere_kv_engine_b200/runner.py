@@ -10,8 +10,10 @@ library's own forward; ``generate``; ``benchmark``: timed repeats after one warm
 the reference's ``int8`` cache is outside this engine), ``--decode-kernel`` (the reference
 picks between its two decode kernels; here ``auto`` is the only choice).  The reference reads a
 line of text and a tokenizer turns it into ids (runner.py:687, :22-28); this engine takes token
-ids: from ``--prompt-ids`` (a JSON file or a comma-separated list) or, like the reference, from
-one line of standard input.
+ids: from ``--prompt-ids`` (a JSON file or a comma-separated list), ``--prompt-len`` (that many
+seeded uniform ids) or, like the reference, from one line of standard input.  Instead of a
+model folder, ``--random-config FILE --random-seed S`` builds the model of a config.json with
+seeded random weights (the reference has no such mode: it runs one published checkpoint).
 
 ``generate_tokens`` is the single-request Python entry point with the reference's name and
 keyword meanings (runner.py:301-406).
@@ -77,7 +79,10 @@ def _read_prompt(arg: str | None) -> list[int]:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description="Qwen3 generation on one B200: generate, check against the float32 "
                                                  "path, or time repeats")
-    parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    parser.add_argument("--model", default=None, help="folder with config.json and model.safetensors")
+    parser.add_argument("--random-config", default=None,
+                        help="a config.json to build with seeded random weights instead of --model")
+    parser.add_argument("--random-seed", type=int, default=0, help="seed of the random weights")
     parser.add_argument("--mode", choices=("check", "generate", "benchmark"), default="check",
                         help="check: compare every step with the float32 path; generate; benchmark: timed repeats")
     parser.add_argument("--repeats", type=int, default=3, help="timed runs of benchmark mode (one warm-up before)")
@@ -87,15 +92,23 @@ def main(argv=None) -> int:
     parser.add_argument("--decode-kernel", choices=("auto",), default="auto", help="attention kernel choice")
     parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
     parser.add_argument("--prompt-ids", default=None, help="JSON file, or comma-separated token ids")
+    parser.add_argument("--prompt-len", type=int, default=None,
+                        help="use this many seeded uniform token ids as the prompt (seed: --seed)")
     parser.add_argument("--max-new-tokens", type=int, default=MAX_NEW_TOKENS)
     parser.add_argument("--temperature", type=float, default=0.0)
     parser.add_argument("--seed", type=int, default=0, help="sampling seed")
     parser.add_argument("--ignore-eos", action="store_true")
     parser.add_argument("--page-size", type=int, default=PAGED_BLOCK_SIZE)
     parser.add_argument("--max-batch-tokens", type=int, default=2048)
+    parser.add_argument("--num-pages", type=int, default=None,
+                        help="pages of the cache pool (default: enough for the prompt and the new tokens)")
     args = parser.parse_args(argv)
     if args.repeats < 1:
         parser.error("--repeats must be positive")
+    if (args.model is None) == (args.random_config is None):
+        parser.error("give --model DIR or --random-config FILE")
+    if args.prompt_len is not None and (args.prompt_ids is not None or args.prompt_len < 1):
+        parser.error("--prompt-len is a positive count and goes without --prompt-ids")
     want_kv = {"bfloat16": "bf16", "float32": "fp32"}[args.dtype]
     if args.kv_dtype is not None and args.kv_dtype != want_kv:
         parser.error(f"--kv-dtype {args.kv_dtype} does not go with --dtype {args.dtype}: the cache dtype is the "
@@ -105,11 +118,30 @@ def main(argv=None) -> int:
         raise RuntimeError("generation needs a CUDA device")
     from .engine.engine import Engine
 
-    prompt = _read_prompt(args.prompt_ids)
+    if args.random_config is not None:
+        with open(args.random_config, "r", encoding="utf-8") as handle:
+            raw_config = json.load(handle)
+
+        def build(dtype, **options):
+            return Engine.from_random(raw_config, args.random_seed, dtype=dtype, **options)
+        vocab = int(raw_config["vocab_size"])
+    else:
+        from .models.registry import load_config
+
+        def build(dtype, **options):
+            return Engine.from_pretrained(args.model, dtype=dtype, **options)
+        vocab = int(load_config(args.model)[1].vocab_size)
+    if args.prompt_len is not None:
+        generator = torch.Generator().manual_seed(args.seed)
+        prompt = torch.randint(0, vocab, (args.prompt_len,), generator=generator).tolist()
+    else:
+        prompt = _read_prompt(args.prompt_ids)
     tokens = len(prompt) + args.max_new_tokens
     options = dict(page_size=args.page_size, max_tokens=tokens + 64, max_seqs=4, max_batch_tokens=args.max_batch_tokens)
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, **options)
-    print(f"model={args.model} mode={args.mode} cache={args.cache} dtype={args.dtype} prompt_tokens={len(prompt)}")
+    if args.num_pages is not None:
+        options["num_pages"] = args.num_pages
+    engine = build(args.dtype, **options)
+    print(f"model={args.model or args.random_config} mode={args.mode} cache={args.cache} dtype={args.dtype} prompt_tokens={len(prompt)}")
     if args.mode == "benchmark":
         generate_tokens(engine, prompt, max_new_tokens=args.max_new_tokens, ignore_eos=True)
         totals, ttfts, tpots = [], [], []
@@ -132,7 +164,7 @@ def main(argv=None) -> int:
         if args.dtype == "float32":
             print("check: the run itself is the float32 path; nothing to compare")
             return 0
-        reference = Engine.from_pretrained(args.model, dtype="float32", **options)
+        reference = build("float32", **options)
         from .engine.batch import SeqStep
         seq_a, seq_b = engine.runner.open("check"), reference.runner.open("check")
         feed, worst, agree = list(prompt), 0.0, 0

@@ -156,3 +156,23 @@ def test_command_line_generate(tmp_path):
     got = json.loads(line.split(" = ", 1)[1])
     w = plain_weights(folder, "float32")
     assert got == plain.greedy_generate(w, tiny.CONFIGS["A"][0], prompt, 5)
+
+
+def test_command_line_random_config_and_check_mode(tmp_path):
+    """``--random-config`` builds seeded random weights without a model folder, ``--prompt-len`` makes a seeded
+    prompt, and the default mode (check) compares the bfloat16 run with the float32 path step by step."""
+    config_file = tmp_path / "config.json"
+    config_file.write_text(json.dumps(tiny.config("C")))
+    cmd = [sys.executable, "-m", "ampere_kv_engine_b200.runner", "--random-config", str(config_file), "--random-seed", "4",
+           "--prompt-len", "37", "--max-new-tokens", "6", "--ignore-eos", "--num-pages", "16"]
+    proc = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert "prompt_tokens=37" in proc.stdout and "mode=check" in proc.stdout
+    line = [l for l in proc.stdout.splitlines() if l.startswith("generated_token_ids = ")][0]
+    assert len(json.loads(line.split(" = ", 1)[1])) == 6
+    check = [l for l in proc.stdout.splitlines() if l.startswith("check: ")][0]
+    assert "steps pick the same token" in check
+    # neither a folder nor a configuration: refused with the two ways named
+    proc = subprocess.run([sys.executable, "-m", "ampere_kv_engine_b200.runner", "--mode", "generate"], cwd=ROOT,
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode != 0 and "--model DIR or --random-config FILE" in proc.stderr
