@@ -297,6 +297,111 @@ __global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_write_fast_kerne
   }
 }
 
+// bfloat16 heads of 64, 128 or 256 dims, rotated whole or not at all, with 16-byte accesses: LPH = D / 16 lanes
+// share a head, lane s of them owns dims [8s, 8s + 8) of the low half and their partners in the high half, so a warp
+// takes 32 / LPH heads at a time and a block of four warps all heads of one token in a few passes.  The kernel above
+// spends about 50 instructions per element on indexing when every lane owns four elements (it was bound by
+// instruction issue: 32 us for 2,048 tokens of 48 heads, a tenth of the DRAM bandwidth); here a lane owns 16.
+template <int LPH>
+__global__ void __launch_bounds__(128) qk_norm_rope_write_vec_kernel(QkRopeWriteParams p) {
+  constexpr int D = LPH * 16, half = D / 2, kHeadsPerWarp = 32 / LPH;
+  __shared__ float cs[D];   // cos [half], sin [half] of this token's angles
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_heads = p.num_heads + 2 * p.num_kv_heads;
+  const int64_t token = blockIdx.x;
+  const bool rotary = p.inv_freq != nullptr;
+  if (rotary && threadIdx.x < half) {
+    float sn, co;
+    sincosf((float)p.positions[token] * p.inv_freq[threadIdx.x], &sn, &co);
+    cs[threadIdx.x] = co;
+    cs[half + threadIdx.x] = sn;
+  }
+  // the token's cache slot, once, in 32-bit arithmetic (the host checked that the pool's slots fit)
+  int page = -1, off = 0;
+  if (p.slots != nullptr && p.k_cache != nullptr) {
+    const int slot = p.slots[token];
+    if (slot >= (int)(p.num_pages * p.page_size)) {
+      if (threadIdx.x == 0) set_status(p.status, kBadSlot);
+    } else if (slot >= 0) {
+      page = slot / p.page_size;
+      off = slot - page * p.page_size;
+    }
+  }
+  __syncthreads();
+  const int sub = lane % LPH, d0 = sub * 8;
+  const __nv_bfloat16* row = (const __nv_bfloat16*)p.qkv + token * (int64_t)total_heads * D;
+  for (int base = 0; base < total_heads; base += 4 * kHeadsPerWarp) {
+    const int head = base + warp * kHeadsPerWarp + lane / LPH;
+    const bool active = head < total_heads;
+    float lo[8], hi[8];
+    if (active) {
+      load8<__nv_bfloat16>(row + head * D + d0, lo);
+      load8<__nv_bfloat16>(row + head * D + half + d0, hi);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) lo[e] = hi[e] = 0.f;
+    }
+    const bool is_q = head < p.num_heads;
+    const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
+    const int local = is_q ? head : (is_k ? head - p.num_heads : head - p.num_heads - p.num_kv_heads);
+    const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
+    // the sum of squares is taken by all lanes (inactive heads sum zeros), so the shuffles stay warp-wide
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!active) continue;
+    if (w != nullptr) {
+      const float inv = rsqrtf(ss / (float)D + p.eps);
+      float wl[8], wh[8];
+      load8<float>(w + d0, wl);
+      load8<float>(w + half + d0, wh);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        lo[e] = lo[e] * inv * wl[e];
+        hi[e] = hi[e] * inv * wh[e];
+      }
+    }
+    if (rotary && (is_q || is_k)) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float co = cs[d0 + e], sn = cs[half + d0 + e];
+        const float a = lo[e], b = hi[e];
+        lo[e] = a * co - b * sn;
+        hi[e] = b * co + a * sn;
+      }
+    }
+    uint4 out_lo, out_hi;
+    {
+      __nv_bfloat162 v0 = __floats2bfloat162_rn(lo[0], lo[1]), v1 = __floats2bfloat162_rn(lo[2], lo[3]);
+      __nv_bfloat162 v2 = __floats2bfloat162_rn(lo[4], lo[5]), v3 = __floats2bfloat162_rn(lo[6], lo[7]);
+      out_lo = make_uint4(*reinterpret_cast<uint32_t*>(&v0), *reinterpret_cast<uint32_t*>(&v1),
+                          *reinterpret_cast<uint32_t*>(&v2), *reinterpret_cast<uint32_t*>(&v3));
+      v0 = __floats2bfloat162_rn(hi[0], hi[1]); v1 = __floats2bfloat162_rn(hi[2], hi[3]);
+      v2 = __floats2bfloat162_rn(hi[4], hi[5]); v3 = __floats2bfloat162_rn(hi[6], hi[7]);
+      out_hi = make_uint4(*reinterpret_cast<uint32_t*>(&v0), *reinterpret_cast<uint32_t*>(&v1),
+                          *reinterpret_cast<uint32_t*>(&v2), *reinterpret_cast<uint32_t*>(&v3));
+    }
+    __nv_bfloat16* dense = nullptr;
+    if (is_q) dense = (__nv_bfloat16*)p.q_out + (token * p.num_heads + local) * (int64_t)D;
+    else if (is_k && p.k_out) dense = (__nv_bfloat16*)p.k_out + (token * p.num_kv_heads + local) * (int64_t)D;
+    else if (!is_k && p.v_out) dense = (__nv_bfloat16*)p.v_out + (token * p.num_kv_heads + local) * (int64_t)D;
+    if (dense != nullptr) {
+      *reinterpret_cast<uint4*>(dense + d0) = out_lo;
+      *reinterpret_cast<uint4*>(dense + half + d0) = out_hi;
+    }
+    if (!is_q && page >= 0) {
+      __nv_bfloat16* cache = (__nv_bfloat16*)(is_k ? p.k_cache : p.v_cache) +
+                             (((int64_t)page * p.num_kv_heads + local) * p.page_size + off) * D;
+      *reinterpret_cast<uint4*>(cache + d0) = out_lo;
+      *reinterpret_cast<uint4*>(cache + half + d0) = out_hi;
+    }
+  }
+}
+
 int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0) return 0;
   if (p.head_dim % 2 || p.head_dim / 2 > 32 * kMaxPairsPerLane) return (int)cudaErrorInvalidValue;
@@ -306,6 +411,19 @@ int launch_qk_norm_rope_write(const QkRopeWriteParams& p, cudaStream_t stream) {
   const int64_t nz = (p.num_tokens + 65534) / 65535;
   if (nz > 65535) return (int)cudaErrorInvalidValue;
   const bool whole_or_none = p.inv_freq == nullptr || p.rotary_dim == p.head_dim || p.rotary_dim == 0;
+  const auto aligned16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+  if (p.dtype == kBFloat16 && p.qkv_parts == 0 && whole_or_none && p.num_tokens <= 0x7fffffffLL &&
+      (p.head_dim == 64 || p.head_dim == 128 || p.head_dim == 256) &&
+      p.num_pages * (int64_t)p.page_size <= 0x7fffffffLL && aligned16(p.qkv) && aligned16(p.q_out) &&
+      aligned16(p.k_out) && aligned16(p.v_out) && aligned16(p.k_cache) && aligned16(p.v_cache) &&
+      aligned16(p.q_weight) && aligned16(p.k_weight)) {
+    QkRopeWriteParams q = p;
+    if (q.rotary_dim != q.head_dim) q.inv_freq = nullptr;
+    const dim3 grid((unsigned)p.num_tokens), block(128), one(1, 1, 1);
+    if (p.head_dim == 64) return (int)launch_chain(qk_norm_rope_write_vec_kernel<4>, grid, block, 0, stream, one, q);
+    if (p.head_dim == 128) return (int)launch_chain(qk_norm_rope_write_vec_kernel<8>, grid, block, 0, stream, one, q);
+    return (int)launch_chain(qk_norm_rope_write_vec_kernel<16>, grid, block, 0, stream, one, q);
+  }
   if (p.qkv_parts == 0 && p.head_dim % 4 == 0 && whole_or_none && p.head_dim / 4 <= 32 * kMaxUnitsPerLane) {
     QkRopeWriteParams q = p;
     if (q.rotary_dim != q.head_dim) q.inv_freq = nullptr;

@@ -142,7 +142,8 @@ def _qkv_reference(qkv, positions, q_w, k_w, nh, nkv, d, eps, theta):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,d,page", [(6, 3, 48, 8), (8, 1, 128, 16), (4, 4, 80, 32), (2, 1, 256, 16)])
+@pytest.mark.parametrize("nh,nkv,d,page", [(6, 3, 48, 8), (8, 1, 128, 16), (4, 4, 80, 32), (2, 1, 256, 16), (5, 5, 64, 8),
+                                           (7, 1, 128, 32)])
 def test_qk_norm_rope_write(ops, dtype, nh, nkv, d, page):
     g = torch.Generator().manual_seed(d)
     n, pages, eps, theta = 29, 12, 1e-5, 50000.0
