@@ -293,8 +293,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int num_parts, T
     g = to_float<TI>(row[gi]);
     u = to_float<TI>(row[ui]);
   }
-  // silu(g) = g * sigmoid(g), in float (ampere_kv/runner.py:176)
-  out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+  out[idx] = from_float<T>(silu_mul_value<T>(g, u));
 }
 
 template <typename T>
@@ -319,7 +318,7 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
     load4<T>(row + gi + block, u);
   }
 #pragma unroll
-  for (int e = 0; e < V; ++e) r[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+  for (int e = 0; e < V; ++e) r[e] = silu_mul_value<T>(g[e], u[e]);
   T* o = out + token * inter + i;
   if constexpr (sizeof(T) == 2) {
     float lo[4] = {r[0], r[1], r[2], r[3]}, hi[4] = {r[4], r[5], r[6], r[7]};

@@ -369,7 +369,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             }
             g = __bfloat162float(__float2bfloat16_rn(g));
             u = __bfloat162float(__float2bfloat16_rn(u));
-            out[(int64_t)token * out_features + feature] = from_float<OutT>(g / (1.f + expf(-g)) * u);
+            out[(int64_t)token * out_features + feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
           }
         }
       } else if constexpr (kEpilogue == kEpilogueQkv) {
