@@ -22,7 +22,9 @@ import types
 sys.dont_write_bytecode = True
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
-sys.path.insert(0, os.environ.get("REFERENCE_ROOT", "/root/reference"))
+if "REFERENCE_ROOT" not in os.environ:
+    sys.exit("set REFERENCE_ROOT to a checkout of the reference project (ampere-kv-engine)")
+sys.path.insert(0, os.environ["REFERENCE_ROOT"])
 
 import torch  # noqa: E402
 from safetensors.torch import save_file  # noqa: E402

@@ -71,7 +71,7 @@ def test_flagship_layer_sizes_in_both_precisions():
         worst32 = max(worst32, float(diff.max()))
     print(f"float32 vs plain: worst {worst32:.3e}")
     # bfloat16 against float32, every written row.  Stored activations are rounded to 8 bits of mantissa, and a
-    # logit is a sum of 4,096 such products after two layers of them: the error is judged against the row's own
+    # logit is a sum of 4,096 such products after two layers of them: the error is measured against the row's own
     # scale (its root mean square), as a whole (relative RMS error) and at its worst element.
     vocab = FLAGSHIP_LAYERS["vocab_size"]
     worst_rms = worst_peak = 0.0
