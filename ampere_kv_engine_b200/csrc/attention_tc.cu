@@ -95,7 +95,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 struct TcParams {
   PagedAttentionParams p;
   int box_rows;     // rows of one TMA box = min(page_size, keys per stage)
-  int use_tma;      // 1: pages arrive by TMA boxes; 0: by 16-byte cp.async copies (small pages, see issue_block_cp)
 };
 
 // Byte offset of (key k, 16-byte chunk c of the head) inside one stage's K or V area.  The area is laid out
@@ -305,55 +304,6 @@ __device__ __forceinline__ void zero_v_rows(uint8_t* stage, int first, int tid, 
   }
 }
 
-// The same block, fetched with 16-byte cp.async copies by the 32 lanes of a producer warp, into the same swizzled
-// layout.  A TMA copy of one 16-token page is a 2 KB box, and the SM's TMA unit takes on the order of 150 ns per
-// box whatever its size: measured on B200, a CTA streamed 16-token pages at 14 GB/s that way (8 boxes per
-// 32-key block), which caps decode attention near 3 TB/s and made the prompt kernel TMA-bound as well.  Plain
-// asynchronous copies have no such per-page cost.  Each lane finishes with cp.async.mbarrier.arrive.noinc on the
-// stage's barrier, which therefore counts 32 arrivals per producer warp.
-template <int D, int KT>
-__device__ __forceinline__ void issue_block_cp(const TcParams& tp, TableWindow& window, int kvh, int key0,
-                                               int key_end, uint8_t* stage, uint64_t* bar) {
-  const PagedAttentionParams& p = tp.p;
-  const int lane = threadIdx.x & 31;
-  const int P = p.page_size;
-  constexpr int CH = D * 2 / 16;                 // 16-byte chunks per row
-  // lane b keeps the page of the block's b-th run of (up to) 8 keys; runs never straddle a page (P >= 8)
-  int my_page = -1;
-#pragma unroll
-  for (int b = 0; b < KT / 8; ++b) {
-    const int key = key0 + b * 8;
-    int page = -1;
-    if (key < key_end) {
-      page = window.page(key / P, lane);
-      if (page < 0 || page >= p.num_pages) {
-        if (lane == 0) set_status(p.status, kBadPage);
-        page = -1;
-      }
-    }
-    if (lane == b) my_page = page;
-  }
-  const uint32_t stage_addr = smem_addr(stage);
-  const char* k_base = (const char*)p.k_cache;
-  const char* v_base = (const char*)p.v_cache;
-#pragma unroll 4
-  for (int i = 0; i < 2 * KT * CH / 32; ++i) {
-    const int c = i * 32 + lane;
-    const int kv = c / (KT * CH);
-    const int rem = c - kv * (KT * CH);
-    const int row = rem / CH, ch = rem - row * CH;
-    const int key = key0 + row;
-    const int page = __shfl_sync(0xffffffffu, my_page, row >> 3);
-    if (key < key_end && page >= 0) {
-      const char* src = (kv ? v_base : k_base) +
-                        ((((int64_t)page * p.num_kv_heads + kvh) * P + key % P) * (int64_t)D) * 2 + ch * 16;
-      const uint32_t dst = stage_addr + (kv ? KT * D * 2 : 0) + tile_offset_d<D, KT>(row, ch);
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-    }
-  }
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
@@ -424,7 +374,7 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], tp.use_tma ? kProducers : 32 * kProducers);
+      mbar_init(&full[s], kProducers);
       mbar_init(&empty[s], DECODE ? 1 : consumers);     // decode: a block belongs to one consumer warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -445,12 +395,8 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
         ok = false;
         break;
       }
-      if (tp.use_tma)
-        issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi,
-                           smem + s * Smem<D, KT, STAGES>::kStage, &full[s], warp - consumers, kProducers);
-      else
-        issue_block_cp<D, KT>(tp, window, kvh, range_lo + b * KT, range_hi, smem + s * Smem<D, KT, STAGES>::kStage,
-                              &full[s]);
+      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi,
+                         smem + s * Smem<D, KT, STAGES>::kStage, &full[s], warp - consumers, kProducers);
     }
   } else {
     // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
@@ -696,7 +642,7 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], tp.use_tma ? 1 : 32);
+      mbar_init(&full[s], 1);
       mbar_init(&empty[s], kCoopWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -715,11 +661,9 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
     // kernel (which writes this step's K and V) still runs, as far as the ring has room.
     const int first_new = ctx - q_len;
     int b = 0;
-    if (tp.use_tma) {
-      for (; b < num_blocks && b < STAGES && min(range_lo + (b + 1) * KT, range_hi) <= first_new; ++b)
-        issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + b * Layout::kStage,
-                           &full[b], 0, 1);
-    }
+    for (; b < num_blocks && b < STAGES && min(range_lo + (b + 1) * KT, range_hi) <= first_new; ++b)
+      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + b * Layout::kStage,
+                         &full[b], 0, 1);
     pdl_wait();      // this step's K/V pages come from the previous kernels
     for (; b < num_blocks; ++b) {
       const int s = b % STAGES;
@@ -727,11 +671,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
         ok = false;
         break;
       }
-      if (tp.use_tma)
-        issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage,
-                           &full[s], 0, 1);
-      else
-        issue_block_cp<D, KT>(tp, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage, &full[s]);
+      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage,
+                         &full[s], 0, 1);
     }
   } else {
     pdl_wait();      // q comes from the previous kernel
@@ -994,8 +935,6 @@ bool cache_map(const void* base, int64_t rows, int head_dim, int box_rows, CUten
 }
 
 constexpr int kDecodeConsumers = 4;
-constexpr int kMinTmaRows = 8;     // pages of at least this many tokens are fetched as TMA boxes (all of them; the
-                                   // cp.async path is kept for measurements: one warp cannot keep enough copies in flight)
 
 template <int D, int KT, int STAGES, int WARPS, int MIN_CTAS>
 int launch_prompt(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
@@ -1009,7 +948,7 @@ int launch_prompt(const PagedAttentionParams& p, int box_rows, const CUtensorMap
     configured = true;
   }
   const int G = p.num_heads / p.num_kv_heads;
-  TcParams tp{p, box_rows, box_rows >= kMinTmaRows ? 1 : 0};
+  TcParams tp{p, box_rows};
   const dim3 grid((unsigned)(p.num_tiles * ((p.q_tile + 15) / 16)), (unsigned)p.num_kv_heads, 1u);
   const dim3 block(32 * (G + kProducers));      // one consumer warp per q-head of the group, and the producer
   return (int)launch_chain(kernel, grid, block, smem, stream, dim3(1, 1, 1), k_map, v_map, tp);
@@ -1026,7 +965,7 @@ int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& 
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  TcParams tp{p, box_rows, box_rows >= kMinTmaRows ? 1 : 0};
+  TcParams tp{p, box_rows};
   const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, (unsigned)p.num_splits);
   const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
   return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
