@@ -19,7 +19,7 @@ attention model asks for none; the slot is still taken and returned with the req
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 

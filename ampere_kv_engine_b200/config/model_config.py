@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, field, fields, asdict
+from dataclasses import dataclass, fields
 from typing import Any
 
 

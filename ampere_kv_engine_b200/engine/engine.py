@@ -10,7 +10,6 @@ from __future__ import annotations
 
 import torch
 
-from ..config.model_config import ConfigError
 from ..models.decoder import DecoderModel
 from ..models.registry import ARCHITECTURES, config_from_dict, load_config
 from ..sampling.sampler import Sampler, SamplingParams

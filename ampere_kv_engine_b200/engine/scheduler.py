@@ -42,7 +42,6 @@ from __future__ import annotations
 import time
 from dataclasses import dataclass, field
 
-from ..cache.block_pool import OutOfPages
 from ..cache.manager import SequenceCache
 from ..sampling.sampler import SamplingParams
 from .batch import SeqStep

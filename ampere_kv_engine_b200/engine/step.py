@@ -12,12 +12,9 @@ from __future__ import annotations
 
 import torch
 
-from ..cache.block_pool import OutOfPages
 from ..cache.manager import CacheManager, SequenceCache
 from ..kernels import ops
-import numpy as np
-
-from .batch import (BatchLayout, SeqStep, StepContext, build_context, fill_host, make_context, validate_entries)
+from .batch import BatchLayout, SeqStep, build_context, fill_host, make_context, validate_entries
 
 _STATUS_TEXT = {
     1: "a block-table entry pointed outside the page pool",

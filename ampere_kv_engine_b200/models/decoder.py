@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.spec import ModelSpec, PartSpec
+from ..config.spec import ModelSpec
 from ..parts import attention, block, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, CacheSpec, ParamSpec, build_part)
 from ..parts.embedding import LinearHead, TokenEmbedding

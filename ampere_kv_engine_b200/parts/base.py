@@ -12,7 +12,7 @@ blocks).  Registering a new kind is one decorator call and needs no change here.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable
 
 import torch

@@ -14,8 +14,6 @@ The ``window`` argument of :func:`causal_attention` extends the reference's mask
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 

@@ -5,7 +5,7 @@ import json
 import pytest
 
 import tiny
-from ampere_kv_engine_b200.config.model_config import ConfigError, Qwen3Config, read_config_json
+from ampere_kv_engine_b200.config.model_config import ConfigError, read_config_json
 from ampere_kv_engine_b200.models.registry import ARCHITECTURES, config_from_dict, load_config
 
 

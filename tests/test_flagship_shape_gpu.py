@@ -3,7 +3,6 @@
 implementation, and bfloat16 (tcgen05 prompt attention, fused decode kernels, split-K at K = 4096 and 12288)
 against float32 on the same bfloat16-stored weights, whole, decoded one by one, and mixed with page reuse."""
 
-import os
 import tempfile
 
 import pytest

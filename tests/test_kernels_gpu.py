@@ -2,7 +2,6 @@
 tiny models' (head sizes 48/80/128/256, group sizes 1/2/3/8, widths and vocabularies that are no power
 of two), in float32 and bfloat16."""
 
-import math
 
 import pytest
 import torch

@@ -5,7 +5,6 @@ properties of its parts."""
 import importlib.util
 import os
 
-import pytest
 import torch
 from safetensors.torch import load_file
 

@@ -9,7 +9,6 @@ import torch
 from ampere_kv_engine_b200.cache.manager import CacheManager
 from ampere_kv_engine_b200.engine.scheduler import (FINISHED, PREFILLING, RUNNING, WAITING, Scheduler)
 from ampere_kv_engine_b200.parts.base import CacheSpec
-from ampere_kv_engine_b200.sampling.sampler import SamplingParams
 
 VOCAB = 101
 

@@ -9,7 +9,7 @@ from safetensors.torch import load_file, save_file
 
 import tiny
 from ampere_kv_engine_b200.models.decoder import DecoderModel
-from ampere_kv_engine_b200.models.registry import ARCHITECTURES, config_from_dict
+from ampere_kv_engine_b200.models.registry import config_from_dict
 from ampere_kv_engine_b200.weights.loader import WeightError, load_weights
 from ampere_kv_engine_b200.weights.random_init import write_random_model
 from plain import qwen3_plain as plain
