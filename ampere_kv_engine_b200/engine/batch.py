@@ -56,6 +56,10 @@ class StepContext:
     tile_nq: torch.Tensor
     num_tiles: int
     q_tile: int                     # most rows any tile has
+    #: in a step that holds decoded tokens beside prompt portions, the tiles of the single-token sequences come
+    #: first and this is their count (0 in a step of one kind): attention runs them with key splits, apart from
+    #: the prompt tiles
+    num_decode_tiles: int
     max_context: int                # longest ctx_lens entry (host value)
     groups: list[GroupBatch]
     status: torch.Tensor | None     # int32[1] the kernels report bad indices in
@@ -131,6 +135,7 @@ def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout
     host[off[5]:off[5] + max(1, layout.num_logit_rows)] = 0
     put(5, [int(cu[s]) + w for s, e in enumerate(entries) for w in e.want])
     tiles = [(s, int(cu[s]) + q0, min(tile_rows, n - q0)) for s, n in enumerate(q_lens) for q0 in range(0, n, tile_rows)]
+    tiles.sort(key=lambda t: q_lens[t[0]] != 1)       # single-token sequences first, each kind in batch order
     if len(tiles) > layout.num_tiles:
         raise ValueError("the layout has too few attention tiles for this step")
     host[off[6]:off[6] + layout.num_tiles] = 0
@@ -167,6 +172,8 @@ def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_
     def view(index: int, size: int) -> torch.Tensor:
         return dev[off[index]:off[index] + size]
 
+    decoding = sum(1 for n in q_lens if n == 1)
+    num_decode_tiles = decoding if 0 < decoding < len(q_lens) else 0
     groups = []
     for gi, width in enumerate(layout.widths):
         groups.append(GroupBatch(view(9 + 2 * gi, layout.num_tokens),
@@ -176,7 +183,8 @@ def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_
         positions=view(1, layout.num_tokens), cu_q=view(2, layout.num_seqs + 1), ctx_lens=view(3, layout.num_seqs),
         state_slots=view(4, layout.num_seqs), logit_rows=view(5, layout.num_logit_rows),
         num_logit_rows=layout.num_logit_rows, tile_seq=view(6, layout.num_tiles), tile_q0=view(7, layout.num_tiles),
-        tile_nq=view(8, layout.num_tiles), num_tiles=layout.num_tiles, q_tile=tile_rows, max_context=max_context,
+        tile_nq=view(8, layout.num_tiles), num_tiles=layout.num_tiles, q_tile=tile_rows,
+        num_decode_tiles=num_decode_tiles, max_context=max_context,
         groups=groups, status=status, sampled=sampled, q_lens_host=q_lens, ctx_lens_host=ctx_lens,
         state_slots_host=state_slots, h2d_bytes=h2d_bytes)
 

@@ -186,12 +186,14 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
 
 def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
                     q_tile, num_splits, num_heads, num_kv_heads, window, scale, partials=None, status=None,
-                    kernel: str = "auto"):
+                    kernel: str = "auto", out=None):
     """Causal attention of the batch's new tokens over the paged cache.  ``kernel``: ``"auto"`` takes the
     tensor-core kernels where they fit (bfloat16, head size 64 or 128; prompt portions at head size 128 and groups
     of 2, 4 or 8 q-heads on tcgen05) and the general kernel elsewhere; ``"general"`` forces the latter, ``"mma"``
-    keeps prompt portions on the mma.sync kernel."""
-    out = torch.empty_like(q)
+    keeps prompt portions on the mma.sync kernel.  Only the rows of the given tiles are written; with ``out`` they
+    go into that tensor (a batch may be covered by two calls with different tile sizes)."""
+    if out is None:
+        out = torch.empty_like(q)
     if num_splits > 1 and partials is None:
         head_dim = q.shape[1] // num_heads
         partials = torch.empty((q.shape[0] * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32,

@@ -107,13 +107,20 @@ class PagedAttention(Mixer):
             q = q.contiguous()
         group_size = self.num_heads // self.num_kv_heads
         tensor_core = ops.attention_takes_tensor_cores(self.dtype, self.head_dim, group_size, cache.page_size)
-        splits = 1 if ctx.q_tile > 1 and tensor_core else ops.choose_splits(
-            ctx.num_tiles, self.num_kv_heads, ctx.q_tile * group_size, ctx.max_context, tensor_core)
-        out = ops.paged_attention(
-            q, cache.k_cache, cache.v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq, ctx.tile_q0,
-            ctx.tile_nq, num_tiles=ctx.num_tiles, q_tile=ctx.q_tile, num_splits=splits,
-            num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, window=self.window or 0, scale=self.scale,
-            status=ctx.status)
+        out = torch.empty_like(q)
+        # decoded tokens beside prompt portions: the single-token tiles (they come first) run apart, with their keys
+        # split over several CTAs; as one-row tiles of the prompt kernel each would walk its whole context alone
+        first = getattr(ctx, "num_decode_tiles", 0)
+        for lo, hi, q_tile in ((0, first, 1), (first, ctx.num_tiles, ctx.q_tile)):
+            if hi <= lo:
+                continue
+            splits = 1 if q_tile > 1 and tensor_core else ops.choose_splits(
+                hi - lo, self.num_kv_heads, q_tile * group_size, ctx.max_context, tensor_core)
+            ops.paged_attention(
+                q, cache.k_cache, cache.v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq[lo:hi],
+                ctx.tile_q0[lo:hi], ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits,
+                num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, window=self.window or 0, scale=self.scale,
+                status=ctx.status, out=out)
         if residual is not None and self.b_o is None:
             summed = ops.linear_into_residual(out, self.w_o, residual, status=ctx.status)
             if summed is not None:
