@@ -41,6 +41,9 @@ PROMPT_LEN = 1024       # decode starts from 1,024-token prompts
 GEN_LEN = 256
 PREFILL_TOKENS = 2048
 PAGE_SIZE = 16
+SERVING_REQUESTS = 64               # the scheduler load: this many requests ...
+SERVING_PROMPT = (128, 4096)        # ... with prompts of uniformly drawn lengths in this range
+SERVING_OUTPUT = (128, 512)         # ... and this many generated tokens each
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -171,7 +174,9 @@ def main() -> int:
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     max_batch = 64 if not args.no_points else args.batch
-    pool_tokens = max(max_batch * (PROMPT_LEN + GEN_LEN + 64), args.batch * (CONTEXT + 64) if not args.no_points else 0,
+    pool_tokens = max(max_batch * (PROMPT_LEN + GEN_LEN + 64),
+                      max(args.batch * (CONTEXT + 64), SERVING_REQUESTS * (SERVING_PROMPT[1] + SERVING_OUTPUT[1]) // 2
+                          + SERVING_REQUESTS * 64) if not args.no_points else 0,
                       PREFILL_TOKENS + 64)
     engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", device=device, page_size=PAGE_SIZE,
                                 max_tokens=pool_tokens, max_seqs=max_batch + 2, max_batch_tokens=PREFILL_TOKENS)
@@ -280,6 +285,25 @@ def main() -> int:
         points[f"decode_b{args.batch}_ctx{CONTEXT}"] = round(args.batch / (p_ms / 1000), 2)
         points[f"decode_b{args.batch}_ctx{CONTEXT}_hbm_frac"] = round(
             decode_bytes(cfg, args.layers, args.batch, long_ctx) / (p_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)
+        # a scheduler load: many requests of mixed lengths, chunked prefill beside decoding, host tokens in and out
+        # (second pass timed: the decode graphs of its batch sizes exist by then); tokens per second of wall clock
+        import random
+        rng = random.Random(7)
+        lengths = [(rng.randint(*SERVING_PROMPT), rng.randint(*SERVING_OUTPUT)) for _ in range(SERVING_REQUESTS)]
+        for timed_pass in (False, True):
+            scheduler = engine.new_scheduler()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            requests = [scheduler.submit(f"s{i}", synthetic(n_in), n_out, ignore_eos=True)
+                        for i, (n_in, n_out) in enumerate(lengths)]
+            while scheduler.has_work():
+                scheduler.step()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t0
+            assert all(len(r.output_ids) == n_out for r, (_, n_out) in zip(requests, lengths))
+        points["serving_requests"] = SERVING_REQUESTS
+        points["serving_output_tok_s"] = round(sum(n for _, n in lengths) / wall, 1)
+        points["serving_total_tok_s"] = round(sum(a + b for a, b in lengths) / wall, 1)
 
     line = {
         "metric": "decode tok/s at batch 8 (Qwen3-8B shape, B200); prefill and batch 1/64 alongside",
