@@ -322,6 +322,39 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank
   return v;
 }
 
+// Merge of one output row across the key splits of a cluster (at most 8 CTAs): row layout in every CTA's shared
+// memory is (acc[D], max in log2 units, sum).  All loads of a step are issued before the first is used (one round
+// trip through distributed shared memory per step, not one per split); the sums run in split order.
+template <int D>
+__device__ __forceinline__ void merge_row_over_splits(uint32_t base, int splits, int tid, int nthreads,
+                                                      __nv_bfloat16* out) {
+  float mv[8], lv[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    mv[s] = s < splits ? ld_peer_smem(base + D * 4u, (uint32_t)s) : -CUDART_INF_F;
+    lv[s] = s < splits ? ld_peer_smem(base + (D + 1) * 4u, (uint32_t)s) : 0.f;
+  }
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int s = 0; s < 8; ++s)
+    if (lv[s] > 0.f) mx = fmaxf(mx, mv[s]);
+  float w[8], den = 0.f;
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    w[s] = lv[s] > 0.f ? exp2f(mv[s] - mx) : 0.f;
+    den += w[s] * lv[s];
+  }
+  for (int d = tid; d < D; d += nthreads) {
+    float v[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) v[s] = s < splits ? ld_peer_smem(base + d * 4u, (uint32_t)s) : 0.f;
+    float num = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) num += w[s] * v[s];
+    out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+  }
+}
+
 // Producer warps of one CTA.  Measured on B200: one is best; more producers only add warps that spin on the
 // barriers (decode at batch 64, 1,152 keys: 102 us with one producer, 184 us with four).
 constexpr int kProducers = 1;
@@ -522,22 +555,8 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
       cluster_sync_all();
       for (int row = split; row < G; row += p.num_splits) {
         const uint32_t base = smem_addr(merge) + (uint32_t)(row * kRow) * 4u;
-        float mx = -CUDART_INF_F;
-        for (int s = 0; s < p.num_splits; ++s)
-          if (ld_peer_smem(base + (D + 1) * 4u, s) > 0.f) mx = fmaxf(mx, ld_peer_smem(base + D * 4u, s));
-        __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D;
-        for (int d = tid; d < D; d += blockDim.x) {
-          float num = 0.f, den = 0.f;
-          for (int s = 0; s < p.num_splits; ++s) {
-            const float ls = ld_peer_smem(base + (D + 1) * 4u, s);
-            if (ls > 0.f) {
-              const float w = exp2f(ld_peer_smem(base + D * 4u, s) - mx);
-              num += w * ld_peer_smem(base + d * 4u, s);
-              den += w * ls;
-            }
-          }
-          out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
-        }
+        merge_row_over_splits<D>(base, p.num_splits, tid, blockDim.x,
+                                 (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D);
       }
       cluster_sync_all();                   // nobody leaves while a peer may still read its shared memory
       return;
@@ -850,22 +869,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
     cluster_sync_all();
     for (int row = split; row < G; row += p.num_splits) {
       const uint32_t base = smem_addr(merge) + (uint32_t)(row * kRow) * 4u;
-      float mx = -CUDART_INF_F;
-      for (int s = 0; s < p.num_splits; ++s)
-        if (ld_peer_smem(base + (D + 1) * 4u, s) > 0.f) mx = fmaxf(mx, ld_peer_smem(base + D * 4u, s));
-      __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D;
-      for (int d = tid; d < D; d += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < p.num_splits; ++s) {
-          const float ls = ld_peer_smem(base + (D + 1) * 4u, s);
-          if (ls > 0.f) {
-            const float w = exp2f(ld_peer_smem(base + D * 4u, s) - mx);
-            num += w * ld_peer_smem(base + d * 4u, s);
-            den += w * ls;
-          }
-        }
-        out[d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
-      }
+      merge_row_over_splits<D>(base, p.num_splits, tid, blockDim.x,
+                               (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D);
     }
     cluster_sync_all();
     return;

@@ -150,6 +150,18 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// The float at `local_addr` summed over the cluster's CTAs (one per K split, at most 8), in split order.  All loads
+// are issued before the first is used: one round trip through distributed shared memory, not one per split.
+__device__ __forceinline__ float sum_over_splits(uint32_t local_addr, int splits) {
+  float v[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) v[s] = s < splits ? ld_peer_smem(local_addr, (uint32_t)s) : 0.f;
+  float sum = v[0];
+#pragma unroll
+  for (int s = 1; s < 8; ++s) sum += v[s];      // absent splits add an exact zero
+  return sum;
+}
+
 template <int BN, typename OutT, int kStages, int kEpilogue, bool kNormedX>
 __global__ void __launch_bounds__(192)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
@@ -362,11 +374,8 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         if (feature < out_features) {
           for (int token = split + half * p.splits; token < p.tokens; token += 2 * p.splits) {
             const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + j) * 4u;
-            float g = 0.f, u = 0.f;
-            for (int s = 0; s < p.splits; ++s) {
-              g += ld_peer_smem(addr, (uint32_t)s);
-              u += ld_peer_smem(addr + (kTileM / 2) * 4u, (uint32_t)s);
-            }
+            float g = sum_over_splits(addr, p.splits);
+            float u = sum_over_splits(addr + (kTileM / 2) * 4u, p.splits);
             g = __bfloat162float(__float2bfloat16_rn(g));
             u = __bfloat162float(__float2bfloat16_rn(u));
             out[(int64_t)token * out_features + feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
@@ -388,8 +397,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         int it = 0;
         for (int token = split; token < p.tokens; token += p.splits, ++it) {
           const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-          float sum = 0.f;
-          for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+          const float sum = sum_over_splits(addr, p.splits);
           float v = __bfloat162float(__float2bfloat16_rn(sum));
           float* red_it = red + (it & 1) * 4;
           float* xch_it = xch + (it & 1) * kTileM;
@@ -433,8 +441,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         int it = 0;
         for (int token = split; token < p.tokens; token += p.splits, ++it) {
           const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-          float sum = 0.f;
-          for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+          const float sum = sum_over_splits(addr, p.splits);
           float h = 0.f;
           if (feature < p.features) {
             float* cell = p.residual.hidden + (int64_t)token * p.features + feature;
@@ -452,8 +459,7 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         if (feature < p.features) {
           for (int token = split; token < p.tokens; token += p.splits) {
             const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-            float sum = 0.f;
-            for (int s = 0; s < p.splits; ++s) sum += ld_peer_smem(addr, (uint32_t)s);
+            const float sum = sum_over_splits(addr, p.splits);
             out[(int64_t)token * p.features + feature] = from_float<OutT>(sum);
           }
         }
