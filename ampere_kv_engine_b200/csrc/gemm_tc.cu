@@ -283,11 +283,13 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // c ^ (r & 7)).  Warp q makes the K blocks kb = q, q + 4, ...: up to four blocks are under way at a time.
       const GemmNormedX& nx = p.normed;
       pdl_wait();      // hidden and its sums of squares come from the kernels before this one
-      const int t = quarter * 32 + lane;
-      if (t < p.tokens) {
+      // a warp per token, a lane per tile: the partial sums of a token arrive in one round trip (one thread adding
+      // a token's 32 tiles up in turn waited for each load)
+      for (int t = quarter; t < p.tokens; t += 4) {
         float ss = 0.f;
-        for (int i = 0; i < nx.ssq_tiles; ++i) ss += nx.ssq[(int64_t)i * p.tokens + t];
-        inv_rms[t] = rsqrtf(ss / (float)p.k + nx.eps);
+        for (int i = lane; i < nx.ssq_tiles; i += 32) ss += nx.ssq[(int64_t)i * p.tokens + t];
+        ss = warp_sum(ss);
+        if (lane == 0) inv_rms[t] = rsqrtf(ss / (float)p.k + nx.eps);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       // A stage must always be written by the same warp, so that the warp sees each of the stage's "empty" phases

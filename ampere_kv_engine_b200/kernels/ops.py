@@ -262,8 +262,8 @@ SMALL_M_LIMIT = 32
 use_small_m_gemm = True
 #: up to this many tokens a decode branch adds to the residual stream inside its last product and the next product
 #: applies the norm to its own token operand.  Every CTA of that product re-reads the float32 stream for its K
-#: range, which grows with the tokens: measured per decode step on B200, the pair saves 94 us at 4 tokens and 37 us
-#: at 8, and costs 30 us at 12, 160 us at 16 and 1.3 ms at 32.
+#: range, which grows with the tokens: measured per decode step on B200, the pair saves 94 us at 8 tokens and costs
+#: 50 us at 12, 210 us at 16 and 1.3 ms at 32.
 LAZY_NORM_LIMIT = 8
 #: hand split-K partial sums to the consuming kernel instead of adding them up inside the product kernel
 prefer_partials = False
