@@ -162,6 +162,23 @@ __device__ __forceinline__ float sum_over_splits(uint32_t local_addr, int splits
   return sum;
 }
 
+// The same for four places at once (addr[j] == kNoPlace: no such place): 32 loads under way, so that a CTA with many
+// tokens to reduce pays a round trip per four tokens.
+constexpr uint32_t kNoPlace = 0xffffffffu;
+__device__ __forceinline__ void sum4_over_splits(const uint32_t (&addr)[4], int splits, float (&sum)[4]) {
+  float v[4][8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int s = 0; s < 8; ++s) v[j][s] = (addr[j] != kNoPlace && s < splits) ? ld_peer_smem(addr[j], (uint32_t)s) : 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    sum[j] = v[j][0];
+#pragma unroll
+    for (int s = 1; s < 8; ++s) sum[j] += v[j][s];
+  }
+}
+
 template <int BN, typename OutT, int kStages, int kEpilogue, bool kNormedX>
 __global__ void __launch_bounds__(192)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
@@ -374,13 +391,25 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         const int out_features = p.features / 2;
         const int feature = tile * (kTileM / 2) + j;
         if (feature < out_features) {
-          for (int token = split + half * p.splits; token < p.tokens; token += 2 * p.splits) {
-            const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + j) * 4u;
-            float g = sum_over_splits(addr, p.splits);
-            float u = sum_over_splits(addr + (kTileM / 2) * 4u, p.splits);
-            g = __bfloat162float(__float2bfloat16_rn(g));
-            u = __bfloat162float(__float2bfloat16_rn(u));
-            out[(int64_t)token * out_features + feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
+          const int step = 2 * p.splits;
+          for (int token = split + half * p.splits; token < p.tokens; token += 2 * step) {     // two tokens at a time
+            uint32_t addr[4];
+            float sum[4];
+#pragma unroll
+            for (int t2 = 0; t2 < 2; ++t2) {
+              const int tok = token + t2 * step;
+              addr[2 * t2] = tok < p.tokens ? smem_u32(smem) + (uint32_t)(tok * kTileM + j) * 4u : kNoPlace;
+              addr[2 * t2 + 1] = tok < p.tokens ? addr[2 * t2] + (kTileM / 2) * 4u : kNoPlace;
+            }
+            sum4_over_splits(addr, p.splits, sum);
+#pragma unroll
+            for (int t2 = 0; t2 < 2; ++t2) {
+              const int tok = token + t2 * step;
+              if (tok >= p.tokens) break;
+              const float g = __bfloat162float(__float2bfloat16_rn(sum[2 * t2]));
+              const float u = __bfloat162float(__float2bfloat16_rn(sum[2 * t2 + 1]));
+              out[(int64_t)tok * out_features + feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
+            }
           }
         }
       } else if constexpr (kEpilogue == kEpilogueQkv) {
@@ -459,10 +488,20 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       } else {
         const int feature = tile * kTileM + row;
         if (feature < p.features) {
-          for (int token = split; token < p.tokens; token += p.splits) {
-            const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-            const float sum = sum_over_splits(addr, p.splits);
-            out[(int64_t)token * p.features + feature] = from_float<OutT>(sum);
+          for (int token = split; token < p.tokens; token += 4 * p.splits) {       // four tokens at a time
+            uint32_t addr[4];
+            float sum[4];
+#pragma unroll
+            for (int t4 = 0; t4 < 4; ++t4) {
+              const int tok = token + t4 * p.splits;
+              addr[t4] = tok < p.tokens ? smem_u32(smem) + (uint32_t)(tok * kTileM + row) * 4u : kNoPlace;
+            }
+            sum4_over_splits(addr, p.splits, sum);
+#pragma unroll
+            for (int t4 = 0; t4 < 4; ++t4) {
+              const int tok = token + t4 * p.splits;
+              if (tok < p.tokens) out[(int64_t)tok * p.features + feature] = from_float<OutT>(sum[t4]);
+            }
           }
         }
       }
