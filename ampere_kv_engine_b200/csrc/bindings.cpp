@@ -538,16 +538,31 @@ void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
   check_launch(akv::launch_paged_attention(p, stream_of(q)), "paged_attention");
 }
 
-void sample(const Tensor& logits, const Tensor& temperature, const Tensor& uniform, Tensor& tokens) {
+int64_t sample_slices() { return akv::kSampleSlices; }
+
+// parts: float32 workspace of 4 * rows * slices entries (maxima, indices and, as doubles, sums); tickets: int32, at
+// least `rows` entries, all zero (the kernel leaves them zero).
+void sample(const Tensor& logits, const Tensor& temperature, const Tensor& uniform, Tensor& tokens, Tensor& parts,
+            Tensor& tickets) {
   check_cuda(logits, "logits");
   AKV_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2, "logits must be float32 [rows, vocab]");
-  const int64_t rows = logits.size(0);
+  const int64_t rows = logits.size(0), cells = rows * akv::kSampleSlices;
   check_f32(temperature, "temperature", rows);
   check_f32(uniform, "uniform", rows);
   check_i32(tokens, "tokens", rows);
+  check_f32(parts, "parts");
+  check_i32(tickets, "tickets");
+  AKV_CHECK(parts.numel() >= 4 * cells && reinterpret_cast<uintptr_t>(parts.data_ptr()) % 8 == 0,
+            "parts must hold 4 * rows * slices float32 entries, 8-byte aligned");
+  AKV_CHECK(tickets.numel() >= rows, "tickets must hold a counter per row");
+  AKV_CHECK(parts.device() == logits.device() && tickets.device() == logits.device(),
+            "the workspaces must be on the logits' device");
+  float* base = parts.data_ptr<float>();
   c10::cuda::CUDAGuard guard(logits.device());
   check_launch(akv::launch_sample(logits.data_ptr<float>(), temperature.data_ptr<float>(), uniform.data_ptr<float>(),
-                                  tokens.data_ptr<int>(), rows, logits.size(1), stream_of(logits)),
+                                  tokens.data_ptr<int>(), rows, logits.size(1), base + 2 * cells,
+                                  reinterpret_cast<int*>(base + 3 * cells), reinterpret_cast<double*>(base),
+                                  tickets.data_ptr<int>(), stream_of(logits)),
                "sample");
 }
 
@@ -585,5 +600,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("window"), py::arg("scale"),
         py::arg("status") = py::none(), py::arg("kernel") = 0);
-  m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("uniform"), py::arg("tokens"));
+  m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("uniform"), py::arg("tokens"),
+        py::arg("parts"), py::arg("tickets"));
+  m.def("sample_slices", &sample_slices);
 }

@@ -150,7 +150,12 @@ int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream)
 
 // tokens[r] = argmax(logits[r]) where temperature[r] == 0, else the inverse-CDF draw of
 // softmax(logits[r] / temperature[r]) at uniform[r].
+// A row is cut into kSampleSlices slices, a block each.  Workspaces: part_max / part_arg / part_sum hold
+// num_rows * kSampleSlices entries (written before they are read); tickets holds num_rows counters that must be zero
+// when the kernel starts and are zero again when it ends.
+constexpr int kSampleSlices = 8;
 int launch_sample(const float* logits, const float* temperature, const float* uniform, int32_t* tokens,
-                  int64_t num_rows, int64_t vocab, cudaStream_t stream);
+                  int64_t num_rows, int64_t vocab, float* part_max, int* part_arg, double* part_sum, int* tickets,
+                  cudaStream_t stream);
 
 }  // namespace akv

@@ -205,9 +205,20 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
     return out
 
 
+_SAMPLE_TICKETS: dict = {}      # per device: zeroed row counters of the sampling kernel (it leaves them zero)
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
-    tokens = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    ext().sample(logits, temperature, uniform, tokens)
+    """int32 token per row: the arg-max where ``temperature`` is 0, else the inverse-CDF draw of
+    ``softmax(logits / temperature)`` at ``uniform``."""
+    rows = logits.shape[0]
+    tokens = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    tickets = _SAMPLE_TICKETS.get(logits.device)
+    if tickets is None or tickets.numel() < rows:
+        tickets = torch.zeros((max(rows, 512),), dtype=torch.int32, device=logits.device)
+        _SAMPLE_TICKETS[logits.device] = tickets
+    parts = torch.empty((4 * rows * ext().sample_slices(),), dtype=torch.float32, device=logits.device)
+    ext().sample(logits, temperature, uniform, tokens, parts, tickets)
     _launched()
     return tokens
 

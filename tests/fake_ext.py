@@ -116,7 +116,10 @@ class FakeExt:
             o = torch.einsum("hts,shd->thd", torch.softmax(scores, -1), v.repeat_interleave(group, dim=1))
             out[q0:q1] = o.reshape(n, -1).to(out.dtype)
 
-    def sample(self, logits, temperature, uniform, tokens):
+    def sample_slices(self):
+        return 8
+
+    def sample(self, logits, temperature, uniform, tokens, parts=None, tickets=None):
         for r in range(logits.shape[0]):
             t = float(temperature[r])
             if t <= 0:

@@ -595,17 +595,20 @@ def _cdf_interval_ok(logits, temperature, u, token):
     return lo - slack <= u * float(cdf[-1]) <= hi + slack
 
 
-@pytest.mark.parametrize("vocab", [1000, 151936])
+@pytest.mark.parametrize("vocab", [13, 1000, 1001, 151936])
 def test_sample_greedy_and_temperature(ops, vocab):
+    """A row is cut into slices, a block each: vocabularies smaller than the slices' granularity (empty slices), no
+    multiple of four (scalar reads) and the benchmark model's; a tie between the first and the last slice."""
     g = torch.Generator().manual_seed(vocab)
     rows = 9
     logits = 3 * torch.randn(rows, vocab, generator=g)
-    logits[0, 17] = logits[0, 900] = 50.0              # a tie: the lowest index wins
+    logits[0, min(17, vocab // 3)] = logits[0, vocab - 2] = 50.0     # a tie across slices: the lowest index wins
+    logits[1, vocab - 1] = 60.0                                      # the maximum in the last slice
     temps = torch.tensor([0.0, 0.0, 0.8, 0.8, 1.5, 0.1, 1.0, 0.8, 0.8])
     us = torch.tensor([0.0, 0.0, 0.0, 0.999999, 0.5, 0.3, 0.77, 0.123, 0.5])
     tokens = ops.sample(dev(logits), dev(temps), dev(us)).cpu().tolist()
-    assert tokens[0] == 17
-    assert tokens[1] == int(logits[1].argmax())
+    assert tokens[0] == min(17, vocab // 3)
+    assert tokens[1] == vocab - 1 == int(logits[1].argmax())
     for r in range(2, rows):
         assert _cdf_interval_ok(logits[r], float(temps[r]), float(us[r]), tokens[r]), (r, tokens[r])
         assert tokens[r] == plain.sample_temperature(logits[r], float(temps[r]), float(us[r])) or \
