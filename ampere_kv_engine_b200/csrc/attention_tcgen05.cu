@@ -135,7 +135,7 @@ struct FaSmemT {
   static constexpr int kQ = 2 * kRows * 128;
   static constexpr int kK = 2 * kKeys * 128;
   static constexpr int kStage = 2 * kK;
-  static constexpr int kBars = (1 + 3 * kStagesKV + 2 + 2 + 2) * 8;
+  static constexpr int kBars = (1 + 4 * kStagesKV + 2 + 2 + 2) * 8;
   static constexpr int kBytes = kQ + kStagesKV * kStage + kBars + 16 + 1024;
 };
 
@@ -185,7 +185,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   uint64_t* q_full = reinterpret_cast<uint64_t*>(kv_smem + kStagesKV * FaSmem::kStage);
   uint64_t* k_full = q_full + 1;                 // [stages]
   uint64_t* v_full = k_full + kStagesKV;         // [stages]
-  uint64_t* kv_empty = v_full + kStagesKV;       // [stages]
+  uint64_t* k_empty = v_full + kStagesKV;        // [stages] the scores of the stage's block are computed: K may go
+  uint64_t* kv_empty = k_empty + kStagesKV;      // [stages] P V of the stage's block is done: V may go
   uint64_t* s_ready = kv_empty + kStagesKV;      // [2] scores of a block are in TMEM buffer (block & 1)
   // P of a block is in shared memory buffer (block & 1): 128 arrivals.  One barrier per buffer, because a softmax
   // warp may run one block ahead of another (the scores are double-buffered), and its arrival for block j + 1 must
@@ -224,6 +225,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     for (int s = 0; s < kStagesKV; ++s) {
       bar_init(&k_full[s], 1);
       bar_init(&v_full[s], 1);
+      bar_init(&k_empty[s], 1);
       bar_init(&kv_empty[s], 1);
     }
     bar_init(&s_ready[0], 1);
@@ -273,32 +275,63 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       }
       return (page * p.num_kv_heads + kvh) * P + key % P;
     };
-    int y_next = row_of(0);
-    for (int b = 0; b < num_blocks && ok; ++b) {
-      const int s = b % kStagesKV;
-      const int y = y_next;
-      y_next = row_of(b + 1);
-      if (b >= kStagesKV) {
-        const bool freed = bar_wait(&kv_empty[s], ((b / kStagesKV) - 1) & 1);
-        if (!__all_sync(0xffffffffu, freed)) {      // the warp decides together: it votes below
-          ok = false;
-          break;
-        }
+    // K of a stage is free as soon as the scores of its block are computed, V only after P V: K runs one block
+    // ahead of V (the issuer computes the scores of block b + 1 before P V of block b), so each iteration fetches
+    // K of block b + 1 and V of block b.  With two stages that is what hides the copy's latency.
+    auto fetch = [&](int blk, int y, bool keys) -> bool {      // this lane's copies of K or V of block blk
+      const int s = blk % kStagesKV;
+      if (blk >= kStagesKV) {
+        const bool freed = bar_wait(keys ? &k_empty[s] : &kv_empty[s], ((blk / kStagesKV) - 1) & 1);
+        if (!__all_sync(0xffffffffu, freed)) return false;       // the warp decides together: it votes below
       }
-      uint8_t* k_dst = kv_smem + s * FaSmem::kStage;
-      uint8_t* v_dst = k_dst + FaSmem::kK;
-      const bool mine = y >= 0;
-      const uint32_t valid_boxes = __popc(__ballot_sync(0xffffffffu, mine && kind == 0));
-      if (lane == 0) {
-        const uint32_t bytes = valid_boxes * (uint32_t)fp.box_rows * 256u;
-        bar_expect_tx(&k_full[s], bytes);
-        bar_expect_tx(&v_full[s], bytes);
-      }
+      const bool mine = y >= 0 && (kind < 2) == keys;
+      const uint32_t valid_boxes = __popc(__ballot_sync(0xffffffffu, y >= 0 && kind == 0));
+      uint64_t* full = keys ? &k_full[s] : &v_full[s];
+      if (lane == 0) bar_expect_tx(full, valid_boxes * (uint32_t)fp.box_rows * 256u);
       __syncwarp();
       if (mine) {
+        uint8_t* dst = kv_smem + s * FaSmem::kStage + (keys ? 0 : FaSmem::kK);
         const uint32_t off = (uint32_t)(kind & 1) * (kKeys * 128) + (uint32_t)x * fp.box_rows * 128;
-        if (kind < 2) tma_2d(k_dst + off, &k_map, (kind & 1) * 64, y, &k_full[s]);
-        else tma_2d(v_dst + off, &v_map, (kind & 1) * 64, y, &v_full[s]);
+        tma_2d(dst + off, keys ? &k_map : &v_map, (kind & 1) * 64, y, full);
+      }
+      return true;
+    };
+    if constexpr (kStagesKV <= 2) {
+      int y_cur = row_of(0), y_next = row_of(1);
+      if (num_blocks > 0 && !fetch(0, y_cur, true)) ok = false;
+      for (int b = 0; b < num_blocks && ok; ++b) {
+        const int y_after = row_of(b + 2);                       // looked up two blocks early
+        if (b + 1 < num_blocks && !fetch(b + 1, y_next, true)) { ok = false; break; }
+        if (!fetch(b, y_cur, false)) { ok = false; break; }
+        y_cur = y_next;
+        y_next = y_after;
+      }
+    } else {
+      // a deep ring has the slack already: K and V of a block are fetched together once P V of the stage's last
+      // tenant is done (measured: the split order costs 15 % on a 512-token portion after 7,680 keys)
+      int y_next = row_of(0);
+      for (int b = 0; b < num_blocks && ok; ++b) {
+        const int s = b % kStagesKV;
+        const int y = y_next;
+        y_next = row_of(b + 1);
+        if (b >= kStagesKV) {
+          const bool freed = bar_wait(&kv_empty[s], ((b / kStagesKV) - 1) & 1);
+          if (!__all_sync(0xffffffffu, freed)) {
+            ok = false;
+            break;
+          }
+        }
+        const uint32_t valid_boxes = __popc(__ballot_sync(0xffffffffu, y >= 0 && kind == 0));
+        if (lane == 0) {
+          bar_expect_tx(&k_full[s], valid_boxes * (uint32_t)fp.box_rows * 256u);
+          bar_expect_tx(&v_full[s], valid_boxes * (uint32_t)fp.box_rows * 256u);
+        }
+        __syncwarp();
+        if (y >= 0) {
+          uint8_t* dst = kv_smem + s * FaSmem::kStage + (kind < 2 ? 0 : FaSmem::kK);
+          const uint32_t off = (uint32_t)(kind & 1) * (kKeys * 128) + (uint32_t)x * fp.box_rows * 128;
+          tma_2d(dst + off, kind < 2 ? &k_map : &v_map, (kind & 1) * 64, y, kind < 2 ? &k_full[s] : &v_full[s]);
+        }
       }
     }
   } else if (warp == 5) {
@@ -318,6 +351,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           umma(tmem + (b & 1) * 64, desc_k_major(q_addr + off), desc_k_major(k_addr + koff), id_s, t > 0 ? 1u : 0u);
         }
         umma_commit(&s_ready[b & 1]);
+        umma_commit(&k_empty[s]);
         return true;
       };
       if (!bar_wait(q_full, 0)) ok = false;
