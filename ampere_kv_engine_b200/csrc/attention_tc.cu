@@ -979,18 +979,19 @@ int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& 
 // Shape of the decode kernel's CTAs: (TMA ring stages of 16 KB at head size 128, consumer warps).  Bandwidth comes
 // from CTAs per SM, and a cluster's CTAs must all fit at once: rings of 4 or more stages (64 KB and up) made the
 // batch-8 kernel 25 us instead of 15 us.  Three stages pay since the producer fetches the blocks of old keys
-// before it waits for the previous kernel.  CTAs that walk many key blocks do best with two consumer warps (more
-// CTAs per SM by registers), short walks with four (the block is done sooner).  Measured per step with
-// (3,4) | (3,2): batch 8 at 1,064 keys 3.48 | 3.49 ms, batch 64 5.56 | 5.47 ms, batch 8 at 8,192 keys
-// 4.88 | 4.81 ms; (2,2) is 1-4 % behind everywhere.  AKV_ATTN_CONFIG=2|3|4|6 forces (2,2) | (3,4) | (2,4) | (3,2).
-int decode_config(int64_t blocks_per_cta) {
+// before it waits for the previous kernel.  Two consumer warps (more CTAs per SM by registers) do best wherever a
+// CTA walks more than a few key blocks; four (the block is done sooner) only for the shortest walks, a few
+// tokens cut into eight splits.  Measured per step with (3,4) | (3,2): batch 1 3.18 | 3.23 ms, batch 8 at 1,064
+// keys 3.48 | 3.49 ms, batch 16 3.96 | 3.89 ms, batch 32 4.70 | 4.65 ms, batch 64 5.56 | 5.47 ms, batch 8 at 8,192
+// keys 4.88 | 4.81 ms; (2,2) is 1-4 % behind everywhere.  AKV_ATTN_CONFIG=2|3|4|6 forces (2,2) | (3,4) | (2,4) | (3,2).
+int decode_config(int splits, int64_t blocks_per_cta) {
   static const int forced = [] {
     const char* v = getenv("AKV_ATTN_CONFIG");
     const int n = v ? atoi(v) : 0;
     return (n == 2 || n == 3 || n == 4 || n == 6) ? n : 0;
   }();
   if (forced) return forced;
-  return blocks_per_cta >= 16 ? 6 : 3;
+  return (splits >= 8 && blocks_per_cta < 16) ? 3 : 6;
 }
 
 }  // namespace
@@ -1035,7 +1036,7 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
                : launch_coop<64, ST, false, W>(p, box_rows, k_map, v_map, stream);
     // an upper bound of the 32-key blocks a CTA walks: the block table's width over the splits
     const int64_t bound_keys = p.window > 0 ? (int64_t)p.window : (int64_t)p.table_width * p.page_size;
-    switch (decode_config(bound_keys / (p.num_splits > 0 ? p.num_splits : 1) / 32)) {
+    switch (decode_config(p.num_splits, bound_keys / (p.num_splits > 0 ? p.num_splits : 1) / 32)) {
       case 2: AKV_COOP(2, 2)
       case 4: AKV_COOP(2, 4)
       case 6: AKV_COOP(3, 2)
