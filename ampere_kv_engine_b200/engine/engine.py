@@ -66,8 +66,8 @@ class Engine:
         self.admission = admission
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self._stream_counter = 0
-        # pinned landing places of the chosen tokens (+ the status word); two, since one step may be in flight
-        # while the one before it is read
+        # pinned landing places of the chosen tokens (+ the status word); three, since one step may be in flight
+        # while the one before it is read, and a third is filled only after both of those
         self._readback = [torch.zeros(max_seqs + 2, dtype=torch.int32) for _ in range(3)]
         if self.device.type == "cuda":
             self._readback = [t.pin_memory() for t in self._readback]

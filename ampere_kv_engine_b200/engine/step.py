@@ -166,8 +166,9 @@ class ModelRunner:
         dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         q_lens, ctx_lens = fill_host(self.manager, entries, layout, pinned.numpy(), 1)
         dev.copy_(pinned, non_blocking=False)
-        # the split count of the attention kernels is fixed at capture: size it for the widest table of the bucket
-        max_context = max(layout.widths) * self.manager.page_size
+        # the split count of the attention kernels is fixed at capture: size it for the middle of the contexts that
+        # this bucket of table widths serves (any count is right for any context; it only decides the speed)
+        max_context = max(1, (max(layout.widths) - _WIDTH_STEP // 2) * self.manager.page_size)
         ctx = make_context(layout, dev, tile_rows=1, max_context=max_context, status=self.status,
                            q_lens=q_lens, ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries],
                            h2d_bytes=int(layout.total * 4), sampled=self.sampled)

@@ -163,19 +163,21 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
     one warp per (token, kv head, 8 rows, split), sixteen to an SM.
     """
     if tensor_core:
-        # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  Cost model: rounds of CTAs over the
-        # GPU's 148 x 4 slots, each CTA walking its share of 32-key blocks plus a fixed start-up and merge worth
-        # about three blocks (measured on B200: batch 8 at 1,152 keys 15 us with 8 splits, 19 us with 4;
-        # batch 64: 60 us with 1 split, 67 us with 2).
+        # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  The GPU holds 148 x 4 CTAs at a time; a
+        # CTA spends about 0.9 us on a 32-key block and a fixed 5.5 us on start-up and merge, and a grid that
+        # needs a second round of CTAs takes about twice as long as one that just fits.  So: the most splits that
+        # still fit in one round.  Where that leaves a quarter of the slots empty, four times as many splits win
+        # once every CTA still walks 16 blocks or more.  Measured on B200 (us at 1/2/4/8 splits, 32 q-heads, 8
+        # kv-heads, head size 128): batch 8 at 1,088 keys 35/24/15/12; batch 24: 40/27/32/36; batch 32:
+        # 46/29/34/48; batch 64: 48/57/68/95; batch 48 at 4,096 keys 169/172/142/159; batch 24: 146/88/92/79.
         items, slots = max(1, num_tiles * num_kv_heads), 148 * 4
         blocks = (max_context + 31) // 32
-        best, best_cost = 1, None
-        for s in (1, 2, 4, 8):
-            if s > 1 and blocks // s < 2:
-                break
-            cost = -(-items * s // slots) * (-(-blocks // s) + 3)
-            if best_cost is None or cost < best_cost:
-                best, best_cost = s, cost
+        best = 1
+        for s in (2, 4, 8):
+            if items * s <= slots and blocks // s >= 2:
+                best = s
+        if items * best < 0.75 * slots and best * 4 <= 8 and blocks // (best * 4) >= 16:
+            best *= 4
         return best
     items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), 148 * 16, 128
     if items >= target or max_context <= min_keys:
