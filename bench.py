@@ -143,6 +143,7 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a power of two, 16 or more)")
     parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
                         help="run fewer layers of the same sizes (reported in config)")
     parser.add_argument("--batch", type=int, default=8)
@@ -178,7 +179,7 @@ def main() -> int:
                       max(args.batch * (CONTEXT + 64), SERVING_REQUESTS * (SERVING_PROMPT[1] + SERVING_OUTPUT[1]) // 2
                           + SERVING_REQUESTS * 64) if not args.no_points else 0,
                       PREFILL_TOKENS + 64)
-    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", device=device, page_size=PAGE_SIZE,
+    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", device=device, page_size=args.page_size,
                                 max_tokens=pool_tokens, max_seqs=max_batch + 2, max_batch_tokens=PREFILL_TOKENS)
     runner = engine.runner
     gen = torch.Generator().manual_seed(1234)
@@ -315,7 +316,7 @@ def main() -> int:
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "gen_len": GEN_LEN,
-            "mean_decode_context": round(mean_ctx, 1), "page_size": PAGE_SIZE, "kv_dtype": "bf16",
+            "mean_decode_context": round(mean_ctx, 1), "page_size": args.page_size, "kv_dtype": "bf16",
             "parallelism": "single GPU", "l2": "inputs larger than L2 (all weights stream every step)",
         },
         "e2e": e2e,
