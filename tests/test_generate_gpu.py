@@ -142,6 +142,36 @@ def test_requests_wait_for_pages_and_all_finish():
     assert engine.manager.free_pages() == [8]
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_preempted_requests_are_recomputed_to_the_same_tokens(name):
+    """Optimistic admission with too few pages for everybody's outputs: the newest request gives its pages back,
+    waits and is recomputed over its prompt and the tokens it already has; rounds are queued ahead meanwhile.
+    Everybody ends with the tokens they get alone, no page is lost, and the window's released pages (B) take part."""
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = tiny.CONFIGS[name]
+    lengths = (30, 22, 41, 12)
+    new_tokens = 40
+    need = [(n + new_tokens + page - 1) // page for n in lengths]
+    pool = max(need) + sum(need) // 3
+    engine = Engine.from_pretrained(model_folder(name), dtype="float32", page_size=page, num_pages=pool,
+                                    max_batch_tokens=32)
+    prompts = prompts_for(name, lengths, seed=3)
+    alone = [engine.generate([p], max_new_tokens=new_tokens, ignore_eos=True)[0] for p in prompts]
+    for ahead in (False, True):
+        scheduler = engine.new_scheduler(admission="optimistic", lookahead=ahead)
+        requests = [scheduler.submit(i, p, new_tokens, ignore_eos=True) for i, p in enumerate(prompts)]
+        rounds = 0
+        while scheduler.has_work():
+            scheduler.step()
+            rounds += 1
+            assert rounds < 2000
+        assert [r.output_ids for r in requests] == alone
+        assert all(r.stop_reason == "length" for r in requests)
+        assert scheduler.preemptions >= 1
+        engine.manager.check_invariants()
+        assert engine.manager.free_pages() == [pool] * len(engine.manager.groups)
+
+
 def test_command_line_generate(tmp_path):
     folder = model_folder("A")
     prompt = prompts_for("A", (12,))[0]
