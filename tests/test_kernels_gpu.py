@@ -432,11 +432,14 @@ def test_tensor_core_and_general_kernels_agree(ops, nh, nkv, d, page, window):
     torch.testing.assert_close(decode.run(ops, window, 3, kernel="general"), want, **tol(dtype))
 
 
-@pytest.mark.parametrize("nh,nkv,page,q_tile", [(32, 8, 16, 32), (16, 8, 32, 64), (8, 1, 64, 16), (32, 8, 16, 16)])
-@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("nh,nkv,page,q_tile", [(32, 8, 16, 32), (16, 8, 32, 64), (8, 1, 64, 16), (32, 8, 16, 16),
+                                                 (32, 8, 16, 64), (8, 2, 16, 96), (16, 2, 32, 64), (8, 4, 64, 128)])
+@pytest.mark.parametrize("window", [0, 100, 37])
 def test_tcgen05_prompt_attention(ops, nh, nkv, page, q_tile, window):
     """Prompt portions at head size 128 with groups of 2, 4 and 8 q-heads run on the tcgen05 kernel: whole
-    prompts, portions after a long history, tiles that end mid-way, a portion of one token beside them."""
+    prompts, portions after a long history, tiles that end mid-way, a portion of one token beside them.  Batch
+    tiles of one, two, three or four of the kernel's 128-row query tiles (the last one whole, partial or empty),
+    windows longer and shorter than a tile's span."""
     dtype = torch.bfloat16
     case = PagedCase(dtype, nh, nkv, 128, page, q_lens=[300, 77, 33, 1, 128], ctx_lens=[300, 500, 33, 40, 128],
                      seed=page + nh, q_tile=q_tile)
@@ -445,12 +448,13 @@ def test_tcgen05_prompt_attention(ops, nh, nkv, page, q_tile, window):
     torch.testing.assert_close(case.run(ops, window, 1, kernel="mma"), want, **tol(dtype))
 
 
-def test_tcgen05_prompt_attention_repeats_and_rescales(ops):
+@pytest.mark.parametrize("q_tile", [32, 64])
+def test_tcgen05_prompt_attention_repeats_and_rescales(ops, q_tile):
     """The tcgen05 kernel keeps a stale running maximum and rescales its accumulator only when a score exceeds it
     by 2^8: keys of growing norm force that path in every block, a dominant key early and late in a long history
     tests both sides of it, and repeated launches must agree bit for bit (its warps run at different speeds)."""
     dtype = torch.bfloat16
-    case = PagedCase(dtype, 8, 2, 128, 16, q_lens=[96, 200, 40], ctx_lens=[900, 200, 1500], seed=77, q_tile=32)
+    case = PagedCase(dtype, 8, 2, 128, 16, q_lens=[96, 200, 40], ctx_lens=[900, 200, 1500], seed=77, q_tile=q_tile)
     # sequence 0: key norms grow along the sequence, so that later blocks keep raising the maximum
     ramp = torch.linspace(0.2, 6.0, 900).view(900, 1, 1)
     case.k_seq[0] = (case.k_seq[0].float() * ramp).to(dtype)
@@ -490,13 +494,14 @@ def _last_rows_reference(case, window=0):
     return torch.cat(outs)
 
 
+@pytest.mark.parametrize("q_tile", [32, 64])
 @pytest.mark.parametrize("window", [0, 3000])
-def test_attention_over_thousands_of_keys(ops, window):
+def test_attention_over_thousands_of_keys(ops, window, q_tile):
     """Contexts of several thousand keys, where the K/V rings of the tensor-core kernels wrap hundreds of times:
     prompt portions after a long history (tcgen05 and mma.sync kernels), and decoded tokens with every way of
     splitting the keys.  One far key is made to matter in the longest sequence."""
     dtype = torch.bfloat16
-    case = PagedCase(dtype, 8, 2, 128, 16, q_lens=[200, 37, 64], ctx_lens=[6000, 4100, 2500], seed=41, q_tile=32)
+    case = PagedCase(dtype, 8, 2, 128, 16, q_lens=[200, 37, 64], ctx_lens=[6000, 4100, 2500], seed=41, q_tile=q_tile)
     far = 77
     for kv in range(2):
         direction = torch.nn.functional.normalize(case.k_seq[0][far, kv].float(), dim=0)
