@@ -196,13 +196,22 @@ paged_attention_kernel(PagedAttentionParams p, int row_groups, int64_t total_ite
   }
 }
 
-// out[row] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits taken in order.
+// out[row] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits taken in order.  One block per (tile, row
+// of the tile, q-head): only the rows of the call's tiles are merged and written.  (A batch may be covered by two
+// calls with different tiles and split counts; the other call's rows have no partial sums in this call's
+// workspace and their results must stay.)
 template <typename T>
-__global__ void merge_splits_kernel(const float* __restrict__ partials, T* __restrict__ out, int num_splits,
-                                    int head_dim) {
+__global__ void merge_splits_kernel(const float* __restrict__ partials, T* __restrict__ out,
+                                    const int32_t* __restrict__ tile_q0, const int32_t* __restrict__ tile_nq,
+                                    int q_tile, int num_heads, int num_splits, int head_dim) {
   pdl_launch_dependents();
   pdl_wait();
-  const int64_t row = blockIdx.x;
+  const int64_t per_tile = (int64_t)q_tile * num_heads;
+  const int64_t tile = blockIdx.x / per_tile;
+  const int in_tile = (int)(blockIdx.x - tile * per_tile);
+  const int r = in_tile / num_heads, head = in_tile - r * num_heads;
+  if (r >= tile_nq[tile]) return;
+  const int64_t row = ((int64_t)tile_q0[tile] + r) * num_heads + head;
   const float* base = partials + row * num_splits * (int64_t)(head_dim + 2);
   float m = -CUDART_INF_F;
   for (int s = 0; s < num_splits; ++s) {
@@ -226,10 +235,12 @@ __global__ void merge_splits_kernel(const float* __restrict__ partials, T* __res
 
 template <typename T>
 static int launch_merge(const PagedAttentionParams& p, cudaStream_t stream) {
-  const int64_t rows = p.num_tokens * p.num_heads;
-  if (rows > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const int64_t blocks = (int64_t)p.num_tiles * p.q_tile * p.num_heads;
+  if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  if (blocks == 0) return 0;
   const int threads = p.head_dim <= 32 ? 32 : (p.head_dim <= 64 ? 64 : 128);
-  merge_splits_kernel<T><<<(unsigned)rows, threads, 0, stream>>>(p.partials, (T*)p.out, p.num_splits, p.head_dim);
+  merge_splits_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>(p.partials, (T*)p.out, p.tile_q0, p.tile_nq, p.q_tile,
+                                                                    p.num_heads, p.num_splits, p.head_dim);
   return (int)cudaGetLastError();
 }
 

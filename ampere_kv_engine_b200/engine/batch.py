@@ -61,6 +61,9 @@ class StepContext:
     #: the prompt tiles
     num_decode_tiles: int
     max_context: int                # longest ctx_lens entry (host value)
+    #: (longest, mean) context of the sequences that bring one token: what the choice of key splits for their
+    #: attention assumes (a captured decode step: estimates for the steps it will serve)
+    decode_contexts: tuple[int, int]
     groups: list[GroupBatch]
     status: torch.Tensor | None     # int32[1] the kernels report bad indices in
     sampled: torch.Tensor | None = None   # int32 tokens the previous step chose (for entries with a ``source``)
@@ -165,7 +168,8 @@ def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout
 
 def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_context: int,
                  status: torch.Tensor | None, q_lens: list[int], ctx_lens: list[int], state_slots: list[int],
-                 h2d_bytes: int, sampled: torch.Tensor | None = None) -> StepContext:
+                 h2d_bytes: int, sampled: torch.Tensor | None = None,
+                 decode_contexts: tuple[int, int] | None = None) -> StepContext:
     """Views into the device copy ``dev`` of a filled index buffer."""
     off = layout.offsets
 
@@ -174,6 +178,9 @@ def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_
 
     decoding = sum(1 for n in q_lens if n == 1)
     num_decode_tiles = decoding if 0 < decoding < len(q_lens) else 0
+    if decode_contexts is None:
+        single = [c for n, c in zip(q_lens, ctx_lens) if n == 1] or [max_context]
+        decode_contexts = (max(single), sum(single) // len(single))
     groups = []
     for gi, width in enumerate(layout.widths):
         groups.append(GroupBatch(view(9 + 2 * gi, layout.num_tokens),
@@ -184,7 +191,7 @@ def make_context(layout: BatchLayout, dev: torch.Tensor, *, tile_rows: int, max_
         state_slots=view(4, layout.num_seqs), logit_rows=view(5, layout.num_logit_rows),
         num_logit_rows=layout.num_logit_rows, tile_seq=view(6, layout.num_tiles), tile_q0=view(7, layout.num_tiles),
         tile_nq=view(8, layout.num_tiles), num_tiles=layout.num_tiles, q_tile=tile_rows,
-        num_decode_tiles=num_decode_tiles, max_context=max_context,
+        num_decode_tiles=num_decode_tiles, max_context=max_context, decode_contexts=decode_contexts,
         groups=groups, status=status, sampled=sampled, q_lens_host=q_lens, ctx_lens_host=ctx_lens,
         state_slots_host=state_slots, h2d_bytes=h2d_bytes)
 

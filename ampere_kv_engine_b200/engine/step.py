@@ -169,9 +169,13 @@ class ModelRunner:
         # the split count of the attention kernels is fixed at capture: size it for the middle of the contexts that
         # this bucket of table widths serves (any count is right for any context; it only decides the speed)
         max_context = max(1, (max(layout.widths) - _WIDTH_STEP // 2) * self.manager.page_size)
+        # and for the mix of lengths this batch has (the next batches of the bucket are mostly this one, grown)
+        live = [c for c in ctx_lens if c > 0] or [max_context]
+        mean_context = max(1, max_context * sum(live) // (len(live) * max(live)))
         ctx = make_context(layout, dev, tile_rows=1, max_context=max_context, status=self.status,
                            q_lens=q_lens, ctx_lens=ctx_lens, state_slots=[e.seq.state_slot for e in entries],
-                           h2d_bytes=int(layout.total * 4), sampled=self.sampled)
+                           h2d_bytes=int(layout.total * 4), sampled=self.sampled,
+                           decode_contexts=(max_context, mean_context))
         # one eager run first (library handles and workspaces come into being outside the capture); it writes the
         # same cache slots the captured run writes again
         self.model.forward(ctx, self.views)

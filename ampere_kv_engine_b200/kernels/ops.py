@@ -9,6 +9,8 @@ fallback: without the extension these functions raise.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from . import build
@@ -156,28 +158,42 @@ def attention_takes_tensor_cores(dtype: torch.dtype, head_dim: int, group_size: 
 
 
 def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
-                  tensor_core: bool = False) -> int:
-    """How many key ranges each decoded token's attention is cut into so that a small batch still fills the GPU.
+                  tensor_core: bool = False, mean_context: int | None = None) -> int:
+    """How many key ranges each decoded token's attention is cut into so that a small batch still fills the GPU
+    and a long sequence among short ones does not keep one CTA walking alone.  ``max_context`` / ``mean_context``:
+    the keys the longest and the average token of the batch walks (the mean defaults to the maximum).
 
     The tensor-core decode kernel runs one CTA per (token, kv head, split), four to an SM; the general kernel
     one warp per (token, kv head, 8 rows, split), sixteen to an SM.
     """
     if tensor_core:
-        # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  The GPU holds 148 x 4 CTAs at a time; a
-        # CTA spends about 0.9 us on a 32-key block and a fixed 5.5 us on start-up and merge, and a grid that
-        # needs a second round of CTAs takes about twice as long as one that just fits.  So: the most splits that
-        # still fit in one round.  Where that leaves a quarter of the slots empty, four times as many splits win
-        # once every CTA still walks 16 blocks or more.  Measured on B200 (us at 1/2/4/8 splits, 32 q-heads, 8
-        # kv-heads, head size 128): batch 8 at 1,088 keys 35/24/15/12; batch 24: 40/27/32/36; batch 32:
-        # 46/29/34/48; batch 64: 48/57/68/95; batch 48 at 4,096 keys 169/172/142/159; batch 24: 146/88/92/79.
+        # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  A cost in microseconds, fitted to
+        # measurements on B200 (32 q-heads, 8 kv-heads, head size 128, batches of 4 to 64, 1,088 to 8,000 keys,
+        # equal and mixed lengths): a CTA spends about 1.1 us on a 32-key block and a fixed 5.5 us (7.5 us in a
+        # cluster) on start-up and merge; the GPU holds 148 x 4 CTAs at a time.  With equal lengths all CTAs end
+        # together, so a grid that needs a further round of CTAs pays for a whole one; with mixed lengths slots
+        # free up all the time and only the fraction counts.  The step ends when the CTA of the longest range that
+        # started in the last round ends, and never before the bytes have crossed the memory system.
+        # Measured (us at 1/2/4/8 splits): batch 8 at 1,088 keys 35/24/15/12; batch 24: 40/27/32/36; batch 64:
+        # 48/57/68/95; batch 48 at 4,096 keys 169/172/142/159; batch 64 with 300 to 4,600 keys (mean 2,500):
+        # 178/153/142/155; batch 12 likewise: 149/82/48/37.
         items, slots = max(1, num_tiles * num_kv_heads), 148 * 4
-        blocks = (max_context + 31) // 32
-        best = 1
-        for s in (2, 4, 8):
-            if items * s <= slots and blocks // s >= 2:
-                best = s
-        if items * best < 0.75 * slots and best * 4 <= 8 and blocks // (best * 4) >= 16:
-            best *= 4
+        blocks_max = max(1, (max_context + 31) // 32)
+        blocks_mean = blocks_max if mean_context is None else max(1, min(blocks_max, (int(mean_context) + 31) // 32))
+        evenness = (blocks_mean / blocks_max) ** 2
+        moved = items * blocks_mean * 16384 / 6.0e6       # us for the K/V bytes (heads of 128 dims) at 6 TB/s
+        best, best_cost = 1, None
+        for i, s in enumerate((1, 2, 4, 8)):
+            if s > 1 and blocks_max // s < 2:
+                break
+            fixed = 5.5 if s == 1 else 7.5
+            walk_max = -(-blocks_max // s) * 1.1 + fixed
+            walk_mean = -(-blocks_mean // s) * 1.1 + fixed
+            rounds = items * s / slots
+            rounds += (math.ceil(rounds) - rounds) * evenness
+            cost = max(max(0.0, rounds - 1.0) * walk_mean + walk_max, moved) * (1.0 + 0.03 * i)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
         return best
     items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), 148 * 16, 128
     if items >= target or max_context <= min_keys:

@@ -111,12 +111,15 @@ class PagedAttention(Mixer):
         # decoded tokens beside prompt portions: the single-token tiles (they come first) run apart, with their keys
         # split over several CTAs; as one-row tiles of the prompt kernel each would walk its whole context alone
         first = getattr(ctx, "num_decode_tiles", 0)
-        keys = min(ctx.max_context, self.window) if self.window else ctx.max_context    # a token walks this many at most
         for lo, hi, q_tile in ((0, first, 1), (first, ctx.num_tiles, ctx.q_tile)):
             if hi <= lo:
                 continue
+            # the keys that the longest and the average tile walks: the context, or the window if that is shorter
+            longest, mean = ctx.decode_contexts if q_tile == 1 else (ctx.max_context, ctx.max_context)
+            if self.window:
+                longest, mean = min(longest, self.window), min(mean, self.window)
             splits = 1 if q_tile > 1 and tensor_core else ops.choose_splits(
-                hi - lo, self.num_kv_heads, q_tile * group_size, keys, tensor_core)
+                hi - lo, self.num_kv_heads, q_tile * group_size, longest, tensor_core, mean_context=mean)
             ops.paged_attention(
                 q, cache.k_cache, cache.v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq[lo:hi],
                 ctx.tile_q0[lo:hi], ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits,

@@ -413,6 +413,33 @@ def test_paged_attention_mixed_batch(ops, dtype, nh, nkv, d, page, window):
         torch.testing.assert_close(case.run(ops, window, splits), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kernel", ["auto", "general"])
+def test_a_batch_covered_by_two_calls_with_different_splits(ops, dtype, kernel):
+    """A step that holds decoded tokens beside prompt portions runs attention twice, over different tiles and with
+    different numbers of key splits, into one output.  A call writes the rows of its own tiles only: the other
+    call's rows have no partial sums in its workspace (here the workspaces are filled with NaN beforehand)."""
+    case = PagedCase(dtype, 8, 2, 64, 16, q_lens=[1, 40, 1, 23, 1], ctx_lens=[300, 90, 77, 400, 1], seed=5)
+    want = case.reference(0)
+    q = dev(torch.cat([x.reshape(x.shape[0], -1) for x in case.q_seq]))
+    ctx_lens = dev(torch.tensor(case.ctx_lens, dtype=torch.int32))
+    cu = case.cu.tolist()
+    single = [(s, cu[s], 1) for s, n in enumerate(case.q_lens) if n == 1]
+    portions = [(s, cu[s] + q0, min(16, n - q0)) for s, n in enumerate(case.q_lens) if n > 1 for q0 in range(0, n, 16)]
+    for first_splits, second_splits in ((3, 2), (2, 5), (1, 4), (4, 1)):
+        out = torch.full_like(q, float("nan"))
+        status = status_word()
+        for tiles, q_tile, splits in ((single, 1, first_splits), (portions, 16, second_splits)):
+            cols = [dev(torch.tensor([t[i] for t in tiles], dtype=torch.int32)) for i in range(3)]
+            partials = torch.full((q.shape[0] * 8 * splits * (64 + 2),), float("nan"), device=q.device)
+            ops.paged_attention(q, dev(case.k_cache), dev(case.v_cache), dev(case.table), dev(case.cu), ctx_lens,
+                                cols[0], cols[1], cols[2], num_tiles=len(tiles), q_tile=q_tile, num_splits=splits,
+                                num_heads=8, num_kv_heads=2, window=0, scale=64 ** -0.5, partials=partials,
+                                status=status, kernel=kernel, out=out)
+        assert int(status.item()) == 0
+        torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
 @pytest.mark.parametrize("nh,nkv,d,page", [(32, 8, 128, 16), (8, 8, 64, 32), (16, 1, 128, 64), (6, 2, 128, 8)])
 @pytest.mark.parametrize("window", [0, 50])
 def test_tensor_core_and_general_kernels_agree(ops, nh, nkv, d, page, window):
