@@ -634,7 +634,10 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool is_producer = warp == kCoopWarps;
   const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
-  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  // CTAs start in the order of blockIdx.x, then .y: taken tile-major, all kv heads of the first tile start before
+  // any of the second, so that the host's order of the tiles (longest context first) is the order of the work
+  const int linear = blockIdx.y * gridDim.x + blockIdx.x;
+  const int tile = linear / gridDim.y, kvh = linear - tile * gridDim.y, split = blockIdx.z;
 
   pdl_launch_dependents();
   const int seq = p.tile_seq[tile];

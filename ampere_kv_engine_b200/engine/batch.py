@@ -138,7 +138,9 @@ def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout
     host[off[5]:off[5] + max(1, layout.num_logit_rows)] = 0
     put(5, [int(cu[s]) + w for s, e in enumerate(entries) for w in e.want])
     tiles = [(s, int(cu[s]) + q0, min(tile_rows, n - q0)) for s, n in enumerate(q_lens) for q0 in range(0, n, tile_rows)]
-    tiles.sort(key=lambda t: q_lens[t[0]] != 1)       # single-token sequences first, each kind in batch order
+    # single-token sequences first, the longest context first among them (their CTAs start in this order, and the
+    # step's attention ends with the last long one); prompt tiles after them in batch order
+    tiles.sort(key=lambda t: (0, -ctx_lens[t[0]]) if q_lens[t[0]] == 1 else (1, 0))
     if len(tiles) > layout.num_tiles:
         raise ValueError("the layout has too few attention tiles for this step")
     host[off[6]:off[6] + layout.num_tiles] = 0

@@ -172,11 +172,12 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
         # equal and mixed lengths): a CTA spends about 1.1 us on a 32-key block and a fixed 5.5 us (7.5 us in a
         # cluster) on start-up and merge; the GPU holds 148 x 4 CTAs at a time.  With equal lengths all CTAs end
         # together, so a grid that needs a further round of CTAs pays for a whole one; with mixed lengths slots
-        # free up all the time and only the fraction counts.  The step ends when the CTA of the longest range that
-        # started in the last round ends, and never before the bytes have crossed the memory system.
+        # free up all the time and only the fraction counts.  The longest sequences' CTAs start first (the batch
+        # layout orders the tiles so), so the step takes the longest walk or the rounds of mean walks, whichever
+        # is more, and never less than the bytes need to cross the memory system.
         # Measured (us at 1/2/4/8 splits): batch 8 at 1,088 keys 35/24/15/12; batch 24: 40/27/32/36; batch 64:
         # 48/57/68/95; batch 48 at 4,096 keys 169/172/142/159; batch 64 with 300 to 4,600 keys (mean 2,500):
-        # 178/153/142/155; batch 12 likewise: 149/82/48/37.
+        # 171/110/119/144; batch 40 likewise: 160/94/75/88; batch 20: 144/81/48/46.
         items, slots = max(1, num_tiles * num_kv_heads), 148 * 4
         blocks_max = max(1, (max_context + 31) // 32)
         blocks_mean = blocks_max if mean_context is None else max(1, min(blocks_max, (int(mean_context) + 31) // 32))
@@ -191,7 +192,7 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
             walk_mean = -(-blocks_mean // s) * 1.1 + fixed
             rounds = items * s / slots
             rounds += (math.ceil(rounds) - rounds) * evenness
-            cost = max(max(0.0, rounds - 1.0) * walk_mean + walk_max, moved) * (1.0 + 0.03 * i)
+            cost = max(walk_max, rounds * walk_mean, moved) * (1.0 + 0.03 * i)
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
