@@ -309,3 +309,63 @@ def test_lookahead_cancel_and_empty_rounds():
     assert [r.request_id for r in done] == ["a"] and a.stop_reason == "cancelled"
     assert not s.has_work() and ex.manager.free_pages() == [64] and ex.launched == ex.collected
     assert a.output_ids == expected_output(prompt(8), len(a.output_ids))
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_arrivals_cancels_and_pools_end_right(seed):
+    """Random prompts, limits, arrival rounds, cancellations, deadlines and end-of-sequence tokens, under both
+    admission rules, round by round and queued ahead, with full and windowed cache groups and pools from roomy to
+    barely enough: every request ends exactly once, with the tokens it would get alone (cut at its end-of-sequence
+    token, or a prefix of them if it was cancelled or timed out), and every page and slot comes back."""
+    import random
+    rng = random.Random(seed)
+    specs = [CacheSpec("full", 2, 16)] + ([CacheSpec("window", 2, 16, window=rng.choice((8, 24)))] if seed % 3 == 0 else [])
+    page = rng.choice((4, 16))
+    count = rng.randint(3, 9)
+    prompts = [prompt(rng.randint(1, 70), salt=rng.randint(0, 50)) for _ in range(count)]
+    limits = [rng.randint(1, 30) for _ in range(count)]
+    arrive = sorted(rng.randint(0, 25) for _ in range(count))
+    biggest = max((len(p) + n + page) // page + 1 for p, n in zip(prompts, limits))
+    pages = biggest + rng.choice((0, 2, biggest, 4 * biggest))
+    admission = rng.choice(("budget", "optimistic"))
+    ahead = bool(seed % 2)
+    eos = rng.randrange(VOCAB) if rng.random() < 0.5 else None
+    ex = AheadExecutor(pages=pages, page=page, seqs=rng.choice((2, 4, 8)), specs=specs)
+    s = Scheduler(ex, max_batch_tokens=rng.choice((8, 24, 64)), admission=admission, lookahead=ahead,
+                  eos_token_ids=(eos,) if eos is not None else ())
+    cancel_at = {i: arrive[i] + rng.randint(0, 20) for i in range(count) if rng.random() < 0.25}
+    deadline = {i: float(arrive[i] + rng.randint(1, 30)) for i in range(count) if rng.random() < 0.15}
+    requests, ended = {}, []
+    for round_no in range(3000):
+        for i in range(count):
+            if arrive[i] == round_no and i not in requests:
+                requests[i] = s.submit(i, prompts[i], limits[i], deadline=deadline.get(i))
+            if cancel_at.get(i) == round_no and i in requests:
+                s.cancel(requests[i])
+        if len(requests) == count and not s.has_work():
+            break
+        done, stats = s.step(now=float(round_no))
+        ended += done
+        assert stats.batch_tokens <= s.max_batch_tokens
+    else:
+        raise AssertionError("the scheduler did not finish")
+    assert sorted(r.request_id for r in ended) == list(range(count)), "every request ends exactly once"
+    for i, r in requests.items():
+        full = expected_output(prompts[i], limits[i])
+        if eos is not None and eos in full:
+            full = full[:full.index(eos) + 1]
+        assert r.status == FINISHED and r.stop_reason
+        if r.stop_reason in ("length", "eos"):
+            assert r.output_ids == full, (i, r.stop_reason)
+            if r.stop_reason == "eos":
+                assert full[-1] == eos
+            else:
+                assert len(full) == limits[i]
+        else:
+            assert r.stop_reason in ("cancelled", "deadline", "out of pages"), r.stop_reason
+            assert r.output_ids == full[:len(r.output_ids)]
+            if r.stop_reason == "out of pages":
+                assert admission == "optimistic"
+    ex.manager.check_invariants()
+    assert ex.manager.free_pages() == [pages] * len(specs) and s.reserved == [0] * len(specs)
+    assert ex.launched == ex.collected
