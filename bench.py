@@ -130,11 +130,146 @@ def decode_bytes(cfg, layers, batch, mean_ctx) -> float:
     return weights + batch * mean_ctx * n["kv_bytes_per_token"]
 
 
-def prefill_flops(cfg, layers, tokens) -> float:
+def prefill_flops(cfg, layers, tokens) -> dict:
     n = model_numbers(cfg, layers)
     gemm = 2.0 * tokens * layers * n["layer_params"] + 2.0 * n["head_params"]
     attn = 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * layers * tokens * (tokens + 1) / 2
-    return gemm + attn
+    return {"gemm": gemm, "attention": attn}
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference project (installed under baseline/_ref) on its stock default path.
+
+    Its loader needs the published checkpoint and its extension holds sm_86 code only, but its default generation
+    path needs neither: ``ampere_kv.runner.generate_tokens(model, input_ids, cache_kind="contiguous")``
+    (ampere_kv/runner.py:301-406; ``--cache contiguous`` is the command line's default, runner.py:667) takes the
+    model as an argument and reads weights off it by attribute.  A tree of ``types.SimpleNamespace`` with exactly
+    those attributes, holding seeded random bfloat16 tensors of the Qwen3-8B sizes, stands in for the checkpoint.
+    The reference without its extension decodes one request at a time, so a "step" of the batch is one token for
+    each of the batch's requests in turn.  Nothing of this repository's package is imported here.
+    """
+    import traceback
+    import types
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = args.layers
+    steps, warmup, batch = args.steps, max(3, args.warmup), args.batch
+    try:
+        if not os.path.isdir(os.path.join(ref_root, "ampere_kv")):
+            raise RuntimeError("baseline/_ref/ampere_kv is missing (the offline install did not travel)")
+        sys.path.insert(0, ref_root)
+        sys.dont_write_bytecode = True
+        os.environ.setdefault("HF_HUB_OFFLINE", "1")
+        import torch
+        from ampere_kv import runner as ref           # imports the checkpoint library at module level
+        device = torch.device("cuda:0")
+        torch.cuda.set_device(device)
+        gen = torch.Generator(device=device).manual_seed(0)
+        h, nh, nkv, d, inter, vocab = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                                       cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+        ns = types.SimpleNamespace
+
+        def matrix(rows, cols):
+            return (torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02).bfloat16()
+
+        def lin(rows, cols):
+            return ns(weight=matrix(rows, cols), bias=None)
+
+        def norm(size):
+            w = 1.0 + 0.1 * torch.randn((size,), generator=gen, device=device, dtype=torch.float32)
+            return ns(weight=w.bfloat16(), variance_epsilon=cfg["rms_norm_eps"])
+
+        layers = []
+        for _ in range(args.layers):
+            attn = ns(q_proj=lin(nh * d, h), k_proj=lin(nkv * d, h), v_proj=lin(nkv * d, h), o_proj=lin(h, nh * d),
+                      q_norm=norm(d), k_norm=norm(d), head_dim=d, sliding_window=None)
+            mlp = ns(gate_proj=lin(inter, h), up_proj=lin(inter, h), down_proj=lin(h, inter))
+            layers.append(ns(self_attn=attn, mlp=mlp, input_layernorm=norm(h), post_attention_layernorm=norm(h)))
+        exponent = torch.arange(0, d, 2, dtype=torch.int64).float() / d
+        model = ns(model=ns(embed_tokens=ns(weight=matrix(vocab, h)), layers=layers, norm=norm(h)),
+                   lm_head=lin(vocab, h),
+                   config=ns(head_dim=d, num_key_value_heads=nkv, rope_theta=cfg["rope_theta"], hidden_act="silu"),
+                   _ampere_inv_freq=(1.0 / (cfg["rope_theta"] ** exponent)).to(device),
+                   generation_config=ns(eos_token_id=None))
+        host_gen = torch.Generator().manual_seed(1234)
+        prompts = [torch.randint(0, vocab, (1, PROMPT_LEN), generator=host_gen).pin_memory() for _ in range(batch)]
+
+        def run(prompt_host, new_tokens, timings=None):
+            ids = prompt_host.to(device, non_blocking=True)
+            return ref.generate_tokens(model, ids, max_new_tokens=new_tokens, cache_kind="contiguous",
+                                       ignore_eos=True, timings=timings)
+
+        def device_ms(prompt_host, new_tokens):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            run(prompt_host, new_tokens)
+            stop.record()
+            torch.cuda.synchronize()
+            return start.elapsed_time(stop)
+
+        run(prompts[0], 4)                       # library handles, kernels loaded
+        with ClockSampler() as clocks:
+            step_ms = e2e_step_ms = 0.0
+            for prompt in prompts:
+                # the K timed decode steps of this request: a run of 1 + W + K tokens less a run of 1 + W tokens
+                short = min(device_ms(prompt, 1 + warmup) for _ in range(2))
+                timings: dict = {}
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                run(prompt, 1 + warmup + steps, timings)
+                stop.record()
+                torch.cuda.synchronize()
+                step_ms += (start.elapsed_time(stop) - short) / steps
+                e2e_step_ms += timings["tpot_ms"]        # its own host clock: token ids on the host every step
+        clock_summary = clocks.summary()
+        # prefill: the time to the first token of a 2,048-token prompt, by the reference's own clock
+        long_prompt = torch.randint(0, vocab, (1, PREFILL_TOKENS), generator=host_gen).pin_memory()
+        run(long_prompt, 1)
+        ttft = []
+        for _ in range(3):
+            timings = {}
+            run(long_prompt, 1, timings)
+            ttft.append(timings["ttft_ms"])
+        prefill_ms = statistics.median(ttft)
+        peaks = load_peaks()
+        flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+        line = {
+            "impl": "reference",
+            "metric": "decode tok/s at batch 8 (Qwen3-8B shape, B200); prefill alongside",
+            "value": round(batch / (step_ms / 1000), 2), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)",
+            "config": {
+                "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                "hidden": h, "heads": nh, "kv_heads": nkv, "head_dim": d, "intermediate": inter, "vocab": vocab,
+                "global_batch": batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                "path": "ampere_kv.runner.generate_tokens, cache_kind=contiguous (its default), SDPA, no extension",
+                "batching": "one request at a time (its batched decode needs its sm_86 extension)",
+                "timing": "CUDA events: run of 1+W+K tokens less run of 1+W tokens, per request, summed",
+                "parallelism": "single GPU", "l2": "inputs larger than L2 (all weights stream every token)",
+            },
+            "e2e": {"value": round(batch / (e2e_step_ms / 1000), 2), "unit": "tokens/s",
+                    "ms_per_step": round(e2e_step_ms, 4), "h2d_bytes_per_step": 8 * batch,
+                    "d2h_bytes_per_step": 8 * batch},
+            "gpu_launches": 0,
+            "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1000), 1), "tokens": PREFILL_TOKENS,
+                        "ms": round(prefill_ms, 3),
+                        "frac": round(flops["gemm"] / (prefill_ms / 1000) / (peaks["bf16_tflops"] * 1e12), 4)},
+            "clocks": clock_summary,
+        }
+        print(json.dumps(line))
+        return 0
+    except BaseException as exc:        # the actual error goes on record instead of a guess
+        if isinstance(exc, KeyboardInterrupt):
+            raise
+        last = traceback.format_exception_only(type(exc), exc)[-1].strip()
+        where = traceback.extract_tb(exc.__traceback__)[-1]
+        print(json.dumps({"impl": "reference", "unavailable":
+                          f"{last} (at {os.path.basename(where.filename)}:{where.lineno})"[:400]}))
+        return 0
 
 
 def main() -> int:
@@ -151,12 +286,10 @@ def main() -> int:
     args = parser.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "installed offline into baseline/_ref, but it only runs the published Qwen3-8B checkpoint, "
-                          "loaded by name with local_files_only=True (ampere_kv/runner.py:33-36; no checkpoint and no "
-                          "network here, no random-weights mode), and its extension holds sm_86 machine code only "
-                          "(setup.py:19), which a B200 cannot load"}))
-        return 0
+        if args.gpus != 1:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference runs on one GPU; --gpus must be 1"}))
+            return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
         return 2
@@ -273,7 +406,11 @@ def main() -> int:
     flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1000), 1), "tokens": PREFILL_TOKENS,
                "ms": round(prefill_ms, 3),
-               "frac": round(flops / (prefill_ms / 1000) / (peaks["bf16_tflops"] * 1e12), 4)}
+               "frac": round(flops["gemm"] / (prefill_ms / 1000) / (peaks["bf16_tflops"] * 1e12), 4),
+               "frac_of": "matrix-product FLOPs / burst bf16 peak", "gemm_tflop": round(flops["gemm"] / 1e12, 3),
+               "attention_tflop": round(flops["attention"] / 1e12, 3),
+               "frac_with_attention": round((flops["gemm"] + flops["attention"]) / (prefill_ms / 1000)
+                                            / (peaks["bf16_tflops"] * 1e12), 4)}
 
     points = {}
     if not args.no_points:
