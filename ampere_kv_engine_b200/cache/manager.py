@@ -4,9 +4,11 @@ What the reference keeps per layer and per request (one pool and one block table
 36 layers, advanced in lock-step: ampere_kv/paged_cache.py:10-27, ampere_kv/scheduler.py:63-64,
 :202) is kept once per *group* here.  A group is the set of schedule positions whose mixers
 ask for the same kind of cache (:class:`CacheSpec`): all positions, or only a window of them.
-Every group has its own page pool, its own storage
-``[positions in group, 2 (K, V), pages, kv_heads, page_size, head_dim]`` and one block table
-per request; a page id means the same page for every position of the group.
+Every group has its own page pool, one block table per request, and for every tensor its
+mixers store per token (attention: ``k`` and ``v``; another mixer may name one compressed
+tensor, or keys and values of different widths) a storage
+``[positions in group, pages, heads, page_size, width]``; a page id means the same page for
+every position and every tensor of the group.
 
 Pages come back in two ways: all of a request's pages when it is closed, and, in a window
 group, every page that lies wholly behind the window of the next query, as soon as the
@@ -19,7 +21,7 @@ attention model asks for none; the slot is still taken and returned with the req
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -33,11 +35,13 @@ class LayerCacheView:
 
     position: int
     group: int | None          # index into CacheManager.groups / StepContext.groups
-    k_cache: torch.Tensor | None
+    k_cache: torch.Tensor | None    # tensors["k"] / tensors["v"] of an attention cache, else None
     v_cache: torch.Tensor | None
     page_size: int
     writes: bool               # False: the pages belong to an earlier position, only read them
     state: torch.Tensor | None  # [max_seqs, *state_shape] float32, or None
+    #: every tensor the position's cache spec names: name -> [pages, heads, page_size, width]
+    tensors: dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 @dataclass
@@ -47,14 +51,16 @@ class CacheGroup:
     positions: list[int]
     page_size: int
     pool: IdPool
-    storage: torch.Tensor | None = None
+    #: tensor name -> [positions, pages, heads, page_size, width], or None when storage is not allocated
+    storage: dict[str, torch.Tensor] | None = None
 
     @property
     def window(self) -> int | None:
         return self.spec.window if self.spec.kind == "window" else None
 
     def bytes_per_page(self, element_size: int) -> int:
-        return len(self.positions) * 2 * self.spec.num_kv_heads * self.page_size * self.spec.head_dim * element_size
+        per_token = sum(t.heads * t.width for t in self.spec.stored())
+        return len(self.positions) * per_token * self.page_size * element_size
 
 
 class SequenceCache:
@@ -105,6 +111,11 @@ class CacheManager:
                 raise ValueError(f"schedule position {pos}: unknown cache kind {spec.kind!r}")
             if spec.kind == "window" and (spec.window is None or spec.window <= 0):
                 raise ValueError(f"schedule position {pos}: a window cache needs a positive window")
+            stored = spec.stored()
+            if not stored or any(t.heads <= 0 or t.width <= 0 for t in stored) or \
+                    len({t.name for t in stored}) != len(stored):
+                raise ValueError(f"schedule position {pos}: a paged cache stores at least one tensor per token, "
+                                 f"each with a name of its own and positive sizes; got {stored}")
             key = spec.group_key()
             if key not in by_key:
                 count = num_pages if isinstance(num_pages, int) else num_pages[len(self.groups)]
@@ -125,9 +136,10 @@ class CacheManager:
         self._state_shapes = [tuple(spec.state_shape) for spec in cache_specs]
         if allocate_storage:
             for group in self.groups:
-                shape = (len(group.positions), 2, group.pool.count, group.spec.num_kv_heads, page_size,
-                         group.spec.head_dim)
-                group.storage = torch.empty(shape, dtype=dtype, device=self.device)
+                group.storage = {
+                    t.name: torch.empty((len(group.positions), group.pool.count, t.heads, page_size, t.width),
+                                        dtype=dtype, device=self.device)
+                    for t in group.spec.stored()}
         self._cache_of = list(cache_of)
         self.sequences: dict[object, SequenceCache] = {}
 
@@ -140,10 +152,11 @@ class CacheManager:
             return LayerCacheView(position, None, None, None, self.page_size, False, state)
         group = self.groups[g]
         slot = self._position_slot[position]
-        k = v = None
+        tensors = {}
         if group.storage is not None:
-            k, v = group.storage[slot, 0], group.storage[slot, 1]
-        return LayerCacheView(position, g, k, v, self.page_size, self._cache_of[position] is None, state)
+            tensors = {name: whole[slot] for name, whole in group.storage.items()}
+        return LayerCacheView(position, g, tensors.get("k"), tensors.get("v"), self.page_size,
+                              self._cache_of[position] is None, state, tensors)
 
     def layer_views(self) -> list[LayerCacheView]:
         return [self.layer_view(i) for i in range(len(self._position_group))]
@@ -240,6 +253,10 @@ class CacheManager:
 
     def free_pages(self) -> list[int]:
         return [g.pool.num_free for g in self.groups]
+
+    def pages_to_start(self, num_tokens: int) -> list[int]:
+        """Pages per group that a request without a cache yet needs for its first ``num_tokens`` positions."""
+        return [(num_tokens + g.page_size - 1) // g.page_size for g in self.groups]
 
     def pages_for_tokens(self, num_tokens: int, chunk: int = 0) -> list[int]:
         """Upper bound of pages per group a request of ``num_tokens`` positions holds at any time,

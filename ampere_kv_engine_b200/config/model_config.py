@@ -190,14 +190,16 @@ def read_config_json(model_dir: str) -> dict[str, Any]:
             raise ConfigError(f"{path}: not valid JSON ({exc})") from exc
     if not isinstance(raw, dict):
         raise ConfigError(f"{path}: the top level must be an object")
-    # eos ids may live beside the model in generation_config.json (ampere_kv/runner.py:331)
+    # The reference stops on ``model.generation_config.eos_token_id`` (ampere_kv/runner.py:331): the ids of
+    # generation_config.json where that file carries them (a published checkpoint lists more ids there than in
+    # config.json), else config.json's own.
     gen_path = os.path.join(model_dir, "generation_config.json")
-    if raw.get("eos_token_id") is None and os.path.isfile(gen_path):
+    if os.path.isfile(gen_path):
         with open(gen_path, "r", encoding="utf-8") as handle:
             try:
                 gen = json.load(handle)
-            except json.JSONDecodeError:
-                gen = {}
+            except json.JSONDecodeError as exc:
+                raise ConfigError(f"{gen_path}: not valid JSON ({exc})") from exc
         if isinstance(gen, dict) and gen.get("eos_token_id") is not None:
             raw["eos_token_id"] = gen["eos_token_id"]
     return raw

@@ -31,13 +31,38 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: how its parts are arranged (``block``) and which parts they are."""
+    """One layer: how its parts are arranged (``block``, a registered block kind) and which parts they are.
+
+    The block kind decides which roles it has and builds each from the spec under that role's name.  The four
+    roles of a two-branch layer (a mixer and a feed-forward, a norm before each) have fields of their own;
+    a block with other roles (more norms, one norm shared by parallel branches, no feed-forward at all) finds
+    them in ``parts``, and its own constants in ``params``.
+    """
 
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: PartSpec | None = None
+    feed_forward: PartSpec | None = None
+    mixer_norm: PartSpec | None = None
+    feed_forward_norm: PartSpec | None = None
+    parts: dict[str, PartSpec] = field(default_factory=dict)
+    params: dict[str, Any] = field(default_factory=dict)
+
+    def roles(self) -> dict[str, PartSpec]:
+        """Every part of the layer by role name."""
+        out = {name: getattr(self, name) for name in ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+               if getattr(self, name) is not None}
+        for name, spec in self.parts.items():
+            if name in out:
+                raise ValueError(f"layer spec: role {name!r} is given twice")
+            out[name] = spec
+        return out
+
+    def role(self, name: str) -> PartSpec:
+        roles = self.roles()
+        if name not in roles:
+            raise ValueError(f"layer spec: block kind {self.block!r} needs a part in role {name!r}; "
+                             f"the layer has {sorted(roles)}")
+        return roles[name]
 
 
 @dataclass(frozen=True)

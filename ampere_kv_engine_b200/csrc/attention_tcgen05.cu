@@ -38,7 +38,6 @@ constexpr int kD = 128;             // head size
 constexpr int kRows = 128;          // query rows per CTA
 constexpr int kKeys = 64;           // keys per block
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
 
 __device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
@@ -51,21 +50,7 @@ __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(bar)) : "memory");
 }
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = s_addr(bar);
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
+  return mbar_wait_bounded(s_addr(bar), parity, kWaitLimit);
 }
 __device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
@@ -639,13 +624,7 @@ int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream)
     const int n = v ? atoi(v) : 0;
     return (n == 2 || n == 4) ? n : 0;
   }();
-  static const int sms = [] {
-    int device = 0, count = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
-      count = 148;
-    return count;
-  }();
+  const int sms = sm_count();
   const bool shallow = forced ? forced == 2 : (int64_t)grid.x * grid.y > sms;
   if (shallow) return launch_stages<2>(q_map, k_map, v_map, fp, grid, stream);
   return launch_stages<4>(q_map, k_map, v_map, fp, grid, stream);

@@ -89,6 +89,13 @@ Tensor smoke_add(const Tensor& a, const Tensor& b) {
   return out;
 }
 
+void wait_selftest(int64_t limit, Tensor& status) {
+  check_i32(status, "status", 1);
+  AKV_CHECK(limit >= 1 && limit <= 1000000, "limit must be between 1 and 1000000 tries");
+  c10::cuda::CUDAGuard guard(status.device());
+  check_launch(akv::launch_wait_selftest((uint32_t)limit, status.data_ptr<int>(), stream_of(status)), "wait_selftest");
+}
+
 void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const OptTensor& status,
                const OptTensor& sampled) {
   check_cuda(table, "table");
@@ -572,6 +579,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the engine";
   namespace py = pybind11;
   m.def("smoke_add", &smoke_add, "a + b on the device (toolchain check)");
+  m.def("wait_selftest", &wait_selftest, py::arg("limit"), py::arg("status"),
+        "a bounded wait on a barrier that nothing completes: leaves the wait-timeout code in status");
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("hidden"), py::arg("status") = py::none(),
         py::arg("sampled") = py::none());
   m.def("add_rmsnorm", &add_rmsnorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
@@ -603,4 +612,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("uniform"), py::arg("tokens"),
         py::arg("parts"), py::arg("tickets"));
   m.def("sample_slices", &sample_slices);
+  m.def("sm_count", &akv::sm_count, "streaming multiprocessors of the current device");
 }

@@ -103,6 +103,27 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// The one bounded wait of the package: poll an mbarrier (shared-memory address) for the given phase parity at most
+// `limit` times.  False when the phase did not complete; the caller then records kWaitTimeout, stops issuing work,
+// and leaves the kernel in order.  Every mbarrier wait of the TMA / tcgen05 kernels goes through this loop.
+constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;     // about a second
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar_addr, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
 // Programmatic dependent launch.  A kernel of the step's chain lets the next kernel start while it still runs
 // (pdl_launch_dependents, at its top) and waits for the previous kernel's results right before it first touches
 // them (pdl_wait).  What a kernel does before pdl_wait must not depend on the previous kernel: set-up, barrier

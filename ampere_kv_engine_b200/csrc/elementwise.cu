@@ -28,6 +28,43 @@ __global__ void smoke_add_kernel(const float* __restrict__ a, const float* __res
   if (i < n) out[i] = a[i] + b[i];
 }
 
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices] = {};      // 0: not asked yet (a race writes the same value twice)
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    cudaGetLastError();
+    return kFallbackSmCount;
+  }
+  if (cached[device] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) {
+      cudaGetLastError();
+      return kFallbackSmCount;
+    }
+    cached[device] = count;
+  }
+  return cached[device];
+}
+
+// Self-test of the bounded wait: one thread initialises an mbarrier that nobody ever arrives on and on which no
+// copy is in flight, waits on it through the package's one wait loop with the given limit, finds that the wait ran
+// out, reports kWaitTimeout as every production kernel would, and returns.  Nothing hangs and nothing faults.
+__global__ void wait_selftest_kernel(uint32_t limit, int* status) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&bar);
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(1u));
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (!mbar_wait_bounded(addr, 0u, limit)) set_status(status, kWaitTimeout);
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(addr) : "memory");
+}
+
+int launch_wait_selftest(uint32_t limit, int* status, cudaStream_t stream) {
+  if (limit == 0 || limit > 1000u * 1000u || status == nullptr) return (int)cudaErrorInvalidValue;
+  wait_selftest_kernel<<<1, 1, 0, stream>>>(limit, status);
+  return (int)cudaGetLastError();
+}
+
 int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream) {
   if (n == 0) return 0;
   const int threads = 256;

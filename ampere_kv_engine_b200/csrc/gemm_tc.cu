@@ -34,7 +34,6 @@ namespace {
 
 constexpr int kTileM = 128;      // features per CTA
 constexpr int kTileK = 64;       // K elements per stage: 128 bytes, one swizzle row
-constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -45,21 +44,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
+  return mbar_wait_bounded(smem_u32(bar), parity, kWaitLimit);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
@@ -595,7 +580,7 @@ int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmPara
   // and takes the deeper ring instead (64 tokens, o: 12.8 -> 11.5 us, down: 23.6 -> 21.7 us).
   constexpr int kDefault = BN == 16 ? 4 : 3;
   const int64_t ctas = (int64_t)((p.features + kTileM - 1) / kTileM) * p.splits;
-  const bool deep = BN > 16 && ctas <= 2 * 148;
+  const bool deep = BN > 16 && ctas <= 2 * sm_count();
   switch (epilogue) {
     case kEpilogueGated:
       return launch_stages<BN, __nv_bfloat16, kDefault, kEpilogueGated, kNormedX>(w_map, x_map, p, stream);
@@ -644,7 +629,7 @@ int small_m_gemm_splits(int64_t features, int64_t k) {
   const int64_t tiles = (features + kTileM - 1) / kTileM;
   const int64_t kb_total = (k + kTileK - 1) / kTileK;
   int splits = 1;
-  while (splits < 8 && tiles * splits < 2 * 148 && kb_total / (splits * 2) >= 4) splits *= 2;
+  while (splits < 8 && tiles * splits < 2 * sm_count() && kb_total / (splits * 2) >= 4) splits *= 2;
   return splits;
 }
 

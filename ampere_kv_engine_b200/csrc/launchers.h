@@ -12,6 +12,15 @@
 
 namespace akv {
 
+// Streaming multiprocessors of the current device, asked once per device.  When no device answers (a build box
+// without a GPU) the count of the B200 this package is written for stands in.
+constexpr int kFallbackSmCount = 148;
+int sm_count();
+
+// Runs the package's bounded mbarrier wait on a barrier that nothing completes, `limit` tries (at most a million),
+// and reports kWaitTimeout in `status`: a self-test of the path a production kernel takes when a wait gives up.
+int launch_wait_selftest(uint32_t limit, int* status, cudaStream_t stream);
+
 int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream);
 
 // hidden[n, :] = float(table[ids[n], :]).  With `sampled` (may be null), an id of -(r + 1) stands for sampled[r]:

@@ -2,8 +2,8 @@
 //
 // This has no counterpart in the reference project.  It exists for hosts that embed the library under a memory
 // regime of their own: a process whose device memory was handed out in full at start-up by its own pool, a
-// real-time loop that may not call into the allocator, a CUDA-graph capture in which cudaMalloc is illegal, or a
-// plugin that is only allowed to touch the buffers it is given.  Such callers cannot use the ordinary split
+// real-time loop that may not call into the allocator, or a plugin that is only allowed to touch the buffers it is
+// given.  Such callers cannot use the ordinary split
 // attention path, because that path needs a float32 workspace for the per-split partial results and the Python
 // wrapper allocates it on every call.
 //

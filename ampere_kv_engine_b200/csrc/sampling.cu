@@ -212,7 +212,7 @@ int launch_sample(const float* logits, const float* temperature, const float* un
   // as many slices per row as keep a few hundred blocks in flight: 8 for a handful of rows, 1 from 75 rows on
   // (measured at 64 rows: 8 slices 19.9 us, 1 slice 14.2 us for the arg-max; at 8 rows: 5.6 us against 7.4 us)
   int slices = kSampleSlices;
-  while (slices > 1 && num_rows * slices > 148) slices /= 2;
+  while (slices > 1 && num_rows * slices > sm_count()) slices /= 2;
   if (part_max == nullptr || part_arg == nullptr || part_sum == nullptr || tickets == nullptr)
     return (int)cudaErrorInvalidValue;
   int64_t slice_len = (vocab + slices - 1) / slices;

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import torch
 
+from ..config.engine_config import EngineConfig, dtype_name
 from ..models.decoder import DecoderModel
 from ..models.registry import ARCHITECTURES, config_from_dict, load_config
 from ..sampling.sampler import Sampler, SamplingParams
@@ -19,17 +20,8 @@ from .batch import SeqStep
 from .scheduler import Request, Scheduler
 from .step import ModelRunner
 
-_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
-
-
 def parse_dtype(name) -> torch.dtype:
-    if isinstance(name, torch.dtype):
-        if name not in (torch.bfloat16, torch.float32):
-            raise ValueError(f"dtype must be bfloat16 or float32, got {name}")
-        return name
-    if name not in _DTYPES:
-        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {name!r}")
-    return _DTYPES[name]
+    return {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype_name(name)]
 
 
 def set_exact_matmul() -> None:
@@ -47,23 +39,26 @@ def set_exact_matmul() -> None:
 class Engine:
     """Model + cache + scheduler + sampler on one device."""
 
-    def __init__(self, model: DecoderModel, *, page_size: int = 16, num_pages: int | None = None,
-                 max_tokens: int | None = None, max_seqs: int = 256, max_batch_tokens: int = 2048,
-                 admission: str = "budget"):
+    def __init__(self, model: DecoderModel, config: EngineConfig | None = None, **options):
+        """``config`` and/or single options of :class:`EngineConfig` by keyword (they override ``config``'s)."""
         set_exact_matmul()
         self.model = model
         self.device = model.device
-        if num_pages is None:
-            if max_tokens is None:
-                max_tokens = min(model.spec.max_position, 8192) * 4
-            num_pages = (max_tokens + page_size - 1) // page_size + max_seqs
-        self.runner = ModelRunner(model, page_size=page_size, num_pages=num_pages, max_seqs=max_seqs)
+        if config is None and "dtype" not in options:
+            options["dtype"] = dtype_name(model.dtype)      # no word on the dtype: the model's
+        config = EngineConfig.from_options(config, **options)
+        if parse_dtype(config.dtype) != model.dtype:
+            raise ValueError(f"engine option 'dtype' is {config.dtype} but the model was built in {model.dtype}")
+        self.config = config = config.resolved(model.spec.max_position)
+        self.runner = ModelRunner(model, page_size=config.page_size, num_pages=config.num_pages,
+                                  max_seqs=config.max_seqs, kv_dtype=parse_dtype(config.kv_dtype),
+                                  cuda_graphs=config.cuda_graphs)
         self.manager = self.runner.manager
         self.sampler = Sampler(self.device)
         self.vocab_size = model.spec.vocab_size
-        self.max_batch_tokens = max_batch_tokens
-        self.max_seqs = max_seqs
-        self.admission = admission
+        self.max_batch_tokens = config.max_batch_tokens
+        self.max_seqs = max_seqs = config.max_seqs
+        self.admission = config.admission
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self._stream_counter = 0
         # pinned landing places of the chosen tokens (+ the status word); three, since one step may be in flight
@@ -76,22 +71,27 @@ class Engine:
     # ------------------------------------------------------------------ construction
 
     @classmethod
-    def from_pretrained(cls, model_dir: str, *, dtype="bfloat16", device="cuda", **engine_options) -> "Engine":
-        arch, config = load_config(model_dir)
-        model = DecoderModel(arch.build_spec(config), dtype=parse_dtype(dtype), device=device)
+    def from_pretrained(cls, model_dir: str, *, dtype=None, device="cuda", config: EngineConfig | None = None,
+                        **engine_options) -> "Engine":
+        """``dtype`` (or ``config.dtype``; default bfloat16) is the compute dtype the weights are loaded in."""
+        options = EngineConfig.from_options(config, **engine_options, **({} if dtype is None else {"dtype": dtype}))
+        arch, model_config = load_config(model_dir)
+        model = DecoderModel(arch.build_spec(model_config), dtype=parse_dtype(options.dtype), device=device)
         load_weights(model, model_dir)
-        return cls(model, **engine_options)
+        return cls(model, options)
 
     @classmethod
-    def from_random(cls, config, seed: int = 0, *, dtype="bfloat16", device="cuda", **engine_options) -> "Engine":
-        """``config``: a typed configuration, or a dict of config.json keys (with ``architectures``)."""
-        if isinstance(config, dict):
-            arch, config = config_from_dict(config)
+    def from_random(cls, model_config, seed: int = 0, *, dtype=None, device="cuda",
+                    config: EngineConfig | None = None, **engine_options) -> "Engine":
+        """``model_config``: a typed configuration, or a dict of config.json keys (with ``architectures``)."""
+        options = EngineConfig.from_options(config, **engine_options, **({} if dtype is None else {"dtype": dtype}))
+        if isinstance(model_config, dict):
+            arch, model_config = config_from_dict(model_config)
         else:
-            arch = ARCHITECTURES[config.architectures[0]]
-        model = DecoderModel(arch.build_spec(config), dtype=parse_dtype(dtype), device=device)
+            arch = ARCHITECTURES[model_config.architectures[0]]
+        model = DecoderModel(arch.build_spec(model_config), dtype=parse_dtype(options.dtype), device=device)
         init_random(model, seed)
-        return cls(model, **engine_options)
+        return cls(model, options)
 
     # ------------------------------------------------------------------ executor interface (for the scheduler)
 
@@ -140,7 +140,7 @@ class Engine:
     def new_scheduler(self, **overrides) -> Scheduler:
         options = dict(max_batch_tokens=self.max_batch_tokens, max_seqs=self.max_seqs,
                        eos_token_ids=self.eos_token_ids, admission=self.admission,
-                       max_context=None)
+                       max_context=self.config.max_context, lookahead=self.config.lookahead)
         options.update(overrides)
         return Scheduler(self, **options)
 

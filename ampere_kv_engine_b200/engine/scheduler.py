@@ -217,7 +217,7 @@ class Scheduler:
                     return
             else:
                 first = min(len(request.tokens), self.max_batch_tokens)
-                need = [(first + self.manager.page_size - 1) // self.manager.page_size] * len(self.manager.groups)
+                need = self.manager.pages_to_start(first)
                 if any(n > g.pool.num_free for n, g in zip(need, self.manager.groups)):
                     return
             self.waiting.pop(0)

@@ -151,6 +151,23 @@ def kv_write(k, v, slots, k_cache, v_cache, status=None) -> None:
     _launched()
 
 
+#: streaming multiprocessors assumed when no device can be asked (planning on a host without a GPU): a B200's
+FALLBACK_SM_COUNT = 148
+_SM_COUNT: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (default: the current CUDA device), asked once per device."""
+    if not torch.cuda.is_available():
+        return FALLBACK_SM_COUNT
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _SM_COUNT:
+        _SM_COUNT[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _SM_COUNT[index]
+
+
 def attention_takes_tensor_cores(dtype: torch.dtype, head_dim: int, group_size: int, page_size: int) -> bool:
     """Whether the TMA + tensor-core attention kernels take these sizes (else the general kernel runs)."""
     return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group_size <= 16 and page_size >= 8
@@ -158,7 +175,7 @@ def attention_takes_tensor_cores(dtype: torch.dtype, head_dim: int, group_size: 
 
 
 def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
-                  tensor_core: bool = False, mean_context: int | None = None) -> int:
+                  tensor_core: bool = False, mean_context: int | None = None, sms: int | None = None) -> int:
     """How many key ranges each decoded token's attention is cut into so that a small batch still fills the GPU
     and a long sequence among short ones does not keep one CTA walking alone.  ``max_context`` / ``mean_context``:
     the keys the longest and the average token of the batch walks (the mean defaults to the maximum).
@@ -166,11 +183,12 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
     The tensor-core decode kernel runs one CTA per (token, kv head, split), four to an SM; the general kernel
     one warp per (token, kv head, 8 rows, split), sixteen to an SM.
     """
+    sms = sms or sm_count()
     if tensor_core:
         # 1, 2, 4 or 8 splits (merged inside the kernel by a cluster).  A cost in microseconds, fitted to
         # measurements on B200 (32 q-heads, 8 kv-heads, head size 128, batches of 4 to 64, 1,088 to 8,000 keys,
         # equal and mixed lengths): a CTA spends about 1.1 us on a 32-key block and a fixed 5.5 us (7.5 us in a
-        # cluster) on start-up and merge; the GPU holds 148 x 4 CTAs at a time.  With equal lengths all CTAs end
+        # cluster) on start-up and merge; the GPU holds four CTAs per SM at a time.  With equal lengths all CTAs end
         # together, so a grid that needs a further round of CTAs pays for a whole one; with mixed lengths slots
         # free up all the time and only the fraction counts.  The longest sequences' CTAs start first (the batch
         # layout orders the tiles so), so the step takes the longest walk or the rounds of mean walks, whichever
@@ -178,7 +196,7 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
         # Measured (us at 1/2/4/8 splits): batch 8 at 1,088 keys 35/24/15/12; batch 24: 40/27/32/36; batch 64:
         # 48/57/68/95; batch 48 at 4,096 keys 169/172/142/159; batch 64 with 300 to 4,600 keys (mean 2,500):
         # 171/110/119/144; batch 40 likewise: 160/94/75/88; batch 20: 144/81/48/46.
-        items, slots = max(1, num_tiles * num_kv_heads), 148 * 4
+        items, slots = max(1, num_tiles * num_kv_heads), sms * 4
         blocks_max = max(1, (max_context + 31) // 32)
         blocks_mean = blocks_max if mean_context is None else max(1, min(blocks_max, (int(mean_context) + 31) // 32))
         evenness = (blocks_mean / blocks_max) ** 2
@@ -196,7 +214,7 @@ def choose_splits(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_con
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
-    items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), 148 * 16, 128
+    items, target, min_keys = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 7) // 8)), sms * 16, 128
     if items >= target or max_context <= min_keys:
         return 1
     want = target // items

@@ -12,9 +12,8 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import ModelSpec
-from ..parts import attention, block, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, CacheSpec, ParamSpec, build_part)
-from ..parts.embedding import LinearHead, TokenEmbedding
+from ..parts import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, CacheSpec, ParamSpec, build_part
 
 
 class DecoderModel:
@@ -26,29 +25,26 @@ class DecoderModel:
         self.dtype = dtype
         self.device = torch.device(device)
         kw = dict(hidden_size=spec.hidden_size, dtype=dtype, device=self.device)
-        self.embedding = TokenEmbedding(spec.embedding, **kw)
-        self.blocks = []
-        for layer in spec.layers:
-            mixer = build_part(MIXERS, layer.mixer, **kw)
-            ff = build_part(FEED_FORWARDS, layer.feed_forward, **kw)
-            n1 = build_part(NORMS, layer.mixer_norm, **kw)
-            n2 = build_part(NORMS, layer.feed_forward_norm, **kw)
-            self.blocks.append(BLOCKS.get(layer.block)(mixer, ff, n1, n2))
+        self.embedding = build_part(EMBEDDINGS, spec.embedding, **kw)
+        self.blocks = [BLOCKS.get(layer.block)(layer, **kw) for layer in spec.layers]
         self.final_norm = build_part(NORMS, spec.final_norm, **kw)
-        self.head = LinearHead(spec.head, **kw)
+        self.head = build_part(HEADS, spec.head, **kw)
         self.loaded = False
 
     # ------------------------------------------------------------------ tensors
 
     def _parts(self):
-        yield self.embedding
+        """Every part, a part's own children after it."""
+        def walk(part):
+            yield part
+            for child in part.children():
+                yield from walk(child)
+        yield from walk(self.embedding)
         for blk in self.blocks:
-            yield blk.mixer_norm
-            yield blk.mixer
-            yield blk.feed_forward_norm
-            yield blk.feed_forward
-        yield self.final_norm
-        yield self.head
+            for part in blk.parts():
+                yield from walk(part)
+        yield from walk(self.final_norm)
+        yield from walk(self.head)
 
     def param_specs(self) -> dict[str, ParamSpec]:
         """Every tensor of the checkpoint by its full name."""
@@ -76,15 +72,13 @@ class DecoderModel:
     @property
     def graph_safe(self) -> bool:
         """Every part only enqueues device work that depends on the batch layout alone."""
-        parts = list(self._parts()) + [blk.mixer.position_encoding for blk in self.blocks
-                                       if hasattr(blk.mixer, "position_encoding")]
-        return all(getattr(part, "graph_safe", False) for part in parts)
+        return all(getattr(part, "graph_safe", False) for part in self._parts())
 
     # ------------------------------------------------------------------ cache needs
 
     def cache_specs(self) -> list[CacheSpec]:
         """One per schedule position."""
-        return [self.blocks[e.layer].mixer.cache_spec() for e in self.spec.schedule]
+        return [self.blocks[e.layer].cache_spec() for e in self.spec.schedule]
 
     def cache_of(self) -> list[int | None]:
         return [e.cache_of for e in self.spec.schedule]

@@ -49,6 +49,9 @@ class PagedAttention(Mixer):
                                             dtype=self.dtype, device=self.device)
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm_weight = self.k_norm_weight = None
 
+    def children(self):
+        return (self.position_encoding,)
+
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(kind="window" if self.window is not None else "full", num_kv_heads=self.num_kv_heads,
                          head_dim=self.head_dim, window=None if self.window is None else int(self.window))

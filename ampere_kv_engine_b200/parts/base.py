@@ -6,8 +6,9 @@ computes on the flat token batch of one step.  Parts never look at a model confi
 and do not know which architecture uses them; the reference, by contrast, wires one model's
 attribute paths into every function (ampere_kv/runner.py:60-77, 102-179).
 
-Kinds are looked up in five registries (mixers, feed-forwards, norms, position encodings,
-blocks).  Registering a new kind is one decorator call and needs no change here.
+Kinds are looked up in seven registries (mixers, feed-forwards, norms, position encodings,
+blocks, embeddings, heads).  Registering a new kind is one decorator call and needs no change
+here.
 """
 
 from __future__ import annotations
@@ -17,7 +18,7 @@ from typing import Any, Callable
 
 import torch
 
-from ..config.spec import PartSpec
+from ..config.spec import LayerSpec, PartSpec
 from ..kernels import ops
 
 
@@ -37,11 +38,23 @@ class ParamSpec:
 
 
 @dataclass(frozen=True)
+class CacheTensor:
+    """One thing a token leaves in a paged cache: ``heads`` rows of ``width`` elements."""
+
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
 class CacheSpec:
     """What a mixer needs the cache manager to keep for each request.
 
-    ``kind``: ``"none"``, ``"full"`` (keys/values of every position) or ``"window"`` (only
-    the last ``window`` positions are ever read, pages behind it are given back).
+    ``kind``: ``"none"``, ``"full"`` (every position is kept) or ``"window"`` (only the last
+    ``window`` positions are ever read, pages behind it are given back).  What a position stores
+    is a tuple of named tensors (``tensors``); when none is given it is what attention stores:
+    ``k`` and ``v``, each ``num_kv_heads`` rows of ``head_dim``.  A mixer that keeps one
+    compressed tensor per token, or keys and values of different widths, names them itself.
     ``state_shape`` asks for a fixed-size float32 state per request (``()`` = none).
     Mixers whose specs are equal share a cache group: one page pool, one block table per
     request.
@@ -52,9 +65,17 @@ class CacheSpec:
     head_dim: int = 0
     window: int | None = None
     state_shape: tuple[int, ...] = ()
+    tensors: tuple[CacheTensor, ...] | None = None
+
+    def stored(self) -> tuple[CacheTensor, ...]:
+        if self.kind == "none":
+            return ()
+        if self.tensors is not None:
+            return tuple(self.tensors)
+        return (CacheTensor("k", self.num_kv_heads, self.head_dim), CacheTensor("v", self.num_kv_heads, self.head_dim))
 
     def group_key(self) -> tuple:
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+        return (self.kind, self.stored(), self.window)
 
 
 class Part:
@@ -76,6 +97,11 @@ class Part:
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         """Receive the tensors of :meth:`param_specs` (already on the device, cast per kind)."""
+
+    def children(self) -> tuple["Part", ...]:
+        """Parts this part built for itself (a mixer's position encoding): the model asks them for tensors and for
+        ``graph_safe`` as it asks the part itself."""
+        return ()
 
 
 class Norm(Part):
@@ -134,14 +160,58 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block:
-    """Arrangement of one layer's parts around the residual stream."""
+class Embedding(Part):
+    """Token ids to the float32 residual stream."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
+        """[tokens] int32 -> [tokens, hidden] float32.  ``ctx.sampled`` may stand for ids the host has not read."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normalised activations of the wanted rows to float32 logits."""
+
+    def tie(self, embedding: Embedding) -> None:
+        """Called once all tensors are loaded: a head that shares the embedding's matrix takes it here."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of one layer's parts around the residual stream.
+
+    A block kind is built from the layer's spec and builds its own parts from the roles it knows
+    (:meth:`build_role`), so how many norms or branches a layer has is the block's business.  The model needs three
+    things of it: :meth:`parts` (whose tensors to load), :meth:`cache_spec` (what the layer keeps per request: one
+    cache view per schedule position) and :meth:`forward`.
+    """
+
+    #: registry of each role this base class knows; a block kind with other roles extends it
+    ROLE_REGISTRIES: dict[str, "Registry"] = {}
+
+    def __init__(self, layer: LayerSpec, *, hidden_size: int, dtype: torch.dtype, device: torch.device):
+        self.layer = layer
+        self.hidden_size, self.dtype, self.device = hidden_size, dtype, device
+        self._built: list[Part] = []
+
+    def build_role(self, role: str, registry: "Registry | None" = None) -> Part:
+        """Build the part the layer spec names for ``role`` and remember it."""
+        registry = registry or self.ROLE_REGISTRIES.get(role)
+        if registry is None:
+            raise ValueError(f"block kind {self.layer.block!r}: no registry is known for role {role!r}")
+        part = build_part(registry, self.layer.role(role), hidden_size=self.hidden_size, dtype=self.dtype,
+                          device=self.device)
+        self._built.append(part)
+        return part
+
+    def parts(self) -> list[Part]:
+        return list(self._built)
+
+    def cache_spec(self) -> CacheSpec:
+        """What this layer keeps per request: its mixer's needs (a layer without a mixer keeps nothing)."""
+        mixer = getattr(self, "mixer", None)
+        return mixer.cache_spec() if mixer is not None else CacheSpec()
 
     def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx, cache
                 ) -> tuple[torch.Tensor, torch.Tensor | None]:
@@ -197,12 +267,18 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+Block.ROLE_REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "mixer_norm": NORMS,
+                         "feed_forward_norm": NORMS}
 
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
 register_block = BLOCKS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
 
 
 def build_part(registry: Registry, spec: PartSpec, *, hidden_size: int, dtype: torch.dtype,

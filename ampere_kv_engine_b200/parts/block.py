@@ -14,6 +14,15 @@ from .base import Block, register_block
 
 @register_block("prenorm")
 class PreNormBlock(Block):
+    """roles: ``mixer_norm``, ``mixer``, ``feed_forward_norm``, ``feed_forward``."""
+
+    def __init__(self, layer, **kw):
+        super().__init__(layer, **kw)
+        self.mixer_norm = self.build_role("mixer_norm")
+        self.mixer = self.build_role("mixer")
+        self.feed_forward_norm = self.build_role("feed_forward_norm")
+        self.feed_forward = self.build_role("feed_forward")
+
     def forward(self, hidden, delta, ctx, cache):
         x = self.run_norm(self.mixer_norm, hidden, delta, ctx, consumer=self.mixer)
         attn = self.run_branch(self.mixer, hidden, x, ctx, cache)

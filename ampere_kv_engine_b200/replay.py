@@ -40,21 +40,27 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
+    parser.add_argument("--max-seqs", type=int, default=8,
+                        help="most requests live at a time (default 8; the trace format promises four)")
+    parser.add_argument("--no-graphs", action="store_true",
+                        help="run decode-only steps as they come instead of replaying them as CUDA graphs")
     parser.add_argument("--device", default="cuda")
     args = parser.parse_args(argv)
-    if args.max_tokens <= 0:
-        parser.error("--max-tokens must be positive")
+    if args.max_tokens <= 0 or args.max_seqs <= 0:
+        parser.error("--max-tokens and --max-seqs must be positive")
     if 64 % args.page_size and args.page_size % 64:
         parser.error("--page-size must divide 64 or be a multiple of it")
 
+    from .config.engine_config import EngineConfig
     from .engine.batch import SeqStep
     from .engine.engine import Engine
 
     os.makedirs(args.out, exist_ok=True)
     round_to = max(64, args.page_size)
     num_pages = (args.max_tokens + round_to - 1) // round_to * round_to // args.page_size
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, device=args.device, page_size=args.page_size,
-                                    num_pages=num_pages, max_seqs=8)
+    engine = Engine.from_pretrained(args.model, device=args.device, config=EngineConfig(
+        dtype=args.dtype, page_size=args.page_size, num_pages=num_pages, max_seqs=args.max_seqs,
+        cuda_graphs=not args.no_graphs))
     runner = engine.runner
     live: dict[str, object] = {}
     for line in stdin:

@@ -100,6 +100,8 @@ def main(argv=None) -> int:
     parser.add_argument("--ignore-eos", action="store_true")
     parser.add_argument("--page-size", type=int, default=PAGED_BLOCK_SIZE)
     parser.add_argument("--max-batch-tokens", type=int, default=2048)
+    parser.add_argument("--max-context", type=int, default=None,
+                        help="longest prompt + new tokens accepted (default: the model's max_position_embeddings)")
     parser.add_argument("--num-pages", type=int, default=None,
                         help="pages of the cache pool (default: enough for the prompt and the new tokens)")
     args = parser.parse_args(argv)
@@ -109,10 +111,13 @@ def main(argv=None) -> int:
         parser.error("give --model DIR or --random-config FILE")
     if args.prompt_len is not None and (args.prompt_ids is not None or args.prompt_len < 1):
         parser.error("--prompt-len is a positive count and goes without --prompt-ids")
-    want_kv = {"bfloat16": "bf16", "float32": "fp32"}[args.dtype]
-    if args.kv_dtype is not None and args.kv_dtype != want_kv:
-        parser.error(f"--kv-dtype {args.kv_dtype} does not go with --dtype {args.dtype}: the cache dtype is the "
-                     f"compute dtype")
+    from .config.engine_config import EngineConfig, EngineConfigError
+    try:
+        base_options = EngineConfig(dtype=args.dtype, kv_dtype=args.kv_dtype, page_size=args.page_size, max_seqs=4,
+                                    max_batch_tokens=args.max_batch_tokens, num_pages=args.num_pages,
+                                    max_context=args.max_context)
+    except EngineConfigError as exc:
+        parser.error(str(exc))
     import torch
     if not torch.cuda.is_available():
         raise RuntimeError("generation needs a CUDA device")
@@ -123,13 +128,14 @@ def main(argv=None) -> int:
             raw_config = json.load(handle)
 
         def build(dtype, **options):
-            return Engine.from_random(raw_config, args.random_seed, dtype=dtype, **options)
+            return Engine.from_random(raw_config, args.random_seed, config=base_options.replace(
+                dtype=dtype, kv_dtype=None, **options))
         vocab = int(raw_config["vocab_size"])
     else:
         from .models.registry import load_config
 
         def build(dtype, **options):
-            return Engine.from_pretrained(args.model, dtype=dtype, **options)
+            return Engine.from_pretrained(args.model, config=base_options.replace(dtype=dtype, kv_dtype=None, **options))
         vocab = int(load_config(args.model)[1].vocab_size)
     if args.prompt_len is not None:
         generator = torch.Generator().manual_seed(args.seed)
@@ -137,9 +143,7 @@ def main(argv=None) -> int:
     else:
         prompt = _read_prompt(args.prompt_ids)
     tokens = len(prompt) + args.max_new_tokens
-    options = dict(page_size=args.page_size, max_tokens=tokens + 64, max_seqs=4, max_batch_tokens=args.max_batch_tokens)
-    if args.num_pages is not None:
-        options["num_pages"] = args.num_pages
+    options = dict(max_tokens=tokens + 64)
     engine = build(args.dtype, **options)
     print(f"model={args.model or args.random_config} mode={args.mode} cache={args.cache} dtype={args.dtype} prompt_tokens={len(prompt)}")
     if args.mode == "benchmark":

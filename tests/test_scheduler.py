@@ -369,3 +369,28 @@ def test_random_arrivals_cancels_and_pools_end_right(seed):
     ex.manager.check_invariants()
     assert ex.manager.free_pages() == [pages] * len(specs) and s.reserved == [0] * len(specs)
     assert ex.launched == ex.collected
+
+
+def test_kernel_status_becomes_an_error_and_is_cleared(fake_ext):
+    """A kernel that met an impossible index, or whose bounded wait gave up, leaves a code in the status word; the
+    step's owner turns it into one Python error at its sync point and clears the word."""
+    from ampere_kv_engine_b200.config.engine_config import EngineConfig
+    from ampere_kv_engine_b200.engine.engine import Engine
+    from ampere_kv_engine_b200.engine.step import KernelStatusError
+    from models_util import model_folder
+    engine = Engine.from_pretrained(model_folder("A"), device="cpu", config=EngineConfig(dtype="float32", num_pages=16))
+    runner = engine.runner
+    runner.raise_on_status()                         # nothing reported: nothing raised
+    for code, text in ((5, "bounded wait"), (1, "block-table"), (3, "token id"), (77, "unknown")):
+        runner.status.fill_(code)
+        with pytest.raises(KernelStatusError, match=text):
+            runner.raise_on_status()
+        assert int(runner.status.item()) == 0
+    # through the executor: a code left by the step surfaces when its tokens are collected
+    scheduler = engine.new_scheduler(lookahead=False)
+    scheduler.submit("r", [1, 2, 3], 4, ignore_eos=True)
+    scheduler.step()
+    runner.status.fill_(5)
+    with pytest.raises(KernelStatusError, match="bounded wait"):
+        scheduler.step()
+    assert int(runner.status.item()) == 0
