@@ -29,6 +29,43 @@ import numpy as np
 import torch
 
 
+class Replayer:
+    """Feeds trace steps to an engine's own step function and hands back the logits.  It owns nothing but the map
+    from request ids to their cache holds."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.runner = engine.runner
+        self.live: dict[str, object] = {}
+
+    def step(self, record: dict):
+        """Run one trace step; float32 logits [wanted, vocab] on the device, or None when nothing was wanted."""
+        from .engine.batch import SeqStep
+        entries = []
+        for item in record.get("entries", []):
+            rid = str(item["id"])
+            if rid not in self.live:
+                self.live[rid] = self.runner.open(rid)
+            entries.append(SeqStep(self.live[rid], [int(t) for t in item["tokens"]],
+                                   [int(w) for w in item.get("want", [])]))
+        logits = None
+        if entries:
+            logits = self.runner.step(entries)
+            if logits is not None:
+                logits = logits.to(torch.float32)
+        for rid in record.get("end", []):
+            rid = str(rid)
+            if rid in self.live:
+                self.runner.close(self.live.pop(rid))
+        return logits
+
+
+def pool_pages(max_tokens: int, page_size: int) -> int:
+    """Pages for ``max_tokens`` tokens rounded up to a multiple of 64 (or of the page size, if that is larger)."""
+    round_to = max(64, page_size)
+    return (max_tokens + round_to - 1) // round_to * round_to // page_size
+
+
 def main(argv=None, stdin=None, stdout=None) -> int:
     stdin = sys.stdin if stdin is None else stdin
     stdout = sys.stdout if stdout is None else stdout
@@ -52,40 +89,25 @@ def main(argv=None, stdin=None, stdout=None) -> int:
         parser.error("--page-size must divide 64 or be a multiple of it")
 
     from .config.engine_config import EngineConfig
-    from .engine.batch import SeqStep
     from .engine.engine import Engine
 
     os.makedirs(args.out, exist_ok=True)
-    round_to = max(64, args.page_size)
-    num_pages = (args.max_tokens + round_to - 1) // round_to * round_to // args.page_size
     engine = Engine.from_pretrained(args.model, device=args.device, config=EngineConfig(
-        dtype=args.dtype, page_size=args.page_size, num_pages=num_pages, max_seqs=args.max_seqs,
-        cuda_graphs=not args.no_graphs))
-    runner = engine.runner
-    live: dict[str, object] = {}
+        dtype=args.dtype, page_size=args.page_size, num_pages=pool_pages(args.max_tokens, args.page_size),
+        max_seqs=args.max_seqs, cuda_graphs=not args.no_graphs))
+    replayer = Replayer(engine)
     for line in stdin:
         line = line.strip()
         if not line:
             continue
         record = json.loads(line)
         step = record["step"]
-        entries = []
-        for item in record.get("entries", []):
-            rid = str(item["id"])
-            if rid not in live:
-                live[rid] = runner.open(rid)
-            entries.append(SeqStep(live[rid], [int(t) for t in item["tokens"]], [int(w) for w in item.get("want", [])]))
-        if entries:
-            logits = runner.step(entries)
-            if logits is not None:
-                host = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
-                with open(os.path.join(args.out, f"{step}.f32"), "wb") as handle:
-                    handle.write(np.ascontiguousarray(host).tobytes())
-            runner.raise_on_status()
-        for rid in record.get("end", []):
-            rid = str(rid)
-            if rid in live:
-                runner.close(live.pop(rid))
+        logits = replayer.step(record)
+        if logits is not None:
+            host = logits.cpu().numpy().astype("<f4", copy=False)
+            with open(os.path.join(args.out, f"{step}.f32"), "wb") as handle:
+                handle.write(np.ascontiguousarray(host).tobytes())
+        engine.runner.raise_on_status()
         print(f"done {step}", file=stdout, flush=True)
     return 0
 

@@ -40,7 +40,7 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor)
     x: [T, heads, D]; positions: [T] absolute.  Angles in float32, duplicated to both
     halves; cos/sin cast to x's dtype; x*cos + rotate_half(x)*sin in x's dtype.
     """
-    angles = positions.to(torch.float32)[:, None] * inv_freq[None, :]          # [T, D/2]
+    angles = positions.to(torch.float32)[:, None] * inv_freq.to(positions.device)[None, :]   # [T, D/2]
     angles = torch.cat((angles, angles), dim=-1)                               # [T, D]
     cos = angles.cos().to(x.dtype)[:, None, :]
     sin = angles.sin().to(x.dtype)[:, None, :]
@@ -64,8 +64,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     kf = k.float().repeat_interleave(group, dim=1)
     vf = v.float().repeat_interleave(group, dim=1)
     scores = torch.einsum("thd,shd->hts", q.float(), kf) * dim ** -0.5
-    i = torch.arange(tokens)[:, None]
-    j = torch.arange(tokens)[None, :]
+    i = torch.arange(tokens, device=q.device)[:, None]
+    j = torch.arange(tokens, device=q.device)[None, :]
     visible = j <= i
     if window is not None:
         visible &= j > i - window
@@ -145,8 +145,9 @@ def forward_logits(w: dict, config: dict, token_ids: list[int]) -> torch.Tensor:
     position, this keeps all).  A tied head reuses the embedding (runner.py:297 reads
     ``lm_head.weight``, which is the embedding tensor when tied).
     """
-    ids = torch.tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(len(token_ids))
+    device = w["model.embed_tokens.weight"].device       # the whole computation runs where the tensors are
+    ids = torch.tensor(token_ids, dtype=torch.long, device=device)
+    positions = torch.arange(len(token_ids), device=device)
     h = w["model.embed_tokens.weight"][ids]
     windows = layer_windows(config)
     for index in range(config["num_hidden_layers"]):

@@ -151,24 +151,29 @@ def test_embedding_and_head_parts(dtype):
 def test_prenorm_block_against_plain_layer(dtype):
     """One whole layer (norm, attention, residual, norm, feed-forward, residual) on a whole sequence."""
     from ampere_kv_engine_b200.cache.manager import CacheManager
-    from ampere_kv_engine_b200.config.spec import PartSpec
+    from ampere_kv_engine_b200.config.spec import LayerSpec, PartSpec
     from ampere_kv_engine_b200.engine.batch import SeqStep, build_context
-    from ampere_kv_engine_b200.parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+    from ampere_kv_engine_b200.parts.base import BLOCKS
     cfg = {"hidden_size": 80, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 32,
            "intermediate_size": 112, "rms_norm_eps": 1e-5, "rope_theta": 12345.0, "num_hidden_layers": 1}
     p = "model.layers.0"
-    mixer = build(MIXERS, PartSpec("attention", {
-        "num_heads": 5, "num_kv_heads": 5, "head_dim": 32, "qk_norm": True, "qk_norm_eps": 1e-5, "bias": False,
-        "window": None, "scale": None, "position_encoding": PartSpec("rope", {"theta": 12345.0, "rotary_dim": 32})},
-        f"{p}.self_attn"), 80, dtype)
-    ff = build(FEED_FORWARDS, PartSpec("gated_mlp", {"intermediate_size": 112}, f"{p}.mlp"), 80, dtype)
-    n1 = build(NORMS, PartSpec("rmsnorm", {"eps": 1e-5}, f"{p}.input_layernorm"), 80, dtype)
-    n2 = build(NORMS, PartSpec("rmsnorm", {"eps": 1e-5}, f"{p}.post_attention_layernorm"), 80, dtype)
+    layer = LayerSpec(
+        "prenorm",
+        mixer=PartSpec("attention", {
+            "num_heads": 5, "num_kv_heads": 5, "head_dim": 32, "qk_norm": True, "qk_norm_eps": 1e-5, "bias": False,
+            "window": None, "scale": None, "position_encoding": PartSpec("rope", {"theta": 12345.0, "rotary_dim": 32})},
+            f"{p}.self_attn"),
+        feed_forward=PartSpec("gated_mlp", {"intermediate_size": 112}, f"{p}.mlp"),
+        mixer_norm=PartSpec("rmsnorm", {"eps": 1e-5}, f"{p}.input_layernorm"),
+        feed_forward_norm=PartSpec("rmsnorm", {"eps": 1e-5}, f"{p}.post_attention_layernorm"))
+    # the block kind builds its own parts from the roles of the layer spec
+    block = BLOCKS.get("prenorm")(layer, hidden_size=80, dtype=dtype, device=torch.device("cuda"))
+    mixer = block.mixer
+    assert [type(x).__name__ for x in block.parts()] == ["RMSNorm", "PagedAttention", "RMSNorm", "GatedMLP"]
     w = {}
-    for i, part in enumerate((mixer, ff, n1, n2)):
+    for i, part in enumerate(block.parts()):
         for k, v in random_params(part, 10 + i, dtype).items():
             w[f"{part.spec.prefix}.{k}"] = v
-    block = BLOCKS.get("prenorm")(mixer, ff, n1, n2)
     manager = CacheManager([mixer.cache_spec()], [None], page_size=16, num_pages=8, max_seqs=2, dtype=dtype, device="cuda")
     seq = manager.open("s")
     manager.reserve(seq, 50)
