@@ -54,6 +54,8 @@ class EngineConfig:
     cuda_graphs: bool = True
     #: queue each scheduler round before the previous round's tokens are read
     lookahead: bool = True
+    #: wrap scheduler rounds and model steps in NVTX ranges (for a timeline profiler)
+    nvtx: bool = False
 
     def __post_init__(self):
         object.__setattr__(self, "dtype", dtype_name(self.dtype))
@@ -81,7 +83,7 @@ class EngineConfig:
         if self.kv_dtype is not None and self.kv_dtype != self.dtype:
             raise EngineConfigError(f"engine option 'kv_dtype' ({self.kv_dtype}) must equal 'dtype' ({self.dtype}): "
                                     f"cache pages are read by the attention kernels as they are stored")
-        for name in ("cuda_graphs", "lookahead"):
+        for name in ("cuda_graphs", "lookahead", "nvtx"):
             if not isinstance(getattr(self, name), bool):
                 raise EngineConfigError(f"engine option '{name}' must be true or false, got {getattr(self, name)!r}")
 

@@ -104,7 +104,16 @@ class Engine:
         token being chosen within each wanted request (the sampler's draw depends on it).  The chosen tokens stay
         on the device (``runner.sampled``, row i for ``wanted[i]``), where the next step's entries with a
         ``source`` find them, and travel to a pinned host buffer that :meth:`collect` reads."""
-        logits = self.runner.step(entries)
+        if self.config.nvtx:
+            decode = sum(1 for e in entries if len(e.tokens) == 1)
+            torch.cuda.nvtx.range_push(f"step: decode_tokens={decode} prompt_tokens="
+                                       f"{sum(len(e.tokens) for e in entries) - decode} seqs={len(entries)}")
+            try:
+                logits = self.runner.step(entries)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        else:
+            logits = self.runner.step(entries)
         if logits is None:
             return None
         tokens = self.sampler.sample(logits, [r.sampling for r in wanted], steps)
@@ -140,7 +149,8 @@ class Engine:
     def new_scheduler(self, **overrides) -> Scheduler:
         options = dict(max_batch_tokens=self.max_batch_tokens, max_seqs=self.max_seqs,
                        eos_token_ids=self.eos_token_ids, admission=self.admission,
-                       max_context=self.config.max_context, lookahead=self.config.lookahead)
+                       max_context=self.config.max_context, lookahead=self.config.lookahead,
+                       nvtx=self.config.nvtx)
         options.update(overrides)
         return Scheduler(self, **options)
 

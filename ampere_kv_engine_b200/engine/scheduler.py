@@ -66,6 +66,26 @@ class Request:
         self.preemptions = 0
         self.admit_order = -1
         self.inflight_row: int | None = None    # row of this request's newest token in the round not yet read
+        #: host clock (time.perf_counter) at submit and at every token's arrival on the host; kept only when the
+        #: scheduler records times
+        self.submitted_at: float | None = None
+        self.token_times: list[float] = []
+
+    @property
+    def ttft_ms(self) -> float | None:
+        """Submit to first token on the host, as the reference's request timings count it (ampere_kv/runner.py:385-405)."""
+        if self.submitted_at is None or not self.token_times:
+            return None
+        return (self.token_times[0] - self.submitted_at) * 1000
+
+    @property
+    def largest_gap_ms(self) -> float | None:
+        """The longest wait between two consecutive tokens of this request: what a running request feels when a
+        prompt arrives beside it (the reference's scheduler benchmark reports the same,
+        ampere_kv/bench_scheduler.py:242-271)."""
+        if len(self.token_times) < 2:
+            return None
+        return max(b - a for a, b in zip(self.token_times, self.token_times[1:])) * 1000
 
     @property
     def tokens(self) -> list[int]:
@@ -93,7 +113,7 @@ class StepStats:
 class Scheduler:
     def __init__(self, executor, *, max_batch_tokens: int = 2048, max_seqs: int = 256,
                  eos_token_ids=(), admission: str = "budget", max_context: int | None = None,
-                 lookahead: bool | None = None):
+                 lookahead: bool | None = None, record_times: bool = False, nvtx: bool = False):
         if max_batch_tokens < 1 or max_seqs < 1:
             raise ValueError("max_batch_tokens and max_seqs must be positive")
         if admission not in ("budget", "optimistic"):
@@ -116,6 +136,12 @@ class Scheduler:
         self.lookahead = can_look_ahead if lookahead is None else bool(lookahead) and can_look_ahead
         self._inflight = None       # (handle, wanted requests) of the queued round whose tokens are not read yet
         self.dropped_tokens = 0     # speculative tokens of requests that had already ended
+        #: keep the host time of every submit and every token (``Request.ttft_ms`` / ``largest_gap_ms``)
+        self.record_times = bool(record_times)
+        #: wrap every round in an NVTX range that names what it holds, as the reference's profiling run does
+        #: (ampere_kv/bench_external.py:82-126); needs a CUDA build of torch, costs a few microseconds a round
+        self.nvtx = bool(nvtx)
+        self.rounds = 0
 
     # ------------------------------------------------------------------ public
 
@@ -136,6 +162,8 @@ class Scheduler:
                              f"maximum context of {self.max_context}")
         request = Request(request_id, prompt, max_new_tokens, sampling or SamplingParams(), ignore_eos, deadline)
         request.budget = self._budget(total)
+        if self.record_times:
+            request.submitted_at = time.perf_counter()
         for need, group in zip(request.budget, self.manager.groups):
             if need > group.pool.count:
                 raise ValueError(f"the request needs up to {need} pages of cache group {group.index}, "
@@ -153,6 +181,18 @@ class Scheduler:
 
     def step(self, now: float | None = None) -> tuple[list[Request], StepStats]:
         """One round.  Returns the requests that finished in it (each exactly once) and what ran."""
+        self.rounds += 1
+        if not self.nvtx:
+            return self._round(now)
+        import torch
+        torch.cuda.nvtx.range_push(f"round {self.rounds}: running={len(self.running)} prefilling={len(self.prefilling)} "
+                                   f"waiting={len(self.waiting)}")
+        try:
+            return self._round(now)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    def _round(self, now: float | None = None) -> tuple[list[Request], StepStats]:
         now = time.monotonic() if now is None else now
         finished = self._stop_round(now)
         self._admit()
@@ -320,6 +360,8 @@ class Scheduler:
 
     def _commit(self, request: Request, token: int) -> None:
         request.output_ids.append(token)
+        if self.record_times:
+            request.token_times.append(time.perf_counter())
         if len(request.output_ids) >= request.max_new_tokens:
             request.stop_reason = "length"
         elif token in self.eos_ids and not request.ignore_eos:

@@ -36,6 +36,14 @@ QWEN3_8B = {
     "rms_norm_eps": 1e-6, "max_position_embeddings": 40960, "tie_word_embeddings": False,
     "hidden_act": "silu", "attention_bias": False,
 }
+# BASELINE.json configs[3] and [4]: the further sizes (`--shape 14b|32b`), each with its own workload
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+SHAPES = {"8b": QWEN3_8B, "14b": QWEN3_14B, "32b": QWEN3_32B}
+LONG_CONTEXT = 32768    # 32b: decode at batch 16 with prompts of this many tokens ...
+LONG_BATCH = 16
+LONG_CHUNK = 2048       # ... prefilled in portions of this many
+SERVING_CONTEXT_14B = 16384
 CONTEXT = 8192          # the engine's context limit in this run
 PROMPT_LEN = 1024       # decode starts from 1,024-token prompts
 GEN_LEN = 256
@@ -272,6 +280,174 @@ def reference_arm(args) -> int:
         return 0
 
 
+def serving_load(engine, synthetic, num_requests, prompt_range, output_range, seed=7) -> dict:
+    """A scheduler load: many requests of mixed lengths, chunked prefill beside decoding, host tokens in and out.
+    Two passes; the second is timed (the decode graphs of its batch sizes exist by then).  Throughput by the wall
+    clock, and per request the time to its first token and its longest wait between two tokens."""
+    import random
+    import torch
+    rng = random.Random(seed)
+    lengths = [(rng.randint(*prompt_range), rng.randint(*output_range)) for _ in range(num_requests)]
+    for timed_pass in (False, True):
+        scheduler = engine.new_scheduler(record_times=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        requests = [scheduler.submit(f"s{i}", synthetic(n_in), n_out, ignore_eos=True)
+                    for i, (n_in, n_out) in enumerate(lengths)]
+        while scheduler.has_work():
+            scheduler.step()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        assert all(len(r.output_ids) == n_out for r, (_, n_out) in zip(requests, lengths))
+    ttft = sorted(r.ttft_ms for r in requests)
+    gaps = sorted(r.largest_gap_ms for r in requests if r.largest_gap_ms is not None)
+    return {"serving_requests": num_requests,
+            "serving_output_tok_s": round(sum(n for _, n in lengths) / wall, 1),
+            "serving_total_tok_s": round(sum(a + b for a, b in lengths) / wall, 1),
+            "serving_rounds": scheduler.rounds,
+            "serving_ttft_ms_median": round(ttft[len(ttft) // 2], 1), "serving_ttft_ms_max": round(ttft[-1], 1),
+            "serving_largest_gap_ms_median": round(gaps[len(gaps) // 2], 2),
+            "serving_largest_gap_ms_max": round(gaps[-1], 2)}
+
+
+def insert_point(engine, synthetic, batch, prompt_len=PROMPT_LEN, insert_len=PREFILL_TOKENS) -> dict:
+    """``batch`` requests decode; a prompt of ``insert_len`` tokens arrives.  Its time to the first token, the
+    longest token-to-token wait of the running requests while it is prefilled, and their usual one."""
+    import torch
+    scheduler = engine.new_scheduler(record_times=True)
+    running = [scheduler.submit(f"i{i}", synthetic(prompt_len), 96, ignore_eos=True) for i in range(batch)]
+    while any(len(r.output_ids) < 24 for r in running):
+        scheduler.step()
+    torch.cuda.synchronize()
+    newcomer = scheduler.submit("newcomer", synthetic(insert_len), 4, ignore_eos=True)
+    while scheduler.has_work():
+        scheduler.step()
+    gaps = sorted(b - a for r in running for a, b in zip(r.token_times[8:], r.token_times[9:]))
+    return {"insert_prompt_tokens": insert_len, "insert_ttft_ms": round(newcomer.ttft_ms, 2),
+            "insert_running_gap_ms_max": round(max(r.largest_gap_ms for r in running), 2),
+            "insert_running_gap_ms_median": round(gaps[len(gaps) // 2] * 1000, 3)}
+
+
+def _shape_setup(args, shape_cfg, *, pool_tokens, max_seqs, max_context):
+    import torch
+    from ampere_kv_engine_b200.config.engine_config import EngineConfig
+    from ampere_kv_engine_b200.engine.engine import Engine
+    cfg = dict(shape_cfg)
+    cfg["num_hidden_layers"] = args.layers
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    engine = Engine.from_random(cfg, seed=0, device=device, config=EngineConfig(
+        dtype="bfloat16", page_size=args.page_size, max_tokens=pool_tokens, max_seqs=max_seqs,
+        max_batch_tokens=PREFILL_TOKENS, max_context=max_context))
+    gen = torch.Generator().manual_seed(1234)
+    vocab = cfg["vocab_size"]
+    return cfg, engine, (lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist())
+
+
+def _shape_config(cfg, args, full_layers, **more) -> dict:
+    out = {"layers": args.layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
+           "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+           "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": args.page_size,
+           "kv_dtype": "bf16", "parallelism": "single GPU"}
+    out.update(more)
+    return out
+
+
+def serving_shape(args) -> int:
+    """Qwen3-14B sizes: 64 requests, prompts of 128 to 4,096 tokens, 128 to 512 new tokens each, rounds of at most
+    2,048 tokens, 16,384 positions of context.  ``value`` is generated tokens per second of the whole load."""
+    pool = SERVING_REQUESTS * (SERVING_PROMPT[1] + SERVING_OUTPUT[1]) // 2 + SERVING_REQUESTS * 64
+    cfg, engine, synthetic = _shape_setup(args, QWEN3_14B, pool_tokens=pool, max_seqs=SERVING_REQUESTS + 2,
+                                          max_context=SERVING_CONTEXT_14B)
+    with ClockSampler() as clocks:
+        serving = serving_load(engine, synthetic, SERVING_REQUESTS, SERVING_PROMPT, SERVING_OUTPUT)
+    line = {"metric": "generated tok/s of a mixed scheduler load (Qwen3-14B shape, B200)",
+            "value": serving["serving_output_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic (seeded uniform token ids, seeded random weights)",
+            "config": _shape_config(cfg, args, QWEN3_14B["num_hidden_layers"], model="Qwen3-14B shape",
+                                    requests=SERVING_REQUESTS, prompt_tokens="128-4096", new_tokens="128-512",
+                                    max_batch_tokens=PREFILL_TOKENS, seq_len=SERVING_CONTEXT_14B),
+            "points": serving, "clocks": clocks.summary()}
+    print(json.dumps(line))
+    return 0
+
+
+def long_context_shape(args) -> int:
+    """Qwen3-32B sizes: 16 requests with 32,768-token prompts, prefilled in portions of 2,048 tokens, then decoded
+    together.  At full depth the 16 caches (8.6 GB each) do not fit beside the weights: admission by page budget
+    lets as many in as the pool holds and the rest wait; ``value`` is decode tokens per second of the live batch,
+    with the bytes it must read over its time as the roofline fraction."""
+    import torch
+    from ampere_kv_engine_b200.engine.batch import SeqStep
+    from ampere_kv_engine_b200.sampling.sampler import SamplingParams
+    cfg = dict(QWEN3_32B)
+    cfg["num_hidden_layers"] = args.layers
+    peaks = load_peaks()
+    numbers = model_numbers(cfg, args.layers)
+    weight_bytes = 2.0 * (args.layers * numbers["layer_params"] + 2 * numbers["head_params"])
+    free_bytes = torch.cuda.mem_get_info(0)[0]
+    # every request decodes beside the later ones' prompt portions, so it needs room for those tokens too
+    new_tokens = LONG_BATCH * (LONG_CONTEXT // LONG_CHUNK + 1) + args.warmup + args.steps + 8
+    per_request = (LONG_CONTEXT + new_tokens + 64) * numbers["kv_bytes_per_token"]
+    room = free_bytes - weight_bytes - 12 * 2 ** 30          # activations of a 2,048-token portion, logits, slack
+    live = int(max(1, min(LONG_BATCH, room // per_request)))
+    cfg, engine, synthetic = _shape_setup(args, QWEN3_32B, pool_tokens=live * (LONG_CONTEXT + new_tokens + 64),
+                                          max_seqs=LONG_BATCH + 2, max_context=LONG_CONTEXT + new_tokens)
+    runner = engine.runner
+    # through the scheduler: all 16 are submitted, the page budget admits `live` of them, the rest wait
+    scheduler = engine.new_scheduler(record_times=True)
+    requests = [scheduler.submit(f"L{i}", synthetic(LONG_CONTEXT), new_tokens, ignore_eos=True)
+                for i in range(LONG_BATCH)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    prefill_rounds = 0
+    while scheduler.prefilling or not scheduler.running:
+        scheduler.step()
+        prefill_rounds += 1
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    admitted = sum(1 for r in requests if r.seq is not None)
+    waiting = len(scheduler.waiting)
+    for _ in range(args.warmup):
+        scheduler.step()
+    with ClockSampler() as clocks:
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        t0 = time.perf_counter()
+        stats = None
+        for _ in range(args.steps):
+            _, stats = scheduler.step()
+        stop.record()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1000 / args.steps
+        ms = start.elapsed_time(stop) / args.steps
+    batch = stats.decode_tokens
+    assert stats.prefill_tokens == 0 and batch == admitted
+    mean_ctx = sum(r.seq.length for r in requests if r.seq is not None) / batch - args.steps / 2
+    bytes_step = decode_bytes(cfg, args.layers, batch, mean_ctx)
+    achieved = bytes_step / (ms / 1000) / 1e9
+    for r in requests:
+        scheduler.cancel(r)
+    scheduler.step()
+    line = {"metric": "decode tok/s at batch 16 with 32,768-token prompts (Qwen3-32B shape, B200)",
+            "value": round(batch / (ms / 1000), 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)",
+            "config": _shape_config(cfg, args, QWEN3_32B["num_hidden_layers"], model="Qwen3-32B shape",
+                                    global_batch=LONG_BATCH, live_batch=batch, waiting_for_pages=waiting,
+                                    mean_decode_context=round(mean_ctx, 1),
+                                    seq_len=LONG_CONTEXT, prefill_chunk=LONG_CHUNK),
+            "e2e": {"value": round(batch / (e2e_ms / 1000), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4)},
+            "prefill": {"tokens": admitted * LONG_CONTEXT, "seconds": round(prefill_s, 2), "rounds": prefill_rounds,
+                        "value": round(live * LONG_CONTEXT / prefill_s, 1)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
+            "clocks": clocks.summary()}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -279,13 +455,21 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a power of two, 16 or more)")
-    parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
-                        help="run fewer layers of the same sizes (reported in config)")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b",
+                        help="8b: the headline benchmark; 14b: a mixed scheduler load of 64 requests; 32b: long-context "
+                             "decode at batch 16 (each prints its own one line)")
+    parser.add_argument("--layers", type=int, default=None,
+                        help="run fewer layers of the same sizes (reported in config beside the full count)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     args = parser.parse_args()
 
+    if args.layers is None:
+        args.layers = SHAPES[args.shape]["num_hidden_layers"]
     if args.impl == "reference":
+        if args.shape != "8b":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 8b shape only"}))
+            return 0
         if args.gpus != 1:
             print(json.dumps({"impl": "reference", "unavailable": "the reference runs on one GPU; --gpus must be 1"}))
             return 0
@@ -295,6 +479,10 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.shape == "14b":
+        return serving_shape(args)
+    if args.shape == "32b":
+        return long_context_shape(args)
 
     import torch
     from ampere_kv_engine_b200.engine.batch import SeqStep
@@ -312,8 +500,10 @@ def main() -> int:
                       max(args.batch * (CONTEXT + 64), SERVING_REQUESTS * (SERVING_PROMPT[1] + SERVING_OUTPUT[1]) // 2
                           + SERVING_REQUESTS * 64) if not args.no_points else 0,
                       PREFILL_TOKENS + 64)
-    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", device=device, page_size=args.page_size,
-                                max_tokens=pool_tokens, max_seqs=max_batch + 2, max_batch_tokens=PREFILL_TOKENS)
+    from ampere_kv_engine_b200.config.engine_config import EngineConfig
+    engine = Engine.from_random(cfg, seed=0, device=device, config=EngineConfig(
+        dtype="bfloat16", page_size=args.page_size, max_tokens=pool_tokens, max_seqs=max_batch + 2,
+        max_batch_tokens=PREFILL_TOKENS, max_context=CONTEXT))
     runner = engine.runner
     gen = torch.Generator().manual_seed(1234)
     vocab = cfg["vocab_size"]
@@ -425,23 +615,12 @@ def main() -> int:
             decode_bytes(cfg, args.layers, args.batch, long_ctx) / (p_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)
         # a scheduler load: many requests of mixed lengths, chunked prefill beside decoding, host tokens in and out
         # (second pass timed: the decode graphs of its batch sizes exist by then); tokens per second of wall clock
-        import random
-        rng = random.Random(7)
-        lengths = [(rng.randint(*SERVING_PROMPT), rng.randint(*SERVING_OUTPUT)) for _ in range(SERVING_REQUESTS)]
-        for timed_pass in (False, True):
-            scheduler = engine.new_scheduler()
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            requests = [scheduler.submit(f"s{i}", synthetic(n_in), n_out, ignore_eos=True)
-                        for i, (n_in, n_out) in enumerate(lengths)]
-            while scheduler.has_work():
-                scheduler.step()
-            torch.cuda.synchronize()
-            wall = time.perf_counter() - t0
-            assert all(len(r.output_ids) == n_out for r, (_, n_out) in zip(requests, lengths))
-        points["serving_requests"] = SERVING_REQUESTS
-        points["serving_output_tok_s"] = round(sum(n for _, n in lengths) / wall, 1)
-        points["serving_total_tok_s"] = round(sum(a + b for a, b in lengths) / wall, 1)
+        serving = serving_load(engine, synthetic, SERVING_REQUESTS, SERVING_PROMPT, SERVING_OUTPUT)
+        points.update(serving)
+        # a prompt arrives while the batch decodes: what the newcomer waits for its first token and what the
+        # running requests feel meanwhile (the figures of the reference's scheduler benchmark,
+        # ampere_kv/bench_scheduler.py:115-125, 242-271)
+        points.update(insert_point(engine, synthetic, args.batch))
 
     line = {
         "metric": "decode tok/s at batch 8 (Qwen3-8B shape, B200); prefill and batch 1/64 alongside",

@@ -394,3 +394,29 @@ def test_kernel_status_becomes_an_error_and_is_cleared(fake_ext):
     with pytest.raises(KernelStatusError, match="bounded wait"):
         scheduler.step()
     assert int(runner.status.item()) == 0
+
+
+def test_recorded_times_give_ttft_and_the_largest_gap():
+    """With ``record_times`` every request keeps its submit time and the arrival of each token: the time to the
+    first token and the longest wait between two tokens (what a running request feels when a prompt arrives)."""
+    import time as clock
+    ex = StubExecutor()
+    real_execute = ex.execute
+
+    def execute(entries, wanted):
+        if len(ex.batches) == 3:           # one slow round in the middle of the decoding
+            clock.sleep(0.03)
+        return real_execute(entries, wanted)
+    ex.execute = execute
+    s = Scheduler(ex, max_batch_tokens=64, record_times=True)
+    a = s.submit("a", list(range(1, 9)), 6, ignore_eos=True)
+    while s.has_work():
+        s.step()
+    assert len(a.token_times) == 6 and a.submitted_at is not None
+    assert a.ttft_ms is not None and a.ttft_ms >= 0
+    assert a.largest_gap_ms >= 25                      # the slow round shows as the largest gap
+    plain = Scheduler(StubExecutor(), max_batch_tokens=64)
+    b = plain.submit("b", [1, 2, 3], 2, ignore_eos=True)
+    while plain.has_work():
+        plain.step()
+    assert b.token_times == [] and b.ttft_ms is None and b.largest_gap_ms is None
