@@ -8,10 +8,15 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+#include <pybind11/stl.h>
 
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "launchers.h"
+
+namespace py = pybind11;
 
 namespace {
 
@@ -393,6 +398,136 @@ void small_m_gemm_qkv(const OptTensor& x, const Tensor& w, Tensor& q_out, const 
                "small_m_gemm_qkv");
 }
 
+// A chain of products in one persistent kernel (launchers.h: launch_stream_phases).  `phases` is a list of dicts:
+//   w [features, k] bfloat16; x [tokens, k] bfloat16 or None with norm_weight [k] float32 and eps (the token operand
+//   is then the RMS norm of `hidden`); epilogue: "residual" (adds into hidden), "gated" (out [tokens, features / 2]),
+//   "plain" (out [tokens, features]) or "qkv" (q_out, positions, slots, q_weight, k_weight, inv_freq, k_cache,
+//   v_cache, num_heads, num_kv_heads, qk_eps: the arguments of small_m_gemm_qkv).
+// ssq [ceil(hidden / 128), tokens] float32 scratch; parts and sync as stream_phases_scratch says, sync zeroed.
+akv::StreamPhase parse_stream_phase(const py::dict& d, const Tensor& hidden, int64_t tokens, bool full_check) {
+  akv::StreamPhase ph = {};
+  const Tensor w = d["w"].cast<Tensor>();
+  check_cuda(w, "w");
+  AKV_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.device() == hidden.device(),
+            "a phase's w must be a bfloat16 matrix on hidden's device");
+  ph.w = w.data_ptr();
+  ph.features = w.size(0);
+  ph.k = w.size(1);
+  AKV_CHECK(reinterpret_cast<uintptr_t>(ph.w) % 16 == 0 && ph.k % 8 == 0 && ph.k >= 64,
+            "a phase's w must be 16-byte aligned with k a multiple of 8, at least 64");
+  const std::string epilogue = d["epilogue"].cast<std::string>();
+  if (d.contains("x") && !d["x"].is_none()) {
+    const Tensor x = d["x"].cast<Tensor>();
+    check_cuda(x, "x");
+    AKV_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(0) == tokens && x.size(1) == ph.k &&
+                  x.device() == hidden.device() && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0,
+              "a phase's x must be bfloat16 [tokens, k], 16-byte aligned, on hidden's device");
+    ph.x_kind = akv::kStreamXTensor;
+    ph.x = x.data_ptr();
+  } else {
+    const Tensor nw = d["norm_weight"].cast<Tensor>();
+    check_f32(nw, "norm_weight", ph.k);
+    AKV_CHECK(ph.k == hidden.size(1) && reinterpret_cast<uintptr_t>(nw.data_ptr()) % 16 == 0,
+              "a normed token operand has the residual stream's width and a 16-byte aligned weight");
+    ph.x_kind = akv::kStreamXNormed;
+    ph.norm_weight = nw.data_ptr<float>();
+    ph.eps = d["eps"].cast<float>();
+  }
+  if (epilogue == "residual") {
+    ph.epilogue = akv::kEpilogueResidual;
+    AKV_CHECK(ph.features == hidden.size(1), "a residual phase has as many features as the residual stream");
+  } else if (epilogue == "gated" || epilogue == "plain") {
+    ph.epilogue = epilogue == "gated" ? akv::kEpilogueGated : akv::kEpiloguePlain;
+    Tensor out = d["out"].cast<Tensor>();
+    check_cuda(out, "out");
+    const int64_t width = epilogue == "gated" ? ph.features / 2 : ph.features;
+    AKV_CHECK(out.scalar_type() == at::kBFloat16 && out.numel() == tokens * width && out.device() == hidden.device(),
+              "a phase's out must be bfloat16 [tokens, ", width, "] on hidden's device");
+    AKV_CHECK(epilogue != "gated" || ph.features % 128 == 0, "a gated phase needs features in whole tiles of 128");
+    ph.out = out.data_ptr();
+  } else if (epilogue == "qkv") {
+    ph.epilogue = akv::kEpilogueQkv;
+    akv::GemmQkv& e = ph.qkv;
+    e.num_heads = d["num_heads"].cast<int>();
+    e.num_kv_heads = d["num_kv_heads"].cast<int>();
+    e.eps = d["qk_eps"].cast<float>();
+    AKV_CHECK(e.num_heads > 0 && e.num_kv_heads > 0 && ph.features == (int64_t)(e.num_heads + 2 * e.num_kv_heads) * 128,
+              "a qkv phase's w holds (heads + 2 kv_heads) heads of 128 rows each");
+    Tensor q_out = d["q_out"].cast<Tensor>();
+    check_cuda(q_out, "q_out");
+    AKV_CHECK(q_out.scalar_type() == at::kBFloat16 && q_out.numel() == tokens * e.num_heads * 128 &&
+                  q_out.device() == hidden.device(), "q_out must be bfloat16 [tokens, heads * 128]");
+    e.q_out = q_out.data_ptr();
+    const Tensor positions = d["positions"].cast<Tensor>();
+    check_i32(positions, "positions", tokens);
+    e.positions = positions.data_ptr<int>();
+    auto opt = [&](const char* key) -> OptTensor {
+      if (!d.contains(key) || d[key].is_none()) return c10::nullopt;
+      return d[key].cast<Tensor>();
+    };
+    const OptTensor slots = opt("slots"), qw = opt("q_weight"), kw = opt("k_weight"), freq = opt("inv_freq");
+    const OptTensor k_cache = opt("k_cache"), v_cache = opt("v_cache");
+    if (slots.has_value()) { check_i32(*slots, "slots", tokens); e.slots = slots->data_ptr<int>(); }
+    if (qw.has_value()) { check_f32(*qw, "q_weight", 128); e.q_weight = qw->data_ptr<float>(); }
+    if (kw.has_value()) { check_f32(*kw, "k_weight", 128); e.k_weight = kw->data_ptr<float>(); }
+    if (freq.has_value()) { check_f32(*freq, "inv_freq", 64); e.inv_freq = freq->data_ptr<float>(); }
+    AKV_CHECK(k_cache.has_value() == v_cache.has_value(), "k_cache and v_cache come together");
+    if (k_cache.has_value()) {
+      AKV_CHECK(slots.has_value(), "a cache to write needs slots");
+      const CacheGeometry g = check_cache(*k_cache, *v_cache, e.num_kv_heads, 128, q_out);
+      e.k_cache = k_cache->data_ptr();
+      e.v_cache = v_cache->data_ptr();
+      e.num_pages = g.num_pages;
+      e.page_size = g.page_size;
+    }
+  } else {
+    AKV_CHECK(false, "unknown epilogue '", epilogue, "' (residual, gated, plain, qkv)");
+  }
+  (void)full_check;
+  return ph;
+}
+
+void stream_phases(Tensor& hidden, const py::list& phases, Tensor& ssq, Tensor& parts, Tensor& sync,
+                   const OptTensor& status) {
+  check_cuda(hidden, "hidden");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2 && hidden.is_contiguous(),
+            "hidden must be a contiguous float32 [tokens, hidden] tensor");
+  const int64_t tokens = hidden.size(0), width = hidden.size(1);
+  AKV_CHECK(tokens >= 1 && tokens <= 16, "stream_phases takes 1 to 16 tokens, got ", tokens);
+  const int64_t n = (int64_t)phases.size();
+  AKV_CHECK(n >= 1 && n <= akv::kMaxStreamPhases, "stream_phases takes 1 to ", akv::kMaxStreamPhases, " phases, got ", n);
+  akv::StreamPhase list[akv::kMaxStreamPhases];
+  for (int64_t i = 0; i < n; ++i) list[i] = parse_stream_phase(phases[i].cast<py::dict>(), hidden, tokens, true);
+  int64_t part_floats = 0, sync_ints = 0;
+  akv::stream_phases_scratch(list, (int)n, &part_floats, &sync_ints);
+  check_f32(ssq, "ssq");
+  check_f32(parts, "parts");
+  check_i32(sync, "sync");
+  AKV_CHECK(ssq.numel() >= (width + 127) / 128 * tokens, "ssq must hold ceil(hidden / 128) * tokens floats");
+  AKV_CHECK(parts.numel() >= part_floats, "parts must hold ", part_floats, " floats, has ", parts.numel());
+  AKV_CHECK(sync.numel() >= sync_ints, "sync must hold ", sync_ints, " ints, has ", sync.numel());
+  AKV_CHECK(ssq.device() == hidden.device() && parts.device() == hidden.device() && sync.device() == hidden.device(),
+            "scratch tensors must be on hidden's device");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_stream_phases(list, (int)n, tokens, hidden.data_ptr<float>(), width, ssq.data_ptr<float>(),
+                                         parts.data_ptr<float>(), sync.data_ptr<int>(), status_ptr(status),
+                                         stream_of(hidden)),
+               "stream_phases");
+}
+
+// (floats of partial tiles, ints of counters) a launch over matrices of the given (features, k) shapes needs.
+std::pair<int64_t, int64_t> stream_phases_scratch(const std::vector<std::pair<int64_t, int64_t>>& shapes) {
+  AKV_CHECK(!shapes.empty() && (int64_t)shapes.size() <= akv::kMaxStreamPhases, "1 to ", akv::kMaxStreamPhases, " shapes");
+  akv::StreamPhase list[akv::kMaxStreamPhases] = {};
+  for (size_t i = 0; i < shapes.size(); ++i) {
+    list[i].features = shapes[i].first;
+    list[i].k = shapes[i].second;
+  }
+  int64_t part_floats = 0, sync_ints = 0;
+  akv::stream_phases_scratch(list, (int)shapes.size(), &part_floats, &sync_ints);
+  return {part_floats, sync_ints};
+}
+
 void qk_norm_rope_write(const Tensor& qkv, const Tensor& positions, const OptTensor& slots,
                         const OptTensor& q_weight, const OptTensor& k_weight, const OptTensor& inv_freq,
                         Tensor& q_out, const OptTensor& k_out, const OptTensor& v_out, const OptTensor& k_cache,
@@ -596,6 +731,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("eps"), py::arg("splits") = 1,
         py::arg("status") = py::none(), py::arg("nx_hidden") = py::none(), py::arg("nx_ssq") = py::none(),
         py::arg("nx_weight") = py::none(), py::arg("nx_eps") = 0.0);
+  m.def("stream_phases", &stream_phases, py::arg("hidden"), py::arg("phases"), py::arg("ssq"), py::arg("parts"),
+        py::arg("sync"), py::arg("status") = py::none(),
+        "a chain of dependent products for up to 16 tokens in one persistent kernel");
+  m.def("stream_phases_scratch", &stream_phases_scratch, py::arg("shapes"));
+  m.def("stream_phases_max", []() { return (int64_t)akv::kMaxStreamPhases; });
   m.def("small_m_gemm_supported", &small_m_gemm_supported);
   m.def("small_m_gemm_splits", &small_m_gemm_splits);
   m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),

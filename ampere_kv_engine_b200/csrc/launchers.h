@@ -98,6 +98,32 @@ int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, 
                         int64_t features, int64_t k, int splits, const GemmFusion* fusion, int* status,
                         cudaStream_t stream);
 
+// A chain of weight-streaming products in one persistent kernel (stream_phases.cu): up to kMaxStreamPhases
+// products x W^T for at most 16 bfloat16 tokens, each depending on the one before, with the epilogues of
+// launch_small_m_gemm.  The token operand of a phase is a bfloat16 tensor, or the RMS norm of the float32 residual
+// stream `hidden` (its sums of squares come from the last residual phase of the launch, or are added up in the kernel
+// when there is none).
+constexpr int kMaxStreamPhases = 4;
+enum StreamX : int { kStreamXTensor = 0, kStreamXNormed = 1 };
+struct StreamPhase {
+  const void* w;             // [features, k] bfloat16
+  int64_t features, k;
+  int x_kind;                // StreamX
+  const void* x;             // kStreamXTensor: [tokens, k] bfloat16
+  const float* norm_weight;  // kStreamXNormed: [k]
+  float eps;
+  int epilogue;              // GemmEpilogue; kEpilogueResidual adds into `hidden` (features == hidden_size)
+  void* out;                 // plain: bfloat16 [tokens, features]; gated: bfloat16 [tokens, features / 2]
+  GemmQkv qkv;               // kEpilogueQkv
+};
+// CTAs the kernel runs with (one per SM), and the scratch a launch needs: float32 partial tiles and int32 counters
+// (the counters must be zero at launch).
+int stream_phases_grid();
+void stream_phases_scratch(const StreamPhase* phases, int num_phases, int64_t* part_floats, int64_t* sync_ints);
+int launch_stream_phases(const StreamPhase* phases, int num_phases, int64_t tokens, float* hidden,
+                         int64_t hidden_size, float* ssq, float* parts, int* sync, int* status,
+                         cudaStream_t stream);
+
 struct QkRopeWriteParams {
   const void* qkv;          // [N, (NH + 2 NKV) * D]; with qkv_parts > 0: float32 [qkv_parts, N, ...] partial sums
   int qkv_parts;

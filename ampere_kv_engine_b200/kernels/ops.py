@@ -399,3 +399,75 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
             out += bias.to(out_dtype)
         return out
     return torch.nn.functional.linear(x, weight, bias)
+
+
+# ----------------------------------------------------------------------------- chains of products in one kernel
+
+#: a decode step of at most this many bfloat16 tokens runs the tail of each layer and the head of the next (output
+#: projection, gate/up, down, the next q/k/v projection) as ONE persistent kernel that never stops streaming weights
+STREAM_LIMIT = 8
+use_stream_phases = True
+_STREAM_SYNC_INTS = 1 << 16
+
+
+class _StreamScratch:
+    """Per device: sums of squares, partial tiles and zeroed counters of the chained-product kernel.  The counters
+    are handed out slice by slice and zeroed again at the start of every step (``stream_begin_step``)."""
+
+    def __init__(self, device):
+        self.device = device
+        self.ssq = torch.empty((1,), dtype=torch.float32, device=device)
+        self.parts = torch.empty((1,), dtype=torch.float32, device=device)
+        self.sync = torch.zeros((_STREAM_SYNC_INTS,), dtype=torch.int32, device=device)
+        self.cursor = 0
+        self.dirty = False
+
+
+_STREAM_SCRATCH: dict = {}
+
+
+def _stream_scratch(device) -> _StreamScratch:
+    key = torch.device(device)
+    if key not in _STREAM_SCRATCH:
+        _STREAM_SCRATCH[key] = _StreamScratch(key)
+    return _STREAM_SCRATCH[key]
+
+
+def stream_begin_step(device) -> None:
+    """Zero the counters the chained-product kernel used since the last call (one small memset, only if any were)."""
+    scratch = _STREAM_SCRATCH.get(torch.device(device))
+    if scratch is not None and scratch.dirty:
+        scratch.sync[:scratch.cursor].zero_()
+        scratch.cursor = 0
+        scratch.dirty = False
+
+
+def stream_phases(hidden: torch.Tensor, phases: list[dict], status: torch.Tensor | None = None) -> None:
+    """Run ``phases`` (1 to 4 products, each depending on the one before) on the float32 residual stream ``hidden``
+    [tokens <= 16, width] in one persistent kernel.  A phase is a dict: ``w`` [features, k] bfloat16; ``x``
+    [tokens, k] bfloat16, or ``norm_weight`` and ``eps`` for the RMS norm of ``hidden``; ``epilogue`` "residual" (adds
+    the product, rounded to bfloat16, into ``hidden``), "gated" (``out`` = silu(gate) * up over rows alternating in
+    runs of 64), "plain" (``out``) or "qkv" (the arguments of the fused q/k/v projection).  Outputs are written into
+    the tensors the phases name."""
+    scratch = _stream_scratch(hidden.device)
+    part_floats, sync_ints = ext().stream_phases_scratch([(int(p["w"].shape[0]), int(p["w"].shape[1])) for p in phases])
+    ssq_floats = (hidden.shape[1] + 127) // 128 * 16
+    if scratch.ssq.numel() < ssq_floats:
+        scratch.ssq = torch.empty((ssq_floats,), dtype=torch.float32, device=hidden.device)
+    if scratch.parts.numel() < part_floats:
+        scratch.parts = torch.empty((part_floats,), dtype=torch.float32, device=hidden.device)
+    if scratch.cursor + sync_ints > scratch.sync.numel():
+        raise RuntimeError("the chained-product kernel ran out of counters: stream_begin_step() was not called "
+                           "between steps")
+    sync = scratch.sync[scratch.cursor:scratch.cursor + sync_ints]
+    scratch.cursor += sync_ints
+    scratch.dirty = True
+    ext().stream_phases(hidden, phases, scratch.ssq, scratch.parts, sync, status)
+    _launched()
+
+
+def stream_takes(tokens: int, *weights: torch.Tensor) -> bool:
+    """Whether the chained-product kernel takes a step of ``tokens`` tokens over these matrices."""
+    return (use_stream_phases and 1 <= tokens <= STREAM_LIMIT and all(
+        w is not None and w.is_cuda and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous()
+        and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0 and w.shape[1] >= 64 for w in weights))
