@@ -488,7 +488,7 @@ akv::StreamPhase parse_stream_phase(const py::dict& d, const Tensor& hidden, int
 }
 
 void stream_phases(Tensor& hidden, const py::list& phases, Tensor& ssq, Tensor& parts, Tensor& sync,
-                   const OptTensor& status) {
+                   const OptTensor& status, const OptTensor& trace) {
   check_cuda(hidden, "hidden");
   AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2 && hidden.is_contiguous(),
             "hidden must be a contiguous float32 [tokens, hidden] tensor");
@@ -508,10 +508,18 @@ void stream_phases(Tensor& hidden, const py::list& phases, Tensor& ssq, Tensor& 
   AKV_CHECK(sync.numel() >= sync_ints, "sync must hold ", sync_ints, " ints, has ", sync.numel());
   AKV_CHECK(ssq.device() == hidden.device() && parts.device() == hidden.device() && sync.device() == hidden.device(),
             "scratch tensors must be on hidden's device");
+  unsigned long long* trace_ptr = nullptr;
+  if (trace.has_value()) {
+    check_cuda(*trace, "trace");
+    AKV_CHECK(trace->scalar_type() == at::kLong && trace->is_contiguous() &&
+                  trace->numel() >= (int64_t)akv::stream_phases_grid() * akv::kMaxStreamPhases * 16,
+              "trace must be int64 [grid, ", akv::kMaxStreamPhases, ", 16]");
+    trace_ptr = reinterpret_cast<unsigned long long*>(trace->data_ptr<int64_t>());
+  }
   c10::cuda::CUDAGuard guard(hidden.device());
   check_launch(akv::launch_stream_phases(list, (int)n, tokens, hidden.data_ptr<float>(), width, ssq.data_ptr<float>(),
                                          parts.data_ptr<float>(), sync.data_ptr<int>(), status_ptr(status),
-                                         stream_of(hidden)),
+                                         stream_of(hidden), trace_ptr),
                "stream_phases");
 }
 
@@ -732,10 +740,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("status") = py::none(), py::arg("nx_hidden") = py::none(), py::arg("nx_ssq") = py::none(),
         py::arg("nx_weight") = py::none(), py::arg("nx_eps") = 0.0);
   m.def("stream_phases", &stream_phases, py::arg("hidden"), py::arg("phases"), py::arg("ssq"), py::arg("parts"),
-        py::arg("sync"), py::arg("status") = py::none(),
+        py::arg("sync"), py::arg("status") = py::none(), py::arg("trace") = py::none(),
         "a chain of dependent products for up to 16 tokens in one persistent kernel");
   m.def("stream_phases_scratch", &stream_phases_scratch, py::arg("shapes"));
   m.def("stream_phases_max", []() { return (int64_t)akv::kMaxStreamPhases; });
+  m.def("stream_phases_grid", []() { return (int64_t)akv::stream_phases_grid(); });
   m.def("small_m_gemm_supported", &small_m_gemm_supported);
   m.def("small_m_gemm_splits", &small_m_gemm_splits);
   m.def("qk_norm_rope_write", &qk_norm_rope_write, py::arg("qkv"), py::arg("positions"), py::arg("slots"),

@@ -120,9 +120,11 @@ struct StreamPhase {
 // (the counters must be zero at launch).
 int stream_phases_grid();
 void stream_phases_scratch(const StreamPhase* phases, int num_phases, int64_t* part_floats, int64_t* sync_ints);
+// `trace` (null in production): int64 [grid, kMaxStreamPhases, 16] that receives nanosecond stamps of each CTA's
+// progress through each phase, for measurements.
 int launch_stream_phases(const StreamPhase* phases, int num_phases, int64_t tokens, float* hidden,
                          int64_t hidden_size, float* ssq, float* parts, int* sync, int* status,
-                         cudaStream_t stream);
+                         cudaStream_t stream, unsigned long long* trace = nullptr);
 
 struct QkRopeWriteParams {
   const void* qkv;          // [N, (NH + 2 NKV) * D]; with qkv_parts > 0: float32 [qkv_parts, N, ...] partial sums

@@ -10,6 +10,7 @@ fallback: without the extension these functions raise.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -403,10 +404,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 # ----------------------------------------------------------------------------- chains of products in one kernel
 
-#: a decode step of at most this many bfloat16 tokens runs the tail of each layer and the head of the next (output
+#: a decode step of at most this many bfloat16 tokens may run the tail of each layer and the head of the next (output
 #: projection, gate/up, down, the next q/k/v projection) as ONE persistent kernel that never stops streaming weights
 STREAM_LIMIT = 8
-use_stream_phases = True
+#: Off unless AKV_STREAM_PHASES=1: measured on B200 at the benchmark model's sizes the chain of a layer takes 105 us
+#: in the persistent kernel against 72 us as four kernels.  Its weights do stream at the memory's rate (0.36 us per
+#: 16 KB block per SM), but each of the three places where a phase needs the one before it finished everywhere costs
+#: 7 to 10 us (partial tiles through the L2, a ticket, the last sharer's sums, a counter, the operand built anew)
+#: against the 3.6 us of weights that the ring holds, where the four kernels reduce their K splits through
+#: distributed shared memory in about 2 us.  Asking the L2 for blocks ahead of the ring made it slower still.
+use_stream_phases = os.environ.get("AKV_STREAM_PHASES", "0") == "1"
 _STREAM_SYNC_INTS = 1 << 16
 
 
@@ -420,29 +427,40 @@ class _StreamScratch:
         self.parts = torch.empty((1,), dtype=torch.float32, device=device)
         self.sync = torch.zeros((_STREAM_SYNC_INTS,), dtype=torch.int32, device=device)
         self.cursor = 0
-        self.dirty = False
+        self.high_water = 0      # counters ever handed out: a replayed graph may have used them behind our back
 
 
 _STREAM_SCRATCH: dict = {}
 
 
+def _device_key(device) -> torch.device:
+    """``cuda`` and ``cuda:0`` name the same device: always the form with an index."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
+
+
 def _stream_scratch(device) -> _StreamScratch:
-    key = torch.device(device)
+    key = _device_key(device)
     if key not in _STREAM_SCRATCH:
         _STREAM_SCRATCH[key] = _StreamScratch(key)
     return _STREAM_SCRATCH[key]
 
 
 def stream_begin_step(device) -> None:
-    """Zero the counters the chained-product kernel used since the last call (one small memset, only if any were)."""
-    scratch = _STREAM_SCRATCH.get(torch.device(device))
-    if scratch is not None and scratch.dirty:
-        scratch.sync[:scratch.cursor].zero_()
+    """Zero every counter the chained-product kernel has ever been handed on this device (one small memset; nothing
+    before the kernel's first use).  Called at the start of every step, so a captured step carries its own."""
+    if not _STREAM_SCRATCH:
+        return
+    scratch = _STREAM_SCRATCH.get(_device_key(device))
+    if scratch is not None and scratch.high_water:
+        scratch.sync[:scratch.high_water].zero_()
         scratch.cursor = 0
-        scratch.dirty = False
 
 
-def stream_phases(hidden: torch.Tensor, phases: list[dict], status: torch.Tensor | None = None) -> None:
+def stream_phases(hidden: torch.Tensor, phases: list[dict], status: torch.Tensor | None = None,
+                  trace: torch.Tensor | None = None) -> None:
     """Run ``phases`` (1 to 4 products, each depending on the one before) on the float32 residual stream ``hidden``
     [tokens <= 16, width] in one persistent kernel.  A phase is a dict: ``w`` [features, k] bfloat16; ``x``
     [tokens, k] bfloat16, or ``norm_weight`` and ``eps`` for the RMS norm of ``hidden``; ``epilogue`` "residual" (adds
@@ -461,8 +479,8 @@ def stream_phases(hidden: torch.Tensor, phases: list[dict], status: torch.Tensor
                            "between steps")
     sync = scratch.sync[scratch.cursor:scratch.cursor + sync_ints]
     scratch.cursor += sync_ints
-    scratch.dirty = True
-    ext().stream_phases(hidden, phases, scratch.ssq, scratch.parts, sync, status)
+    scratch.high_water = max(scratch.high_water, scratch.cursor)
+    ext().stream_phases(hidden, phases, scratch.ssq, scratch.parts, sync, status, trace)
     _launched()
 
 
@@ -471,3 +489,53 @@ def stream_takes(tokens: int, *weights: torch.Tensor) -> bool:
     return (use_stream_phases and 1 <= tokens <= STREAM_LIMIT and all(
         w is not None and w.is_cuda and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous()
         and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0 and w.shape[1] >= 64 for w in weights))
+
+
+class PendingPhases:
+    """Products that are decided but not launched yet: the tail of one layer (output projection, feed-forward) waits
+    here for the head of the next (its q/k/v projection) so that all of them go into one launch of the
+    chained-product kernel.  Whoever needs the residual stream itself calls :meth:`launch` first."""
+
+    def __init__(self, hidden: torch.Tensor, status: torch.Tensor | None = None):
+        self.hidden, self.status = hidden, status
+        self.phases: list[dict] = []
+        self._max = None
+
+    def room(self, count: int = 1) -> bool:
+        if self._max is None:
+            self._max = int(ext().stream_phases_max())
+        return len(self.phases) + count <= self._max
+
+    def add(self, phase: dict) -> None:
+        if not self.room():
+            self.launch()
+        self.phases.append(phase)
+
+    def launch(self) -> None:
+        if self.phases:
+            stream_phases(self.hidden, self.phases, status=self.status)
+            self.phases = []
+
+
+class StreamNorm:
+    """An RMS norm of the residual stream that is not computed: the consumer adds a phase whose token operand the
+    chained-product kernel makes from the stream itself, after the phases queued before it."""
+
+    def __init__(self, pending: PendingPhases, weight: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.pending, self.weight, self.eps, self.dtype = pending, weight, float(eps), dtype
+
+    @property
+    def hidden(self) -> torch.Tensor:
+        return self.pending.hidden
+
+    @property
+    def shape(self):
+        return self.pending.hidden.shape
+
+    def normed_phase(self, w: torch.Tensor, **epilogue) -> dict:
+        return dict(w=w, norm_weight=self.weight, eps=self.eps, **epilogue)
+
+    def materialize(self) -> torch.Tensor:
+        """Launch what is queued and run the norm kernel after all."""
+        self.pending.launch()
+        return add_rmsnorm(self.pending.hidden, None, self.weight, self.eps, self.dtype, status=self.pending.status)

@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import ModelSpec
+from ..kernels import ops
 from ..parts import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, CacheSpec, ParamSpec, build_part
 
@@ -88,6 +89,7 @@ class DecoderModel:
     @torch.no_grad()
     def forward(self, ctx, cache_views) -> torch.Tensor | None:
         """Run the step's tokens through the schedule; logits [wanted, vocab] float32, or None if none wanted."""
+        ops.stream_begin_step(self.device)
         hidden = self.embedding.forward(ctx.token_ids, ctx)
         delta = None
         for pos, entry in enumerate(self.spec.schedule):

@@ -26,6 +26,7 @@ class PagedAttention(Mixer):
     graph_safe = True
     takes_lazy_norm = True
     adds_residual = True
+    takes_stream_norm = True
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
@@ -91,7 +92,25 @@ class PagedAttention(Mixer):
         k_cache = cache.k_cache if cache.writes else None
         v_cache = cache.v_cache if cache.writes else None
         fused = self.position_encoding.fused_rotary()
-        if fused is not None:
+        q = None
+        if isinstance(x, ops.StreamNorm):
+            # a few decoded tokens: the projection goes behind the products that are still queued (the layer
+            # before's output projection and feed-forward), all in one launch of the chained-product kernel
+            on_tile = (fused is not None and self.b_qkv is None and self.head_dim == 128
+                       and (fused[0] is None or fused[1] == 128) and ops.stream_takes(x.shape[0], self.w_qkv))
+            if on_tile:
+                q = torch.empty((x.shape[0], self.num_heads * 128), dtype=torch.bfloat16, device=self.w_qkv.device)
+                x.pending.add(x.normed_phase(
+                    self.w_qkv, epilogue="qkv", q_out=q, positions=ctx.positions, slots=slots,
+                    q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, inv_freq=fused[0], k_cache=k_cache,
+                    v_cache=v_cache, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+                    qk_eps=self.qk_norm_eps))
+                x.pending.launch()
+            else:
+                x = x.materialize()
+        if q is not None:
+            pass
+        elif fused is not None:
             inv_freq, rotary_dim = fused
             q = ops.project_qkv(
                 x, self.w_qkv, self.b_qkv, ctx.positions, slots, self.q_norm_weight, self.k_norm_weight, inv_freq,
@@ -128,6 +147,13 @@ class PagedAttention(Mixer):
                 ctx.tile_q0[lo:hi], ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits,
                 num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, window=self.window or 0, scale=self.scale,
                 status=ctx.status, out=out)
+        if residual is not None and self.b_o is None and ops.stream_takes(out.shape[0], self.w_o) \
+                and residual.dtype == torch.float32 and residual.is_contiguous() \
+                and residual.shape == (out.shape[0], self.w_o.shape[0]):
+            # queued, not launched: the feed-forward and the next layer's projection join it
+            pending = ops.PendingPhases(residual, ctx.status)
+            pending.add(dict(w=self.w_o, x=out, epilogue="residual"))
+            return pending
         if residual is not None and self.b_o is None:
             summed = ops.linear_into_residual(out, self.w_o, residual, status=ctx.status)
             if summed is not None:

@@ -114,6 +114,10 @@ class Norm(Part):
         (a split-K product) that are to be added together."""
         raise NotImplementedError
 
+    #: True when ``forward`` takes an ``ops.PendingPhases`` as ``delta`` with ``lazy=True`` and answers with an
+    #: ``ops.StreamNorm`` (or None if it cannot): the chained-product kernel then applies the norm
+    takes_pending = False
+
     #: True when ``forward`` also takes a ``Summed`` as ``delta`` (the branch's product kernel has already added
     #: its result to ``hidden`` and left the sums of squares) and a keyword ``lazy``: with ``lazy=True`` it may
     #: return a ``LazyNorm`` for a consumer with ``takes_lazy_norm``.  A norm without it is handed ``delta=None``
@@ -139,8 +143,12 @@ class Mixer(Part):
     #: the small-batch product kernel apply the norm).
     takes_lazy_norm = False
     #: ``forward`` accepts a keyword ``residual`` (the float32 residual stream): it may then add its output there
-    #: itself and return a ``Summed`` instead of the output.
+    #: itself and return a ``Summed`` instead of the output, or queue the product that adds it and return the
+    #: ``PendingPhases``.
     adds_residual = False
+    #: ``forward`` accepts an ``ops.StreamNorm`` as ``x``: it queues its first product behind the products that are
+    #: pending there and launches them together
+    takes_stream_norm = False
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec()
@@ -155,6 +163,7 @@ class Mixer(Part):
 class FeedForward(Part):
     takes_lazy_norm = False     # as for Mixer
     adds_residual = False
+    takes_stream_norm = False
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
@@ -223,6 +232,15 @@ class Block:
     def run_norm(norm: Norm, hidden, delta, ctx, consumer=None, rows=None):
         """``norm`` over ``hidden`` (+ ``delta``), lazily if ``delta`` is a ``Summed`` and both the norm and the
         consumer of its result know how."""
+        if isinstance(delta, ops.PendingPhases):
+            # products still queued for the chained-product kernel: a norm that knows how hands its consumer the
+            # not-yet-computed norm (the consumer queues its own product behind them); otherwise they run now
+            if rows is None and getattr(norm, "takes_pending", False) and getattr(consumer, "takes_stream_norm", False):
+                lazy = norm.forward(hidden, delta, ctx, rows=None, lazy=True)
+                if lazy is not None:
+                    return lazy
+            delta.launch()
+            return norm.forward(hidden, None, ctx, rows=rows)
         if isinstance(delta, ops.Summed):
             if not norm.takes_summed:
                 return norm.forward(hidden, None, ctx, rows=rows)

@@ -23,6 +23,7 @@ class GatedMLP(FeedForward):
     graph_safe = True
     takes_lazy_norm = True
     adds_residual = True
+    takes_stream_norm = True
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
@@ -52,6 +53,17 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, ctx, residual=None):
         status = getattr(ctx, "status", None)
+        if isinstance(x, ops.StreamNorm):
+            # a few decoded tokens: both products go behind the output projection that is still queued; whoever
+            # comes next (the next layer's q/k/v projection, or the final norm) launches them
+            if (residual is x.hidden and self.run == ops.GATE_UP_RUN and self.gate_up.shape[0] % 128 == 0
+                    and ops.stream_takes(x.shape[0], self.gate_up, self.down)):
+                act = torch.empty((x.shape[0], self.intermediate_size), dtype=torch.bfloat16,
+                                  device=self.gate_up.device)
+                x.pending.add(x.normed_phase(self.gate_up, epilogue="gated", out=act))
+                x.pending.add(dict(w=self.down, x=act, epilogue="residual"))
+                return x.pending
+            x = x.materialize()
         act = ops.gated_linear(x, self.gate_up, self.run, status=status)
         if residual is not None:
             summed = ops.linear_into_residual(act, self.down, residual, status=status)

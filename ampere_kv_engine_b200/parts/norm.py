@@ -35,9 +35,14 @@ class RMSNorm(Norm):
         self.weight = tensors["weight"]
 
     takes_summed = True
+    takes_pending = True
 
     def forward(self, hidden, delta, ctx, rows=None, lazy=False):
         status = getattr(ctx, "status", None)
+        if isinstance(delta, ops.PendingPhases):
+            if lazy and rows is None and self.size == hidden.shape[1] and self.weight.data_ptr() % 16 == 0:
+                return ops.StreamNorm(delta, self.weight, self.eps, self.dtype)
+            return None
         if isinstance(delta, ops.Summed):
             if lazy and rows is None and self.size == hidden.shape[1]:
                 return ops.LazyNorm(delta, self.weight, self.eps, self.dtype, status)

@@ -63,7 +63,7 @@ def make_case(tokens, hidden, inter, heads, kv_heads, seed, page=16):
 
 
 @pytest.mark.parametrize("tokens,hidden,inter,heads,kv_heads", [
-    (8, 4096, 12288, 32, 8), (1, 4096, 12288, 32, 8), (5, 512, 1152, 8, 2), (3, 320, 448, 3, 1), (16, 1024, 2048, 8, 8)])
+    (8, 4096, 12288, 32, 8), (1, 4096, 12288, 32, 8), (5, 512, 1152, 8, 2), (3, 320, 448, 3, 1), (7, 1024, 2048, 8, 8)])
 def test_chain_of_four_products_matches_float_arithmetic(tokens, hidden, inter, heads, kv_heads):
     from ampere_kv_engine_b200.kernels import ops
     cfg = {"eps": 1e-6, "qk_eps": 1e-5, "heads": heads, "kv_heads": kv_heads}
@@ -142,3 +142,30 @@ def test_single_phases_match_the_per_product_kernels():
     want = ops.linear(normed, w_plain)
     torch.testing.assert_close(out.float(), want.float(), atol=2e-2, rtol=2e-2)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_engine_with_the_chained_kernel_switched_on(name, monkeypatch):
+    """The whole engine with the option on (it is off by default: the four separate kernels are faster): decoded
+    tokens, portions of two and three tokens, mixed steps of up to eight tokens and captured decode graphs all take
+    the chained-product kernel, and every row must still equal the plain implementation's."""
+    import replay_util as ru
+    import tiny
+    from ampere_kv_engine_b200.kernels import ops
+    from models_util import model_folder, plain_logits
+    monkeypatch.setattr(ops, "use_stream_phases", True)
+    raw, page = tiny.CONFIGS[name]
+    folder = model_folder(name)
+    requests = ru.make_requests(raw["vocab_size"], (5, 17, 33, 70, 45), seed=11)
+    expected = plain_logits(folder, raw, requests, "bfloat16")
+    trace = ru.Trace()
+    for mode, sub in (("last", ru.trace_last_decoded(requests)), ("portions", ru.trace_portions(requests)),
+                      ("mixed", ru.trace_mixed(requests, 64 * 6, seed=5))):
+        trace.extend(sub, mode + ":")
+    wanted = {f"{mode}:{rid}": logits for mode in ("last", "portions", "mixed") for rid, logits in expected.items()}
+    before = ops.launch_count
+    outputs, engine = ru.run_on_device(folder, "bfloat16", trace, 64 * 6, page_size=page, max_seqs=8)
+    ru.compare(trace, outputs, wanted, "bfloat16")
+    assert engine.runner.graph_replays > 20
+    scratch = ops._stream_scratch("cuda")
+    assert scratch.high_water > 0          # the kernel did run
