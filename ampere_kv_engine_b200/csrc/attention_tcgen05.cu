@@ -1,6 +1,7 @@
 // Causal paged attention for prompt portions on the 5th-generation tensor cores (tcgen05), bfloat16, head
-// size 128.  One CTA owns 128 query rows = TQ tokens x G q-heads of one kv head (G = 2, 4 or 8) and walks the
-// keys 64 at a time:
+// size 128.  One CTA owns up to 128 query rows = TQ tokens x G q-heads of one kv head (any G from 1 to 16;
+// TQ = 128 / G rounded down, so a group of 5 fills 125 rows and the last three stay dead) and walks the keys 64 at
+// a time:
 //     S  = Q K^T          tcgen05.mma (M = 128, N = 64, K = 16 x 8), Q and K from shared memory, S in TMEM
 //     P  = softmax part   128 threads, one query row each: tcgen05.ld of the row, mask, running max and sum in
 //                         float32, P written to shared memory as bfloat16 in the swizzled operand layout
@@ -237,7 +238,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   if (warp == 4) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      bar_expect_tx(q_full, FaSmem::kQ);
+      // tq tokens x G heads: all 128 rows when G divides 128, else fewer (rows past them are dead: never live)
+      bar_expect_tx(q_full, 2u * (uint32_t)(fp.tq * G) * 128u);
       // rows of the tile in (token, head) order: box {64 dims, G heads, tq tokens} per 64-dim half
       tma_3d(q_smem, &q_map, 0, kvh * G, q0, q_full);
       tma_3d(q_smem + kRows * 128, &q_map, 64, kvh * G, q0, q_full);
@@ -568,8 +570,8 @@ bool q_map_for(const void* base, int64_t tokens, int heads, int group, int tq, C
 
 }  // namespace
 
-// Prompt portions, bfloat16, head size 128, groups of 2, 4 or 8 q-heads, pages of 16 tokens or more (a power of
-// two), tiles of at least 128 / G tokens.  AKV_PROMPT_KERNEL=mma keeps the mma.sync kernel (for comparisons).
+// Prompt portions, bfloat16, head size 128, groups of 1 to 16 q-heads, pages of 16 tokens or more (a power of
+// two).  AKV_PROMPT_KERNEL=mma keeps the mma.sync kernel (for comparisons).
 bool attention_tcgen05_supported(const PagedAttentionParams& p) {
   static const bool disabled = [] {
     const char* v = getenv("AKV_PROMPT_KERNEL");
@@ -579,10 +581,8 @@ bool attention_tcgen05_supported(const PagedAttentionParams& p) {
   if (!(p.scale > 0.f)) return false;      // the kernel takes the maximum before it scales
   if (p.num_heads % p.num_kv_heads) return false;
   const int G = p.num_heads / p.num_kv_heads;
-  if (G != 2 && G != 4 && G != 8) return false;
+  if (G < 1 || G > 16) return false;
   if (p.page_size < 16 || (p.page_size & (p.page_size - 1))) return false;
-  const int tq = kRows / G;
-  if (p.q_tile % tq != 0 && p.q_tile > tq) return false;
   if (p.num_kv_heads > 65535) return false;
   return encode_fn() != nullptr;
 }

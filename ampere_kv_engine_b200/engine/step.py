@@ -76,6 +76,7 @@ class ModelRunner:
         self.manager = CacheManager(model.cache_specs(), model.cache_of(), page_size=page_size, num_pages=num_pages,
                                     max_seqs=max_seqs, dtype=kv_dtype, device=self.device)
         self.views = self.manager.layer_views()
+        self.q_tile = model.q_tile() if hasattr(model, "q_tile") else ops.ATTENTION_Q_TILE
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         #: the tokens the last step chose, kept on the device: an entry with a ``source`` reads its token here
         self.sampled = torch.zeros(max(1, max_seqs), dtype=torch.int32, device=self.device)
@@ -116,7 +117,8 @@ class ModelRunner:
             if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= _SEQ_BUCKETS[-1]:
                 logits = self._decode_step_captured(entries)
             else:
-                ctx = build_context(self.manager, entries, self.device, status=self.status, sampled=self.sampled)
+                ctx = build_context(self.manager, entries, self.device, status=self.status, sampled=self.sampled,
+                                    q_tile=self.q_tile)
                 self.last_h2d_bytes = ctx.h2d_bytes
                 logits = self.model.forward(ctx, self.views)
         except BaseException:

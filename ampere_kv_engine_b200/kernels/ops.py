@@ -169,6 +169,14 @@ def sm_count(device=None) -> int:
     return _SM_COUNT[index]
 
 
+def attention_q_tile(head_dim: int, group_size: int) -> int:
+    """Query tokens per attention tile that suit a mixer of this shape: the tcgen05 prompt kernel's CTAs take
+    128 // group tokens (128 rows), so a group that does not divide 128 gets tiles of exactly that many."""
+    if head_dim == 128 and 1 <= group_size <= 16 and 128 % group_size:
+        return 128 // group_size
+    return ATTENTION_Q_TILE
+
+
 def attention_takes_tensor_cores(dtype: torch.dtype, head_dim: int, group_size: int, page_size: int) -> bool:
     """Whether the TMA + tensor-core attention kernels take these sizes (else the general kernel runs)."""
     return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group_size <= 16 and page_size >= 8
@@ -227,7 +235,7 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
                     kernel: str = "auto", out=None):
     """Causal attention of the batch's new tokens over the paged cache.  ``kernel``: ``"auto"`` takes the
     tensor-core kernels where they fit (bfloat16, head size 64 or 128; prompt portions at head size 128 and groups
-    of 2, 4 or 8 q-heads on tcgen05) and the general kernel elsewhere; ``"general"`` forces the latter, ``"mma"``
+    of up to 16 q-heads on tcgen05) and the general kernel elsewhere; ``"general"`` forces the latter, ``"mma"``
     keeps prompt portions on the mma.sync kernel.  Only the rows of the given tiles are written; with ``out`` they
     go into that tensor (a batch may be covered by two calls with different tile sizes)."""
     if out is None:

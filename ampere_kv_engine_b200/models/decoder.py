@@ -81,6 +81,13 @@ class DecoderModel:
         """One per schedule position."""
         return [self.blocks[e.layer].cache_spec() for e in self.spec.schedule]
 
+    def q_tile(self) -> int:
+        """Query tokens per attention tile of the batch layout: what every mixer with a preference asks for, if they
+        agree."""
+        wishes = {m.preferred_q_tile() for blk in self.blocks for m in [getattr(blk, "mixer", None)]
+                  if m is not None and m.preferred_q_tile() is not None}
+        return wishes.pop() if len(wishes) == 1 else ops.ATTENTION_Q_TILE
+
     def cache_of(self) -> list[int | None]:
         return [e.cache_of for e in self.spec.schedule]
 

@@ -53,6 +53,9 @@ class PagedAttention(Mixer):
     def children(self):
         return (self.position_encoding,)
 
+    def preferred_q_tile(self):
+        return ops.attention_q_tile(self.head_dim, self.num_heads // self.num_kv_heads)
+
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(kind="window" if self.window is not None else "full", num_kv_heads=self.num_kv_heads,
                          head_dim=self.head_dim, window=None if self.window is None else int(self.window))

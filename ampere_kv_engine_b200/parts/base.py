@@ -153,6 +153,12 @@ class Mixer(Part):
     def cache_spec(self) -> CacheSpec:
         return CacheSpec()
 
+    def preferred_q_tile(self) -> int | None:
+        """Query tokens per attention tile this mixer's kernels like best (None: no preference).  The batch layout
+        cuts prompt portions into tiles of one size for the whole model: the one all mixers agree on, else the
+        default."""
+        return None
+
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         """x: [tokens, hidden] in the compute dtype; ``ctx`` is the step's batch
         (:class:`~ampere_kv_engine_b200.engine.batch.StepContext`); ``cache`` is this schedule

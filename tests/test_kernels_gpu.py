@@ -389,10 +389,14 @@ def test_tensor_core_and_general_kernels_agree(ops, nh, nkv, d, page, window):
 
 
 @pytest.mark.parametrize("nh,nkv,page,q_tile", [(32, 8, 16, 32), (16, 8, 32, 64), (8, 1, 64, 16), (32, 8, 16, 16),
-                                                 (32, 8, 16, 64), (8, 2, 16, 96), (16, 2, 32, 64), (8, 4, 64, 128)])
+                                                 (32, 8, 16, 64), (8, 2, 16, 96), (16, 2, 32, 64), (8, 4, 64, 128),
+                                                 # groups that do not divide 128 (dead rows at a tile's end), one
+                                                 # q-head per kv head, sixteen
+                                                 (40, 8, 16, 25), (40, 8, 16, 32), (6, 2, 16, 42), (4, 4, 16, 32),
+                                                 (16, 1, 16, 32), (12, 2, 32, 21), (14, 2, 16, 64)])
 @pytest.mark.parametrize("window", [0, 100, 37])
 def test_tcgen05_prompt_attention(ops, nh, nkv, page, q_tile, window):
-    """Prompt portions at head size 128 with groups of 2, 4 and 8 q-heads run on the tcgen05 kernel: whole
+    """Prompt portions at head size 128 with groups of 1 to 16 q-heads run on the tcgen05 kernel: whole
     prompts, portions after a long history, tiles that end mid-way, a portion of one token beside them.  Batch
     tiles of one, two, three or four of the kernel's 128-row query tiles (the last one whole, partial or empty),
     windows longer and shorter than a tile's span."""
