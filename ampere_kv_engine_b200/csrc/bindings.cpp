@@ -404,7 +404,7 @@ void small_m_gemm_qkv(const OptTensor& x, const Tensor& w, Tensor& q_out, const 
 //   "plain" (out [tokens, features]) or "qkv" (q_out, positions, slots, q_weight, k_weight, inv_freq, k_cache,
 //   v_cache, num_heads, num_kv_heads, qk_eps: the arguments of small_m_gemm_qkv).
 // ssq [ceil(hidden / 128), tokens] float32 scratch; parts and sync as stream_phases_scratch says, sync zeroed.
-akv::StreamPhase parse_stream_phase(const py::dict& d, const Tensor& hidden, int64_t tokens, bool full_check) {
+akv::StreamPhase parse_stream_phase(const py::dict& d, const Tensor& hidden, int64_t tokens) {
   akv::StreamPhase ph = {};
   const Tensor w = d["w"].cast<Tensor>();
   check_cuda(w, "w");
@@ -483,7 +483,6 @@ akv::StreamPhase parse_stream_phase(const py::dict& d, const Tensor& hidden, int
   } else {
     AKV_CHECK(false, "unknown epilogue '", epilogue, "' (residual, gated, plain, qkv)");
   }
-  (void)full_check;
   return ph;
 }
 
@@ -497,7 +496,7 @@ void stream_phases(Tensor& hidden, const py::list& phases, Tensor& ssq, Tensor& 
   const int64_t n = (int64_t)phases.size();
   AKV_CHECK(n >= 1 && n <= akv::kMaxStreamPhases, "stream_phases takes 1 to ", akv::kMaxStreamPhases, " phases, got ", n);
   akv::StreamPhase list[akv::kMaxStreamPhases];
-  for (int64_t i = 0; i < n; ++i) list[i] = parse_stream_phase(phases[i].cast<py::dict>(), hidden, tokens, true);
+  for (int64_t i = 0; i < n; ++i) list[i] = parse_stream_phase(phases[i].cast<py::dict>(), hidden, tokens);
   int64_t part_floats = 0, sync_ints = 0;
   akv::stream_phases_scratch(list, (int)n, &part_floats, &sync_ints);
   check_f32(ssq, "ssq");

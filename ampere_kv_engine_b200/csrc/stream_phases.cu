@@ -171,7 +171,6 @@ struct StreamParamsDev {
   int num_phases, tokens, hidden_size, grid;
   int stages;                // ring slots of 16 KB
   int xslots;                // K blocks of token operand the buffer holds (the most any CTA needs in any phase)
-  int l2_ahead;              // blocks the L2 is asked for beyond the ring
   float* hidden;             // [tokens, hidden_size] float32: normed-x source, residual target
   float* ssq;                // [ceil(hidden_size / 128), tokens]
   float* parts;
@@ -181,7 +180,15 @@ struct StreamParamsDev {
   StreamPhaseDev phase[kMaxStreamPhases];
 };
 
+// Slots of the measurement trace [grid][phases][kTraceSlots]: where a CTA's warps are in a phase, in nanoseconds.
 constexpr int kTraceSlots = 16;
+enum TraceSlot : int {
+  kTraceFirstCopy = 0, kTraceLastCopy = 1, kTraceFirstMma = 2, kTraceLastMma = 3, kTraceOperandMayStart = 4,
+  kTraceOperandFirstGroup = 5, kTraceOperandDone = 6, kTraceLastEpilogue = 7,
+  // of the CTA's last segment in the phase:
+  kTraceSegAccumulated = 8, kTraceSegPartialStored = 9, kTraceSegTicket = 10, kTraceSegFinalizeStart = 11,
+  kTraceSegFinalizeMath = 12, kTraceSegPublished = 13,
+};
 __device__ __forceinline__ void stamp(const StreamParamsDev& p, int cta, int ph, int what) {
   if (p.trace != nullptr) {
     unsigned long long t;
@@ -227,11 +234,6 @@ struct BlockWalk {
     if (--left == 0) enter(p, cta);
   }
 };
-
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
-               : "memory");
-}
 
 // Shared memory of a launch with `stages` ring slots and `xslots` K blocks of token operand.
 struct StreamSmem {
@@ -317,24 +319,20 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
   if (warp == 0) {
     // ---- weights: run ahead through every phase's share as fast as ring slots free up.  (One thread walks the
     // blocks; every index is kept by increments: a division per block made this loop, not the memory, the limit.)
-    // A second cursor runs p.l2_ahead blocks further ahead and asks the L2 for them: when the ring is full because
-    // the MMAs wait for a phase to finish everywhere, the memory keeps streaming into the L2, and the ring
-    // catches up from there.
+    // (A second cursor that asked the L2 for blocks ahead of the ring, so that the memory would keep streaming
+    // while the MMAs wait for a phase to finish everywhere, made the chain slower the further ahead it ran, with
+    // and without eviction priorities: 108 / 113 / 120 / 135 us at 0 / 8 / 16 / 32 blocks.  It was taken out.)
     if (lane == 0) {
-      BlockWalk load(p, cta), ahead(p, cta);
-      for (int i = 0; i < p.l2_ahead && ahead.valid(); ++i) {
-        tma_prefetch_2d(maps[ahead.ph], ahead.k * kTileK, ahead.y);
-        ahead.next(p, cta);
-      }
+      BlockWalk load(p, cta);
       int s = 0;                 // ring slot of the next block
       uint32_t round = 0;        // parity of the times the ring has been gone around
       bool lapped = false;       // the ring has been filled once: a slot must be waited for
       int stamped = -1;
       while (load.valid()) {
         if (load.ph != stamped) {
-          if (stamped >= 0) stamp(p, cta, stamped, 1);
+          if (stamped >= 0) stamp(p, cta, stamped, kTraceLastCopy);
           stamped = load.ph;
-          stamp(p, cta, stamped, 0);
+          stamp(p, cta, stamped, kTraceFirstCopy);
         }
         if (lapped && !mbar_wait(&empty[s], round ^ 1u)) {
           ok = false;
@@ -343,17 +341,13 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         mbar_expect_tx(&w_full[s], kWBytes);
         tma_load_2d(smem + s * kStageBytes, maps[load.ph], load.k * kTileK, load.y, &w_full[s]);
         load.next(p, cta);
-        if (ahead.valid()) {
-          tma_prefetch_2d(maps[ahead.ph], ahead.k * kTileK, ahead.y);
-          ahead.next(p, cta);
-        }
         if (++s == stages) {
           s = 0;
           round ^= 1u;
           lapped = true;
         }
       }
-      if (stamped >= 0) stamp(p, cta, stamped, 1);
+      if (stamped >= 0) stamp(p, cta, stamped, kTraceLastCopy);
       if (!ok) {
         // copies already issued must land before the CTA's shared memory goes away: every slot whose copy has not
         // been consumed completes its current phase (bounded waits; a slot never used returns at once)
@@ -394,7 +388,7 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
               break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (b == r.lo && i == 0) stamp(p, cta, ph, 2);
+            if (b == r.lo && i == 0) stamp(p, cta, ph, kTraceFirstMma);
             const uint32_t a_addr = smem_u32(smem) + (uint32_t)s * kStageBytes;
             const uint32_t b_addr = smem_u32(xbuf) + (uint32_t)slot * kXBytes;
 #pragma unroll
@@ -419,7 +413,7 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
           if (!mbar_wait(&x_ready[groups_ready], ph & 1)) ok = false;
           ++groups_ready;
         }
-        stamp(p, cta, ph, 3);
+        stamp(p, cta, ph, kTraceLastMma);
         if (ok) umma_commit(mma_phase_done);      // arrives once every MMA of the phase has read the operand
       }
     }
@@ -476,7 +470,7 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         ok = false;
         break;
       }
-      if (xt == 0) stamp(p, cta, ph, 4);
+      if (xt == 0) stamp(p, cta, ph, kTraceOperandMayStart);
       const int group_size = x_group_size(span);
       for (int group = 0; group < kXGroups; ++group) {
         const int slot_lo = group * group_size;
@@ -513,9 +507,9 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the tensor core reads through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&x_ready[group]);
-        if (xt == 0 && group == 0) stamp(p, cta, ph, 5);
+        if (xt == 0 && group == 0) stamp(p, cta, ph, kTraceOperandFirstGroup);
       }
-      if (xt == 0) stamp(p, cta, ph, 6);
+      if (xt == 0) stamp(p, cta, ph, kTraceOperandDone);
     }
   } else {
     // ---- epilogue: every segment's partial tile, and the tiles this CTA completes
@@ -541,7 +535,7 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool stamper = threadIdx.x == kFirstEpiWarp * 32;
-        if (stamper) stamp(p, cta, ph, 8);
+        if (stamper) stamp(p, cta, ph, kTraceSegAccumulated);
         uint32_t v[16];
         tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kBN), v);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -557,17 +551,17 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
 #pragma unroll
           for (int t = 0; t < kRows; ++t)
             if (t < p.tokens) mine[t * kTileM + row] = __uint_as_float(v[t]);
-          if (stamper) stamp(p, cta, ph, 9);
+          if (stamper) stamp(p, cta, ph, kTraceSegPartialStored);
           bar_sync(1, 128);       // everybody's partial is written (CTA scope) ...
           if (threadIdx.x == kFirstEpiWarp * 32) flags[0] = atom_add_acq_rel(&tickets[tile], 1);   // ... and published
           bar_sync(1, 128);
-          if (stamper) stamp(p, cta, ph, 10);
+          if (stamper) stamp(p, cta, ph, kTraceSegTicket);
         }
         const bool last = sharers == 1 || flags[0] == sharers - 1;
         if (last) {
           // the tile is whole (the ticket's acquire, passed on by the barrier, lets everybody see the partials):
           // add them up in slot order and apply the phase's epilogue
-          if (stamper) stamp(p, cta, ph, 11);
+          if (stamper) stamp(p, cta, ph, kTraceSegFinalizeStart);
           float sum[kRows];
 #pragma unroll
           for (int t = 0; t < kRows; ++t) sum[t] = 0.f;
@@ -728,14 +722,14 @@ stream_phases_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
             }
           }
           // the tile is finished: count it, publishing what everybody wrote before the barrier
-          if (stamper) stamp(p, cta, ph, 12);
+          if (stamper) stamp(p, cta, ph, kTraceSegFinalizeMath);
           bar_sync(1, 128);
           if (threadIdx.x == kFirstEpiWarp * 32) red_add_release(tickets + P.tiles, 1);
-          if (stamper) stamp(p, cta, ph, 13);
+          if (stamper) stamp(p, cta, ph, kTraceSegPublished);
         }
         b = seg_end;
         ++seg;
-        if (threadIdx.x == kFirstEpiWarp * 32) stamp(p, cta, ph, 7);
+        if (threadIdx.x == kFirstEpiWarp * 32) stamp(p, cta, ph, kTraceLastEpilogue);
       }
     }
   }
@@ -892,14 +886,6 @@ int launch_stream_phases(const StreamPhase* phases, int num_phases, int64_t toke
   if (stages < 2) return (int)cudaErrorInvalidValue;
   p.stages = stages;
   p.xslots = xslots;
-  // Off by default: measured on B200, asking the L2 for 24 or 48 blocks ahead per CTA made a layer's chain 25 % and
-  // 36 % slower (AKV_STREAM_L2_AHEAD=n for measurements)
-  static const int l2_ahead = [] {
-    const char* v = getenv("AKV_STREAM_L2_AHEAD");
-    const int n = v ? atoi(v) : -1;
-    return (n >= 0 && n <= 256) ? n : 0;
-  }();
-  p.l2_ahead = l2_ahead;
   return launch_kernel(maps, p, stream);
 }
 

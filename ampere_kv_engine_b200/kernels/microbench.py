@@ -4,6 +4,7 @@
     python -m ampere_kv_engine_b200.kernels.microbench decode-attention --batch 64 --context 1152
     python -m ampere_kv_engine_b200.kernels.microbench prefill-attention --tokens 2048
     python -m ampere_kv_engine_b200.kernels.microbench norm --tokens 2048
+    python -m ampere_kv_engine_b200.kernels.microbench chain --tokens 8 [--trace]
 
 The counterpart of the reference's kernel micro-benchmark (``python -m ampere_kv.paged_decode --benchmark``,
 ampere_kv/paged_decode.py:19-100, CUDA-event windows at 64/256/1024/4096 keys).  Each case cycles through
@@ -176,9 +177,81 @@ def bench_rowwise(args) -> dict:
     return out
 
 
+def bench_chain(args) -> dict:
+    """A layer's chain of products (output projection + residual -> norm + gate/up + SiLU-mul -> down + residual ->
+    norm + next q/k/v + rotation + cache write) as ONE launch of the chained-product kernel against the four
+    separate kernels, each on three copies of the weights in turn.  ``--trace``: where the persistent kernel's
+    CTAs are in each phase, from its nanosecond stamps (minimum / median / maximum over the CTAs, microseconds)."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    t, h, inter, heads, kv = args.tokens, args.hidden, args.intermediate, args.heads, args.kv_heads
+    rand = lambda *shape, scale=0.02: torch.randn(*shape, generator=g, device="cuda") * scale
+    copies = []
+    for _ in range(3):
+        gate_up = ops.interleave_gate_up(rand(inter, h).bfloat16(), rand(inter, h).bfloat16(), ops.GATE_UP_RUN)
+        copies.append((rand(h, heads * 128).bfloat16(), gate_up.contiguous(), rand(h, inter).bfloat16(),
+                       rand((heads + 2 * kv) * 128, h).bfloat16()))
+    norm_a, norm_b = 1 + rand(h, scale=0.1), 1 + rand(h, scale=0.1)
+    qn, kn = 1 + rand(128, scale=0.1), 1 + rand(128, scale=0.1)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, 128, 2).float() / 128))).cuda()
+    hidden = rand(t, h, scale=1.0)
+    attn_out = rand(t, heads * 128, scale=1.0).bfloat16()
+    positions = torch.arange(1000, 1000 + t, device="cuda", dtype=torch.int32)
+    slots = torch.arange(t, device="cuda", dtype=torch.int32)
+    k_cache = torch.zeros((t // args.page_size + 2, kv, args.page_size, 128), device="cuda", dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    act = torch.empty((t, inter), dtype=torch.bfloat16, device="cuda")
+    q_out = torch.empty((t, heads * 128), dtype=torch.bfloat16, device="cuda")
+
+    def phases(i):
+        o, gu, down, qkv = copies[i % 3]
+        return [dict(w=o, x=attn_out, epilogue="residual"),
+                dict(w=gu, norm_weight=norm_a, eps=1e-6, epilogue="gated", out=act),
+                dict(w=down, x=act, epilogue="residual"),
+                dict(w=qkv, norm_weight=norm_b, eps=1e-6, epilogue="qkv", q_out=q_out, positions=positions,
+                     slots=slots, q_weight=qn, k_weight=kn, inv_freq=inv_freq, k_cache=k_cache, v_cache=v_cache,
+                     num_heads=heads, num_kv_heads=kv, qk_eps=1e-6)]
+    lists = [phases(i) for i in range(3)]
+
+    def chained(i):
+        ops.stream_begin_step("cuda")
+        ops.stream_phases(hidden, lists[i % 3], status=status)
+
+    def separate(i):
+        o, gu, down, qkv = copies[i % 3]
+        summed = ops.linear_into_residual(attn_out, o, hidden, status=status)
+        x = ops.LazyNorm(summed, norm_a, 1e-6, torch.bfloat16, status)
+        a = ops.gated_linear(x, gu, ops.GATE_UP_RUN, status=status)
+        summed = ops.linear_into_residual(a, down, hidden, status=status)
+        x = ops.LazyNorm(summed, norm_b, 1e-6, torch.bfloat16, status)
+        ops.project_qkv(x, qkv, None, positions, slots, qn, kn, inv_freq, k_cache, v_cache, num_heads=heads,
+                        num_kv_heads=kv, head_dim=128, rotary_dim=128, eps=1e-6, status=status)
+
+    nbytes = sum(w.numel() * 2 for w in copies[0])
+    out = {"weight_mb": round(nbytes / 1e6, 1), "chained_us": timed_graph(chained, args.calls),
+           "separate_us": timed_graph(separate, args.calls)}
+    out["chained_gbs"] = round(nbytes / out["chained_us"] / 1e3, 1)
+    out["separate_gbs"] = round(nbytes / out["separate_us"] / 1e3, 1)
+    if args.trace:
+        grid = int(ops.ext().stream_phases_grid())
+        trace = torch.zeros((grid, 4, 16), dtype=torch.int64, device="cuda")
+        ops.stream_begin_step("cuda")
+        ops.stream_phases(hidden, lists[0], status=status, trace=trace)
+        torch.cuda.synchronize()
+        stamps = trace.cpu().double()
+        stamps = (stamps - stamps[stamps > 0].min()) / 1000.0
+        names = ("first copy", "last copy", "first mma", "last mma", "operand may start", "operand first group",
+                 "operand done", "last epilogue")
+        out["trace_us"] = {f"phase{ph} {name}": [round(float(f(stamps[:, ph, e])), 2) for f in
+                                               (torch.min, torch.median, torch.max)]
+                           for ph in range(4) for e, name in enumerate(names)}
+    out["status"] = int(status.item())
+    return out
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("kernel", choices=("gemm", "decode-attention", "prefill-attention", "norm"))
+    parser.add_argument("kernel", choices=("gemm", "decode-attention", "prefill-attention", "norm", "chain"))
     parser.add_argument("--tokens", type=int, default=8)
     parser.add_argument("--features", type=int, default=24576)
     parser.add_argument("--k", type=int, default=4096)
@@ -193,6 +266,7 @@ def main(argv=None) -> int:
     parser.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0 = the engine's choice)")
     parser.add_argument("--with-general", action="store_true", help="also time the general attention kernel on prompts")
     parser.add_argument("--gated", action="store_true", help="gemm: the SiLU-mul epilogue (gate/up rows in runs of 64)")
+    parser.add_argument("--trace", action="store_true", help="chain: the persistent kernel's per-phase time stamps")
     parser.add_argument("--calls", type=int, default=50)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
@@ -202,6 +276,8 @@ def main(argv=None) -> int:
         result = bench_gemm(args)
     elif args.kernel == "decode-attention":
         result = bench_attention(args, 1, args.batch, args.context)
+    elif args.kernel == "chain":
+        result = bench_chain(args)
     elif args.kernel == "prefill-attention":
         result = bench_attention(args, args.tokens, 1, max(args.context, args.tokens) if args.context > args.tokens
                                  else args.tokens)

@@ -112,7 +112,7 @@ class PagedAttention(Mixer):
             else:
                 x = x.materialize()
         if q is not None:
-            pass
+            pass        # the chained-product kernel made q and wrote K and V
         elif fused is not None:
             inv_freq, rotary_dim = fused
             q = ops.project_qkv(
