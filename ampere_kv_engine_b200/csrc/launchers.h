@@ -116,8 +116,8 @@ struct StreamPhase {
   void* out;                 // plain: bfloat16 [tokens, features]; gated: bfloat16 [tokens, features / 2]
   GemmQkv qkv;               // kEpilogueQkv
 };
-// CTAs the kernel runs with (one per SM), and the scratch a launch needs: float32 partial tiles and int32 counters
-// (the counters must be zero at launch).
+// CTAs the kernel asks for (one per SM, in clusters of four), and the scratch a launch needs: float32 words for
+// partial tiles (none: they stay in shared memory) and int32 counters, one per phase, zero at launch.
 int stream_phases_grid();
 void stream_phases_scratch(const StreamPhase* phases, int num_phases, int64_t* part_floats, int64_t* sync_ints);
 // `trace` (null in production): int64 [grid, kMaxStreamPhases, 16] that receives nanosecond stamps of each CTA's

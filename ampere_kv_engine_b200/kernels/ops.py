@@ -415,18 +415,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 #: a decode step of at most this many bfloat16 tokens may run the tail of each layer and the head of the next (output
 #: projection, gate/up, down, the next q/k/v projection) as ONE persistent kernel that never stops streaming weights
 STREAM_LIMIT = 8
-#: Off unless AKV_STREAM_PHASES=1: measured on B200 at the benchmark model's sizes the chain of a layer takes 105 us
-#: in the persistent kernel against 72 us as four kernels.  Its weights do stream at the memory's rate (0.36 us per
-#: 16 KB block per SM), but each of the three places where a phase needs the one before it finished everywhere costs
-#: 7 to 10 us (partial tiles through the L2, a ticket, the last sharer's sums, a counter, the operand built anew)
-#: against the 3.6 us of weights that the ring holds, where the four kernels reduce their K splits through
-#: distributed shared memory in about 2 us.  Asking the L2 for blocks ahead of the ring made it slower still.
+#: Off unless AKV_STREAM_PHASES=1: measured on B200 at the benchmark model's sizes the chain of a layer takes 100 us
+#: in the persistent kernel against 76 us as four kernels (a decode step of 8 tokens: 4.26 ms against 3.37 ms).  Its
+#: weights do stream at the memory's rate (0.37 us per 16 KB block per SM), but each of the three places where a
+#: phase needs the one before it finished everywhere costs 5 to 6 us (the last tile's sum over the cluster, a
+#: releasing count in global memory, the slowest SM, the operand built anew) against the 3.7 us of weights that the
+#: ring holds, and whole tiles per cluster of four leave a share of the SMs idle at the end of each phase (48 tiles
+#: over 33 clusters).  Asking the L2 for blocks ahead of the ring made it slower still.
 use_stream_phases = os.environ.get("AKV_STREAM_PHASES", "0") == "1"
 _STREAM_SYNC_INTS = 1 << 16
 
 
 class _StreamScratch:
-    """Per device: sums of squares, partial tiles and zeroed counters of the chained-product kernel.  The counters
+    """Per device: sums of squares, whatever scratch the kernel asks for and its zeroed counters.  The counters
     are handed out slice by slice and zeroed again at the start of every step (``stream_begin_step``)."""
 
     def __init__(self, device):
