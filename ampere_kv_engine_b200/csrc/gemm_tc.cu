@@ -5,7 +5,9 @@
 // tcgen05.mma.  K is cut into 1/2/4/8 splits so that a thin output still occupies the whole GPU.  The CTAs of
 // one output tile form a thread-block cluster: each leaves its float32 partial tile in its own shared memory,
 // and after a cluster barrier every CTA adds up, in split order, a share of the tile read from its peers'
-// shared memory (distributed shared memory) and stores it, rounded once.  With ``parts`` instead of ``out``
+// shared memory (distributed shared memory) and stores it, rounded once: a CTA owns the tokens split, split + S,
+// ... and fetches all their partial sums in ONE round trip (a round trip costs about a microsecond when every
+// CTA reduces at once, and at 32 tokens the token-by-token loop paid four).  With ``parts`` instead of ``out``
 // the float32 partial tiles are stored as they are, [splits, tokens, features].
 //
 // One CTA = 6 warps: warp 0 issues the TMA loads (128-byte swizzled tiles of 64 K-elements, a 4-stage ring
@@ -28,6 +30,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
 
 namespace akv {
 
@@ -113,8 +116,11 @@ struct GemmSmem {
   static constexpr int kB = BN * kTileK * 2;
   static constexpr int kStage = kA + kB;
   static constexpr int kReduce = BN * kTileM * 4;                      // float32 partial tile, reuses the stages
-  static constexpr int kQkvScratch = (8 + 2 * kTileM) * 4;            // kEpilogueQkv: warp sums and normed values
-  static_assert(kReduce + kQkvScratch <= kStages * kStage, "the partial tile must fit in the stage ring");
+  // behind it, for the epilogues that work across a tile's features: this CTA's own tokens' values
+  // [tokens][128], then per token four warp sums, the position and the cache slot (at most BN tokens: one split)
+  static constexpr int kOwnScratch = BN * (kTileM + 8) * 4;
+  static_assert(kReduce <= kStages * kStage, "the partial tile must fit in the stage ring");
+  static constexpr bool kOwnFits = kReduce + kOwnScratch <= kStages * kStage;
   static constexpr int kBars = (2 * kStages + 1) * 8 + 16;             // barriers, TMEM base
   static constexpr int kBytes = kStages * kStage + kBars + 64 * 4 + 1024;   // + inverse RMS per token (kNormedX)
 };
@@ -123,52 +129,44 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
-// Float at `local_addr` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster.
-__device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
-
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// The float at `local_addr` summed over the cluster's CTAs (one per K split, at most 8), in split order.  All loads
-// are issued before the first is used: one round trip through distributed shared memory, not one per split.
-__device__ __forceinline__ float sum_over_splits(uint32_t local_addr, int splits) {
-  float v[8];
-#pragma unroll
-  for (int s = 0; s < 8; ++s) v[s] = s < splits ? ld_peer_smem(local_addr, (uint32_t)s) : 0.f;
-  float sum = v[0];
-#pragma unroll
-  for (int s = 1; s < 8; ++s) sum += v[s];      // absent splits add an exact zero
-  return sum;
-}
-
-// The same for four places at once (addr[j] == kNoPlace: no such place): 32 loads under way, so that a CTA with many
-// tokens to reduce pays a round trip per four tokens.
+// Sums over the cluster's CTAs (one per K split, in split order) of kPlaces floats of the partial tiles, every load
+// issued before the first is used: ONE round trip through distributed shared memory (about a microsecond when all
+// CTAs reduce at once), however many tokens this CTA owns.  offset[i] is the float's byte offset in the partial
+// tile, or kNoPlace.
 constexpr uint32_t kNoPlace = 0xffffffffu;
-__device__ __forceinline__ void sum4_over_splits(const uint32_t (&addr)[4], int splits, float (&sum)[4]) {
-  float v[4][8];
+template <int kPlaces, int S>
+__device__ __forceinline__ void gather_sums(uint32_t tile_addr, const uint32_t (&offset)[kPlaces], float (&sum)[kPlaces]) {
+  uint32_t peer[S];
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+  for (int s = 0; s < S; ++s)
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[s]) : "r"(tile_addr), "r"((uint32_t)s));
+  float v[kPlaces][S];
 #pragma unroll
-    for (int s = 0; s < 8; ++s) v[j][s] = (addr[j] != kNoPlace && s < splits) ? ld_peer_smem(addr[j], (uint32_t)s) : 0.f;
+  for (int i = 0; i < kPlaces; ++i)
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    sum[j] = v[j][0];
+    for (int s = 0; s < S; ++s) {
+      v[i][s] = 0.f;
+      if (offset[i] != kNoPlace)
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[i][s]) : "r"(peer[s] + offset[i]) : "memory");
+    }
 #pragma unroll
-    for (int s = 1; s < 8; ++s) sum[j] += v[j][s];
+  for (int i = 0; i < kPlaces; ++i) {
+    sum[i] = v[i][0];
+#pragma unroll
+    for (int s = 1; s < S; ++s) sum[i] += v[i][s];
   }
 }
 
 template <int BN, typename OutT, int kStages, int kEpilogue, bool kNormedX>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, 3)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                     GemmParams p) {
+  static_assert((kEpilogue != kEpilogueQkv && kEpilogue != kEpilogueResidual) || GemmSmem<BN, kStages>::kOwnFits,
+                "the partial tile and the epilogue's scratch must fit in the stage ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * GemmSmem<BN, kStages>::kStage);
@@ -336,163 +334,224 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if (split < p.tokens && feature < p.features)
         res_old = p.residual.hidden[(int64_t)split * p.features + feature];
     }
-    if (!mbar_wait(acc_ready, 0)) ok = false;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // The tail runs once per CTA: its loops over token columns are not unrolled further than they must be (measured:
+    // fetching the instructions of a fully unrolled copy of 64 columns took 4 us, executing them 0.5 us).
     const int row = quarter * 32 + lane;
     const int feature = tile * kTileM + row;
-    float* reduce = reinterpret_cast<float*>(smem);     // [token][128 features]; the stages are drained by now
+    float* reduce = reinterpret_cast<float*>(smem);     // [token][128 features]; the stages are drained by then
     float* part_out = p.parts ? p.parts + (int64_t)split * p.tokens * p.features : nullptr;
-#pragma unroll
-    for (int c = 0; c < BN / 16; ++c) {
-      uint32_t v[16];
-      if (ok) {
-        tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, v);
-      } else {
-#pragma unroll
-        for (int t = 0; t < 16; ++t) v[t] = 0u;
-      }
-#pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        const int token = c * 16 + t;
-        if (part_out) {
-          if (token < p.tokens && feature < p.features)
-            part_out[(int64_t)token * p.features + feature] = __uint_as_float(v[t]);
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    const float first_sn = qkv_sn, first_co = qkv_co;
+    const int64_t first_slot = qkv_slot;
+    if (!mbar_wait(acc_ready, 0)) ok = false;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    {
+      // accumulator -> shared memory (or the caller's partial tiles), 16 token columns at a time
+#pragma unroll 1
+      for (int c = 0; c < BN / 16; ++c) {
+        uint32_t v[16];
+        if (ok) {
+          tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, v);
         } else {
-          reduce[token * kTileM + row] = __uint_as_float(v[t]);
+#pragma unroll
+          for (int t = 0; t < 16; ++t) v[t] = 0u;
+        }
+        if (part_out) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const int token = c * 16 + t;
+            if (token < p.tokens && feature < p.features)
+              part_out[(int64_t)token * p.features + feature] = __uint_as_float(v[t]);
+          }
+        } else {
+          float* dst = reduce + c * 16 * kTileM + row;
+#pragma unroll
+          for (int t = 0; t < 16; ++t) dst[t * kTileM] = __uint_as_float(v[t]);
         }
       }
+    }
+    if (!ok) set_status(p.status, kWaitTimeout);
+    if (p.out != nullptr) {
+      // every CTA of the tile has its partial in shared memory: add them up across the cluster, in split order
+      cluster_sync_all();
+      const uint32_t tile_addr = smem_u32(smem);
+      // This CTA owns the tokens split, split + S, ...: at most BN / S of them.  Their sums over the splits are
+      // gathered in one round trip, whatever their number; what follows works on registers and on this CTA's
+      // own shared memory.
+      auto tail = [&](auto splits_tag, auto own_tag) {
+        constexpr int S = decltype(splits_tag)::value;
+        constexpr int kOwn = decltype(own_tag)::value;       // places (tokens; gate and up rows count apart) per thread
+        float* own = reinterpret_cast<float*>(smem + GemmSmem<BN, kStages>::kReduce);      // [kOwn][128]
+        [[maybe_unused]] float* red = own + kOwn * kTileM;                                 // [kOwn][8]
+        uint32_t off[kOwn];
+        float sum[kOwn];
+        if constexpr (kEpilogue == kEpilogueGated) {
+          // rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64 outputs.  A thread takes
+          // output j of every other token of this CTA's share and adds up both of its rows.
+          constexpr int kTok = kOwn / 2;
+          const int j = row & 63, half = row >> 6;
+          const int out_features = p.features / 2;
+          const int gated_feature = tile * (kTileM / 2) + j;
+#pragma unroll
+          for (int i = 0; i < kTok; ++i) {
+            const int tok = split + half * S + i * 2 * S;
+            const bool there = tok < p.tokens && gated_feature < out_features;
+            off[2 * i] = there ? (uint32_t)(tok * kTileM + j) * 4u : kNoPlace;
+            off[2 * i + 1] = there ? off[2 * i] + (kTileM / 2) * 4u : kNoPlace;
+          }
+          gather_sums<kOwn, S>(tile_addr, off, sum);
+#pragma unroll
+          for (int i = 0; i < kTok; ++i) {
+            const int tok = split + half * S + i * 2 * S;
+            const float g = __bfloat162float(__float2bfloat16_rn(sum[2 * i]));
+            const float u = __bfloat162float(__float2bfloat16_rn(sum[2 * i + 1]));
+            if (off[2 * i] != kNoPlace)
+              out[(int64_t)tok * out_features + gated_feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
+          }
+        } else if constexpr (kEpilogue == kEpilogueQkv) {
+          // The tile is one head of 128 dims; a thread owns dim `row` of it.  Per token of this CTA's share: the
+          // sum rounded as the stored product would be, norm over the head, rotation with the partner dim
+          // (row ^ 64), store to q_out or to the token's cache slot.  The four epilogue warps meet at named
+          // barrier 1, twice for all tokens together.
+          const GemmQkv& e = p.qkv;
+          const int head = tile;
+          const bool is_q = head < e.num_heads, is_k = !is_q && head < e.num_heads + e.num_kv_heads;
+          const int local = is_q ? head : (is_k ? head - e.num_heads : head - e.num_heads - e.num_kv_heads);
+          const bool normed = (is_q ? e.q_weight : (is_k ? e.k_weight : nullptr)) != nullptr;
+          const bool rotate = (is_q || is_k) && e.inv_freq != nullptr;
+          // thread o < kOwn fetches the position and the slot of owned token o (the first one's are known already)
+          int my_pos = 0;
+          int64_t my_slot = -1;
+          {
+            const int tok = split + row * S;
+            if (row > 0 && row < kOwn && tok < p.tokens) {
+              my_pos = e.positions[tok];
+              if (!is_q && e.slots != nullptr) my_slot = e.slots[tok];
+            }
+          }
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o)
+            off[o] = split + o * S < p.tokens ? (uint32_t)((split + o * S) * kTileM + row) * 4u : kNoPlace;
+          gather_sums<kOwn, S>(tile_addr, off, sum);
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o) sum[o] = __bfloat162float(__float2bfloat16_rn(sum[o]));
+          if (normed) {
+#pragma unroll
+            for (int o = 0; o < kOwn; ++o) {
+              const float ss = warp_sum(sum[o] * sum[o]);
+              if (lane == 0) red[o * 8 + (warp & 3)] = ss;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+            for (int o = 0; o < kOwn; ++o) {
+              const float total = red[o * 8] + red[o * 8 + 1] + red[o * 8 + 2] + red[o * 8 + 3];
+              sum[o] = sum[o] * rsqrtf(total / (float)kTileM + e.eps) * qkv_wd;
+            }
+          }
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o) own[o * kTileM + row] = sum[o];
+          if (row > 0 && row < kOwn) {
+            reinterpret_cast<int*>(red)[row * 8 + 4] = my_pos;
+            *reinterpret_cast<int64_t*>(red + row * 8 + 6) = my_slot;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          // token by token from shared memory, so that one copy of the sine and cosine serves them all
+#pragma unroll 1
+          for (int o = 0; o < kOwn; ++o) {
+            const int tok = split + o * S;
+            if (tok >= p.tokens) break;
+            float v = own[o * kTileM + row];
+            float sn = first_sn, co = first_co;
+            int64_t slot = first_slot;
+            if (o > 0) {       // the first token's were fetched while the product ran
+              if (rotate) sincosf((float)reinterpret_cast<const int*>(red)[o * 8 + 4] * qkv_freq, &sn, &co);
+              slot = *reinterpret_cast<const int64_t*>(red + o * 8 + 6);
+            }
+            if (rotate) {
+              const float partner = own[o * kTileM + (row ^ 64)];
+              v = row < 64 ? v * co - partner * sn : v * co + partner * sn;
+            }
+            __nv_bfloat16* dst = nullptr;
+            if (is_q) {
+              dst = (__nv_bfloat16*)e.q_out + ((int64_t)tok * e.num_heads + local) * kTileM;
+            } else if (e.slots != nullptr && e.k_cache != nullptr) {
+              if (slot >= e.num_pages * e.page_size) {
+                if (row == 0) set_status(p.status, kBadSlot);
+              } else if (slot >= 0) {
+                const int64_t page = slot / e.page_size, in_page = slot % e.page_size;
+                dst = (__nv_bfloat16*)(is_k ? e.k_cache : e.v_cache) +
+                      ((page * e.num_kv_heads + local) * e.page_size + in_page) * (int64_t)kTileM;
+              }
+            }
+            if (dst != nullptr) dst[row] = __float2bfloat16_rn(v);
+          }
+        } else if constexpr (kEpilogue == kEpilogueResidual) {
+          // hidden += the tile (rounded as the stored product would be); the new values' squares, summed over the
+          // tile's features, are this tile's share of each token's mean square.
+          float old[kOwn];
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o) {
+            const int tok = split + o * S;
+            const bool there = tok < p.tokens && feature < p.features;
+            off[o] = there ? (uint32_t)(tok * kTileM + row) * 4u : kNoPlace;
+            old[o] = 0.f;
+            if (there) old[o] = o == 0 ? res_old : p.residual.hidden[(int64_t)tok * p.features + feature];
+          }
+          gather_sums<kOwn, S>(tile_addr, off, sum);
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o) {
+            const int tok = split + o * S;
+            float h = 0.f;
+            if (off[o] != kNoPlace) {
+              h = old[o] + __bfloat162float(__float2bfloat16_rn(sum[o]));
+              p.residual.hidden[(int64_t)tok * p.features + feature] = h;
+            }
+            const float ss = warp_sum(h * h);
+            if (lane == 0) red[o * 8 + (warp & 3)] = ss;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (row < kOwn && split + row * S < p.tokens)
+            p.residual.ssq[(int64_t)tile * p.tokens + split + row * S] =
+                red[row * 8] + red[row * 8 + 1] + red[row * 8 + 2] + red[row * 8 + 3];
+        } else {
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o)
+            off[o] = (split + o * S < p.tokens && feature < p.features)
+                         ? (uint32_t)((split + o * S) * kTileM + row) * 4u : kNoPlace;
+          gather_sums<kOwn, S>(tile_addr, off, sum);
+#pragma unroll
+          for (int o = 0; o < kOwn; ++o)
+            if (off[o] != kNoPlace)
+              out[(int64_t)(split + o * S) * p.features + feature] = from_float<OutT>(sum[o]);
+        }
+      };
+      // the usual decode step has no more tokens than splits: one token per CTA, and code that knows it
+      auto tail_of = [&](auto splits_tag) {
+        constexpr int S = decltype(splits_tag)::value;
+        constexpr int kFew = kEpilogue == kEpilogueGated ? 2 : 1;
+        if constexpr (BN / S > kFew) {
+          if (p.tokens <= kFew * S) {
+            tail(splits_tag, std::integral_constant<int, kFew>{});
+            return;
+          }
+        }
+        tail(splits_tag, std::integral_constant<int, BN / S>{});
+      };
+      switch (p.splits) {
+        case 1: tail_of(std::integral_constant<int, 1>{}); break;
+        case 2: tail_of(std::integral_constant<int, 2>{}); break;
+        case 4: tail_of(std::integral_constant<int, 4>{}); break;
+        default: tail_of(std::integral_constant<int, 8>{}); break;
+      }
+      cluster_sync_all();      // nobody leaves while a peer may still read its shared memory
     }
   }
-  if (!ok) set_status(p.status, kWaitTimeout);
-  if (p.out != nullptr) {
-    // every CTA of the tile has its partial in shared memory: add them up across the cluster, in split order
-    cluster_sync_all();
-    if (warp >= 2) {
-      const int row = (warp & 3) * 32 + lane;
-      OutT* out = reinterpret_cast<OutT*>(p.out);
-      if constexpr (kEpilogue == kEpilogueGated) {
-        // rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64 outputs.  A thread takes
-        // output j of every other token of this CTA's share and adds up both of its rows.
-        const int j = row & 63, half = row >> 6;
-        const int out_features = p.features / 2;
-        const int feature = tile * (kTileM / 2) + j;
-        if (feature < out_features) {
-          const int step = 2 * p.splits;
-          for (int token = split + half * p.splits; token < p.tokens; token += 2 * step) {     // two tokens at a time
-            uint32_t addr[4];
-            float sum[4];
-#pragma unroll
-            for (int t2 = 0; t2 < 2; ++t2) {
-              const int tok = token + t2 * step;
-              addr[2 * t2] = tok < p.tokens ? smem_u32(smem) + (uint32_t)(tok * kTileM + j) * 4u : kNoPlace;
-              addr[2 * t2 + 1] = tok < p.tokens ? addr[2 * t2] + (kTileM / 2) * 4u : kNoPlace;
-            }
-            sum4_over_splits(addr, p.splits, sum);
-#pragma unroll
-            for (int t2 = 0; t2 < 2; ++t2) {
-              const int tok = token + t2 * step;
-              if (tok >= p.tokens) break;
-              const float g = __bfloat162float(__float2bfloat16_rn(sum[2 * t2]));
-              const float u = __bfloat162float(__float2bfloat16_rn(sum[2 * t2 + 1]));
-              out[(int64_t)tok * out_features + feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
-            }
-          }
-        }
-      } else if constexpr (kEpilogue == kEpilogueQkv) {
-        // The tile is one head of 128 dims; a thread owns dim `row` of it.  Per token of this CTA's share: add
-        // up the splits, round as the stored product would be, norm over the head, rotate with the partner dim
-        // (row ^ 64), store to q_out or to the token's cache slot.  The four epilogue warps meet at named
-        // barrier 1.
-        const GemmQkv& e = p.qkv;
-        float* red = reinterpret_cast<float*>(smem + GemmSmem<BN, kStages>::kReduce);      // [2][4] warp sums
-        float* xch = red + 8;                                                              // [2][128] normed values
-        const int head = tile;
-        const bool is_q = head < e.num_heads, is_k = !is_q && head < e.num_heads + e.num_kv_heads;
-        const int local = is_q ? head : (is_k ? head - e.num_heads : head - e.num_heads - e.num_kv_heads);
-        const bool normed = (is_q ? e.q_weight : (is_k ? e.k_weight : nullptr)) != nullptr;
-        const bool rotate = (is_q || is_k) && e.inv_freq != nullptr;
-        int it = 0;
-        for (int token = split; token < p.tokens; token += p.splits, ++it) {
-          const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-          const float sum = sum_over_splits(addr, p.splits);
-          float v = __bfloat162float(__float2bfloat16_rn(sum));
-          float* red_it = red + (it & 1) * 4;
-          float* xch_it = xch + (it & 1) * kTileM;
-          if (it > 0) {       // the first token's were fetched while the product ran
-            if (rotate) sincosf((float)e.positions[token] * qkv_freq, &qkv_sn, &qkv_co);
-            if (!is_q && e.slots != nullptr) qkv_slot = e.slots[token];
-          }
-          if (normed) {
-            const float ss = warp_sum(v * v);
-            if (lane == 0) red_it[warp & 3] = ss;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            const float total = red_it[0] + red_it[1] + red_it[2] + red_it[3];
-            v = v * rsqrtf(total / (float)kTileM + e.eps) * qkv_wd;
-          }
-          if (rotate) {
-            xch_it[row] = v;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            const float partner = xch_it[row ^ 64];
-            v = row < 64 ? v * qkv_co - partner * qkv_sn : v * qkv_co + partner * qkv_sn;
-          }
-          __nv_bfloat16* dst = nullptr;
-          if (is_q) {
-            dst = (__nv_bfloat16*)e.q_out + ((int64_t)token * e.num_heads + local) * kTileM;
-          } else if (e.slots != nullptr && e.k_cache != nullptr) {
-            const int64_t slot = qkv_slot;
-            if (slot >= e.num_pages * e.page_size) {
-              if (row == 0) set_status(p.status, kBadSlot);
-            } else if (slot >= 0) {
-              const int64_t page = slot / e.page_size, off = slot % e.page_size;
-              dst = (__nv_bfloat16*)(is_k ? e.k_cache : e.v_cache) +
-                    ((page * e.num_kv_heads + local) * e.page_size + off) * (int64_t)kTileM;
-            }
-          }
-          if (dst != nullptr) dst[row] = __float2bfloat16_rn(v);
-        }
-      } else if constexpr (kEpilogue == kEpilogueResidual) {
-        // hidden += the tile (rounded as the stored product would be); the new values' squares, summed over the
-        // tile's features, are this tile's share of each token's mean square.
-        float* red = reinterpret_cast<float*>(smem + GemmSmem<BN, kStages>::kReduce);      // [2][4] warp sums
-        const int feature = tile * kTileM + row;
-        int it = 0;
-        for (int token = split; token < p.tokens; token += p.splits, ++it) {
-          const uint32_t addr = smem_u32(smem) + (uint32_t)(token * kTileM + row) * 4u;
-          const float sum = sum_over_splits(addr, p.splits);
-          float h = 0.f;
-          if (feature < p.features) {
-            float* cell = p.residual.hidden + (int64_t)token * p.features + feature;
-            h = (it > 0 ? *cell : res_old) + __bfloat162float(__float2bfloat16_rn(sum));
-            *cell = h;
-          }
-          const float ss = warp_sum(h * h);
-          float* red_it = red + (it & 1) * 4;
-          if (lane == 0) red_it[warp & 3] = ss;
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (row == 0) p.residual.ssq[(int64_t)tile * p.tokens + token] = red_it[0] + red_it[1] + red_it[2] + red_it[3];
-        }
-      } else {
-        const int feature = tile * kTileM + row;
-        if (feature < p.features) {
-          for (int token = split; token < p.tokens; token += 4 * p.splits) {       // four tokens at a time
-            uint32_t addr[4];
-            float sum[4];
-#pragma unroll
-            for (int t4 = 0; t4 < 4; ++t4) {
-              const int tok = token + t4 * p.splits;
-              addr[t4] = tok < p.tokens ? smem_u32(smem) + (uint32_t)(tok * kTileM + row) * 4u : kNoPlace;
-            }
-            sum4_over_splits(addr, p.splits, sum);
-#pragma unroll
-            for (int t4 = 0; t4 < 4; ++t4) {
-              const int tok = token + t4 * p.splits;
-              if (tok < p.tokens) out[(int64_t)tok * p.features + feature] = from_float<OutT>(sum[t4]);
-            }
-          }
-        }
-      }
+  if (warp < 2) {
+    if (!ok) set_status(p.status, kWaitTimeout);
+    if (p.out != nullptr) {
+      cluster_sync_all();      // with warps 2-5: the partials are in place, then everybody is done reading
+      cluster_sync_all();
     }
-    cluster_sync_all();      // nobody leaves while a peer may still read its shared memory
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -582,24 +641,6 @@ int launch_bn(const CUtensorMap& w_map, const CUtensorMap& x_map, const GemmPara
   constexpr int kDefault = BN == 16 ? 4 : 3;
   const int64_t ctas = (int64_t)((p.features + kTileM - 1) / kTileM) * p.splits;
   const bool deep = BN > 16 && ctas <= 2 * sm_count();
-  const int forced = ring_stages();
-  if (forced == 2 || forced == 3) {         // measurement: the same ring for every epilogue
-#define AKV_FORCED(ST)                                                                                          \
-    switch (epilogue) {                                                                                         \
-      case kEpilogueGated:                                                                                      \
-        return launch_stages<BN, __nv_bfloat16, ST, kEpilogueGated, kNormedX>(w_map, x_map, p, stream);         \
-      case kEpilogueQkv:                                                                                        \
-        return launch_stages<BN, __nv_bfloat16, ST, kEpilogueQkv, kNormedX>(w_map, x_map, p, stream);           \
-      case kEpilogueResidual:                                                                                   \
-        if constexpr (kNormedX) return (int)cudaErrorInvalidValue;                                              \
-        else return launch_stages<BN, float, ST, kEpilogueResidual, false>(w_map, x_map, p, stream);            \
-      default:                                                                                                  \
-        return bf16_out ? launch_stages<BN, __nv_bfloat16, ST, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream) \
-                        : launch_stages<BN, float, ST, kEpiloguePlain, kNormedX>(w_map, x_map, p, stream);      \
-    }
-    if (forced == 2) { AKV_FORCED(2) } else { AKV_FORCED(3) }
-#undef AKV_FORCED
-  }
   switch (epilogue) {
     case kEpilogueGated:
       return launch_stages<BN, __nv_bfloat16, kDefault, kEpilogueGated, kNormedX>(w_map, x_map, p, stream);
