@@ -2,13 +2,13 @@
 // (cp.async.bulk.tensor, 128-byte swizzle, mbarrier completion, no multicast), scores and the weighted sum of
 // V run on mma.sync m16n8k16 with float32 accumulators, the softmax is an online float32 softmax in registers.
 //
-// Two kernels share the inner loop:
+// Two kernels:
 //   * prompt portions: one CTA per (query tile of up to 16 tokens, kv head); warp g owns q-head kvh*G + g, its
 //     16 MMA rows are the tile's tokens; the G warps share every K/V tile (one read per GQA group).
-//   * decoded tokens: one CTA per (token, kv head, key split); the MMA rows are the G q-heads of the group; four
-//     consumer warps take the CTA's 32-key blocks in turn and are combined in shared memory; 2, 4 or 8 key
-//     splits form a thread-block cluster and are merged through distributed shared memory (other split counts
-//     leave (acc, max, sum) partials for the merge kernel of paged_attention.cu).
+//   * decoded tokens: one CTA per (token, kv head, key split); the MMA rows are the G q-heads of the group; the
+//     consumer warps work on the same 32-key block together; 2, 4 or 8 key splits form a thread-block cluster
+//     and are merged through distributed shared memory (other split counts leave (acc, max, sum) partials for
+//     the merge kernel of paged_attention.cu).
 //
 // Same mathematics as the general kernel and as the reference (ampere_kv/kv_cache.py:76-94,
 // csrc/paged_decode.cu:166-243): score = q.k * scale, key j visible to the query at position t iff j <= t (and
@@ -191,14 +191,12 @@ __device__ __forceinline__ void process_block(const uint32_t (&q_frag)[D / 16][4
   }
 }
 
-// Shared-memory layout: [stage][K area | V area], each area KT * D * 2 bytes, then the mbarriers.  The first
-// bytes of the stage ring are reused for the cross-split merge once the key loop is over.
+// Shared-memory layout of the prompt kernel: [stage][K area | V area], each area KT * D * 2 bytes, then the
+// mbarriers.
 template <int D, int KT, int STAGES>
 struct Smem {
   static constexpr int kArea = KT * D * 2;
   static constexpr int kStage = 2 * kArea;
-  static constexpr int kMerge = 5 * 16 * (D + 2) * 4;   // per consumer warp (up to 4) and combined: 16 rows of (acc[D], max, sum)
-  static_assert(kMerge <= STAGES * kStage, "the merge buffer must fit in the stage ring");
   static constexpr int kBytes = STAGES * kStage + 2 * STAGES * 8 + 1024;   // + alignment slack
 };
 
@@ -344,12 +342,10 @@ __device__ __forceinline__ void merge_row_over_splits(uint32_t base, int splits,
 // barriers (decode at batch 64, 1,152 keys: 102 us with one producer, 184 us with four).
 constexpr int kProducers = 1;
 
-// Warps 0 .. consumers-1 compute (prompt kernel: warp g = q-head g of the group; decode kernel: every warp's
-// rows are the group's heads, the warps share out the key blocks); the last kProducers warps are the producers: they walk the block table and
-// keep the TMA ring full.  full[s]: the stage's bytes have landed; empty[s]: every consumer warp is done with the stage.
-// CLUSTER (decode only): the key splits of one (token, kv head) form a cluster; the partial results are merged
-// through distributed shared memory instead of a second kernel.
-template <int D, int KT, int STAGES, bool DECODE, bool CLUSTER, int WARPS, int MIN_CTAS>
+// The prompt kernel.  Warps 0 .. consumers-1 compute (warp g = q-head g of the group); the last kProducers warps
+// are the producers: they walk the block table and keep the TMA ring full.  full[s]: the stage's bytes have
+// landed; empty[s]: every consumer warp is done with the stage.
+template <int D, int KT, int STAGES, int WARPS, int MIN_CTAS>
 __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                                     const __grid_constant__ CUtensorMap v_map, TcParams tp) {
   const PagedAttentionParams& p = tp.p;
@@ -361,7 +357,7 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
   const int consumers = (int)(blockDim.x >> 5) - kProducers;
   const bool is_producer = warp >= consumers;
   const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads;
-  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int tile = blockIdx.x, kvh = blockIdx.y;
 
   pdl_launch_dependents();
   // a batch tile holds up to q_tile tokens; this kernel's CTAs take 16 of them each
@@ -376,24 +372,18 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
   const int q_len = p.cu_q[seq + 1] - seq_q0;
   const int tile_pos = ctx - q_len + (q0 - seq_q0);
 
-  const int pos_first = tile_pos, pos_last = DECODE ? tile_pos : tile_pos + nq - 1;
+  const int pos_first = tile_pos, pos_last = tile_pos + nq - 1;
   int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
   lo = lo / tp.box_rows * tp.box_rows;     // boxes start on box boundaries inside a page
   const int hi = pos_last + 1;
-  int range_lo = lo, range_hi = hi;
-  if (DECODE && p.num_splits > 1) {
-    int per = (hi - lo + p.num_splits - 1) / p.num_splits;
-    per = (per + KT - 1) / KT * KT;
-    range_lo = lo + split * per;
-    range_hi = min(hi, range_lo + per);
-  }
+  const int range_lo = lo, range_hi = hi;
   const int num_blocks = range_hi > range_lo ? (range_hi - range_lo + KT - 1) / KT : 0;
 
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], kProducers);
-      mbar_init(&empty[s], DECODE ? 1 : consumers);     // decode: a block belongs to one consumer warp
+      mbar_init(&empty[s], consumers);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -417,19 +407,13 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
                          smem + s * Smem<D, KT, STAGES>::kStage, &full[s], warp - consumers, kProducers);
     }
   } else {
-    // rows of this warp: prompt kernel = tokens of head (kvh*G + warp); decode kernel = heads of the group
+    // rows of this warp: the tile's tokens, of head (kvh*G + warp)
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = (lane >> 2) + 8 * r;
-      if (DECODE) {
-        row_token[r] = q0;
-        row_head[r] = kvh * G + row;
-        row_pos[r] = row < G ? tile_pos : -1;
-      } else {
-        row_token[r] = q0 + row;
-        row_head[r] = kvh * G + warp;
-        row_pos[r] = row < nq ? tile_pos + row : -1;
-      }
+      row_token[r] = q0 + row;
+      row_head[r] = kvh * G + warp;
+      row_pos[r] = row < nq ? tile_pos + row : -1;
     }
     // query fragments straight from global memory
     uint32_t q_frag[D / 16][4];
@@ -455,10 +439,9 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
     for (int v = 0; v < D / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
     const float scale_log2 = p.scale * kLog2e;
 
-    // Prompt kernel: every consumer warp (one q-head each) works on every block.  Decode kernel: the consumer
-    // warps take the blocks in turn (warp w: blocks w, w + consumers, ...) and are merged after the loop.
-    // A warp whose wait ran out keeps walking the loop (the consumers' barriers stay matched) but computes nothing.
-    for (int b = DECODE ? warp : 0; b < num_blocks; b += DECODE ? consumers : 1) {
+    // Every consumer warp (one q-head each) works on every block.  A warp whose wait ran out keeps walking the
+    // loop (the consumers' barriers stay matched) but computes nothing.
+    for (int b = 0; b < num_blocks; ++b) {
       const int s = b % STAGES;
       uint8_t* stage = smem + s * Smem<D, KT, STAGES>::kStage;
       if (ok && !mbar_wait(&full[s], (b / STAGES) & 1)) ok = false;
@@ -467,13 +450,8 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
       if (nvalid < KT) {
         // V rows past the end may hold anything (or were never loaded): make them zero before P.V reads them.
         // This only ever happens in a range's last block, so no later TMA load touches these rows.
-        if (DECODE) {
-          zero_v_rows<D, KT>(stage, nvalid, lane, 32);
-          __syncwarp();
-        } else {
-          zero_v_rows<D, KT>(stage, nvalid, tid, consumers * 32);
-          consumer_sync(consumers);
-        }
+        zero_v_rows<D, KT>(stage, nvalid, tid, consumers * 32);
+        consumer_sync(consumers);
       }
       if (ok)
         process_block<D, KT>(q_frag, smem_addr(stage), smem_addr(stage + KT * D * 2), key0, nvalid, row_pos,
@@ -489,83 +467,9 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
   }
   if (!ok && lane == 0) set_status(p.status, kWaitTimeout);
 
-  if (DECODE) {
-    // 1. the consumer warps of this CTA leave (acc, max, sum) of their rows in shared memory and are combined
-    __syncthreads();                      // the stage ring is idle: all loads have landed and been consumed
-    float* merge = reinterpret_cast<float*>(smem);
-    constexpr int kRow = D + 2;
-    if (!is_producer) {
-      float* mine = merge + (1 + warp) * 16 * kRow;
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + 8 * r;
-        if (row < G) {
-#pragma unroll
-          for (int v = 0; v < D / 8; ++v) {
-            const int col = v * 8 + (lane & 3) * 2;
-            mine[row * kRow + col] = ok ? o[v][2 * r] : 0.f;
-            mine[row * kRow + col + 1] = ok ? o[v][2 * r + 1] : 0.f;
-          }
-          if ((lane & 3) == 0) {
-            mine[row * kRow + D] = m[r];            // log2 units
-            mine[row * kRow + D + 1] = ok ? l[r] : 0.f;
-          }
-        }
-      }
-    }
-    __syncthreads();
-    for (int idx = tid; idx < G * kRow; idx += blockDim.x) {
-      const int row = idx / kRow, col = idx - row * kRow;
-      float mx = -CUDART_INF_F;
-      for (int w = 0; w < consumers; ++w) {
-        const float* part = merge + (1 + w) * 16 * kRow + row * kRow;
-        if (part[D + 1] > 0.f) mx = fmaxf(mx, part[D]);
-      }
-      float acc = 0.f;
-      if (col == D) {
-        acc = mx;
-      } else {
-        for (int w = 0; w < consumers; ++w) {
-          const float* part = merge + (1 + w) * 16 * kRow + row * kRow;
-          if (part[D + 1] > 0.f) acc += exp2f(part[D] - mx) * part[col];     // col == D + 1: the sums
-        }
-      }
-      merge[row * kRow + col] = acc;
-    }
-    __syncthreads();
-    // 2. across the key splits
-    if (CLUSTER) {
-      // after the cluster barrier the CTA of rank r merges rows r, r + splits, ... reading its peers' shared
-      // memory in split order
-      cluster_sync_all();
-      for (int row = split; row < G; row += p.num_splits) {
-        const uint32_t base = smem_addr(merge) + (uint32_t)(row * kRow) * 4u;
-        merge_row_over_splits<D>(base, p.num_splits, tid, blockDim.x,
-                                 (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D);
-      }
-      cluster_sync_all();                   // nobody leaves while a peer may still read its shared memory
-      return;
-    }
-    for (int idx = tid; idx < G * D; idx += blockDim.x) {
-      const int row = idx / D, d = idx - row * D;
-      const int64_t out_row = (int64_t)q0 * NH + kvh * G + row;
-      const float sum = merge[row * kRow + D + 1];
-      if (p.num_splits == 1) {
-        ((__nv_bfloat16*)p.out)[out_row * D + d] = __float2bfloat16_rn(sum > 0.f ? merge[row * kRow + d] / sum : 0.f);
-      } else {
-        float* part = p.partials + (out_row * p.num_splits + split) * (int64_t)kRow;
-        part[d] = merge[row * kRow + d];
-        if (d == 0) {
-          part[D] = merge[row * kRow + D] * kLn2;     // natural-log units, as the merge kernel expects
-          part[D + 1] = sum;
-        }
-      }
-    }
-    return;
-  }
   if (is_producer || !ok) return;
 
-  // prompt kernel: every warp writes its own head's rows
+  // every warp writes its own head's rows
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     if (row_pos[r] < 0) continue;
@@ -581,13 +485,12 @@ __global__ void __launch_bounds__(32 * (WARPS + kProducers), MIN_CTAS) attention
 }
 
 // ---------------------------------------------------------------------------------------------- decode, cooperative
-// Decoded tokens, second form: the four consumer warps of a CTA work on the SAME 32-key block, so a stage of the
+// Decoded tokens: the consumer warps of a CTA work on the SAME 32-key block, so a stage of the
 // TMA ring is held for a quarter of the time and the ring turns over four times faster (decode attention is bound
 // by how many bytes a CTA keeps in flight, not by arithmetic).  Warp w scores keys [8w, 8w + 8) of the block
 // (Q K^T, one 16 x 8 tile over all of D), the warps exchange their row maxima and their probabilities through
 // shared memory, then warp w accumulates P V for head dims [w D/4, (w + 1) D/4).  The MMA rows are the G q-heads
 // of the group, as before; 2, 4 or 8 key splits form a cluster and are merged through distributed shared memory.
-constexpr int kMaxCoopWarps = 4;
 constexpr int kPRow = 40;      // bf16 elements per row of the probability tile: 32 keys + padding against bank conflicts
 
 template <int D, int STAGES, int kCoopWarps>
@@ -927,12 +830,10 @@ bool cache_map(const void* base, int64_t rows, int head_dim, int box_rows, CUten
   return true;
 }
 
-constexpr int kDecodeConsumers = 4;
-
 template <int D, int KT, int STAGES, int WARPS, int MIN_CTAS>
 int launch_prompt(const PagedAttentionParams& p, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
                   cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<D, KT, STAGES, false, false, WARPS, MIN_CTAS>;
+  auto kernel = attention_tc_kernel<D, KT, STAGES, WARPS, MIN_CTAS>;
   constexpr int smem = Smem<D, KT, STAGES>::kBytes;
   static bool configured = false;
   if (!configured) {
