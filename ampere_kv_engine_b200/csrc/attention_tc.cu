@@ -297,6 +297,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
+// The meeting before a CTA leaves: it only has to know that its neighbours have read its shared memory (their
+// loads are complete when they arrive, since they have used the values).  Nothing is published, so the arrival does
+// not wait for this CTA's own global stores as a releasing arrival does.
+__device__ __forceinline__ void cluster_meet_to_leave() {
+  asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+  asm volatile("barrier.cluster.wait;" ::: "memory");
+}
 __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
@@ -763,7 +770,7 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
       merge_row_over_splits<D>(base, p.num_splits, tid, blockDim.x,
                                (__nv_bfloat16*)p.out + ((int64_t)q0 * NH + kvh * G + row) * D);
     }
-    cluster_sync_all();
+    cluster_meet_to_leave();      // nobody leaves while a peer may still read its shared memory
     return;
   }
   for (int idx = tid; idx < G * D; idx += blockDim.x) {

@@ -4,19 +4,21 @@
 // (padded to 16/32/64), so every byte of weight is read exactly once by one CTA and feeds a full-width
 // tcgen05.mma.  K is cut into 1/2/4/8 splits so that a thin output still occupies the whole GPU.  The CTAs of
 // one output tile form a thread-block cluster: each leaves its float32 partial tile in its own shared memory,
-// and after a cluster barrier every CTA adds up, in split order, a share of the tile read from its peers'
-// shared memory (distributed shared memory) and stores it, rounded once: a CTA owns the tokens split, split + S,
-// ... and fetches all their partial sums in ONE round trip (a round trip costs about a microsecond when every
-// CTA reduces at once, and at 32 tokens the token-by-token loop paid four).  With ``parts`` instead of ``out``
-// the float32 partial tiles are stored as they are, [splits, tokens, features].
+// and after a cluster barrier the CTA of split s adds up, in split order, the tokens s, s + S, ... of the tile
+// read from its peers' shared memory (distributed shared memory) and stores them, rounded once.  In that tail a
+// warp owns tokens and a lane four consecutive features: the partial sums arrive as 16-byte loads, as many under
+// way as the round trip (about a microsecond when every CTA reduces at once) is worth; a token's 128 features are
+// one warp's, so the epilogues that work across a tile (norm over a head, rotation, the sum of squares for the
+// next RMS norm) need shuffles only and no warp waits for another.  With ``parts`` instead of ``out`` the float32
+// partial tiles are stored as they are, [splits, tokens, features].
 //
 // One CTA = 6 warps: warp 0 issues the TMA loads (128-byte swizzled tiles of 64 K-elements, a 4-stage ring
 // guarded by full/empty mbarriers, no multicast), warp 1 allocates TMEM and issues tcgen05.mma (one thread,
 // accumulator in TMEM, tcgen05.commit frees each stage and finally signals the epilogue), warps 2-5 read the
 // accumulator with tcgen05.ld.  Two or three CTAs share an SM, so one CTA's set-up and epilogue overlap the
 // others' streaming.  It replaces the library GEMMs the reference calls for its
-// projections (ampere_kv/runner.py:64-66, 165, 174-177, 297) when the batch is small; large batches (prompts)
-// stay on the library GEMM.
+// projections (ampere_kv/runner.py:64-66, 165, 174-177, 297) for up to 64 tokens; larger batches (prompts) stay
+// on the library GEMM.
 //
 // Every wait is bounded; a wait that runs out sets kWaitTimeout in the status word, and the CTA still frees
 // its TMEM and leaves.
@@ -116,11 +118,7 @@ struct GemmSmem {
   static constexpr int kB = BN * kTileK * 2;
   static constexpr int kStage = kA + kB;
   static constexpr int kReduce = BN * kTileM * 4;                      // float32 partial tile, reuses the stages
-  // behind it, for the epilogues that work across a tile's features: this CTA's own tokens' values
-  // [tokens][128], then per token four warp sums, the position and the cache slot (at most BN tokens: one split)
-  static constexpr int kOwnScratch = BN * (kTileM + 8) * 4;
   static_assert(kReduce <= kStages * kStage, "the partial tile must fit in the stage ring");
-  static constexpr bool kOwnFits = kReduce + kOwnScratch <= kStages * kStage;
   static constexpr int kBars = (2 * kStages + 1) * 8 + 16;             // barriers, TMEM base
   static constexpr int kBytes = kStages * kStage + kBars + 64 * 4 + 1024;   // + inverse RMS per token (kNormedX)
 };
@@ -129,44 +127,82 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
+// The meeting before a CTA leaves: it only has to know that its neighbours have read its shared memory (their
+// loads are complete when they arrive, since they have used the values).  Nothing is published, so the arrival does
+// not wait for this CTA's own global stores as a releasing arrival does.
+__device__ __forceinline__ void cluster_meet_to_leave() {
+  asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+  asm volatile("barrier.cluster.wait;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Sums over the cluster's CTAs (one per K split, in split order) of kPlaces floats of the partial tiles, every load
-// issued before the first is used: ONE round trip through distributed shared memory (about a microsecond when all
-// CTAs reduce at once), however many tokens this CTA owns.  offset[i] is the float's byte offset in the partial
-// tile, or kNoPlace.
+// Sums over the cluster's CTAs (one per K split, in split order) of kPlaces groups of four consecutive floats of
+// the partial tiles, every load issued before the first is used: ONE round trip through distributed shared
+// memory (about a microsecond when all CTAs reduce at once).  offset[i] is the group's byte offset in the partial
+// tile (a multiple of 16), or kNoPlace.
 constexpr uint32_t kNoPlace = 0xffffffffu;
 template <int kPlaces, int S>
-__device__ __forceinline__ void gather_sums(uint32_t tile_addr, const uint32_t (&offset)[kPlaces], float (&sum)[kPlaces]) {
+__device__ __forceinline__ void gather_sums(uint32_t tile_addr, const uint32_t (&offset)[kPlaces], float4 (&sum)[kPlaces]) {
   uint32_t peer[S];
 #pragma unroll
   for (int s = 0; s < S; ++s)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[s]) : "r"(tile_addr), "r"((uint32_t)s));
-  float v[kPlaces][S];
+  float4 v[kPlaces][S];
 #pragma unroll
   for (int i = 0; i < kPlaces; ++i)
 #pragma unroll
     for (int s = 0; s < S; ++s) {
-      v[i][s] = 0.f;
+      v[i][s] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (offset[i] != kNoPlace)
-        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[i][s]) : "r"(peer[s] + offset[i]) : "memory");
+        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v[i][s].x), "=f"(v[i][s].y), "=f"(v[i][s].z), "=f"(v[i][s].w)
+                     : "r"(peer[s] + offset[i])
+                     : "memory");
     }
 #pragma unroll
   for (int i = 0; i < kPlaces; ++i) {
     sum[i] = v[i][0];
 #pragma unroll
-    for (int s = 1; s < S; ++s) sum[i] += v[i][s];
+    for (int s = 1; s < S; ++s) {
+      sum[i].x += v[i][s].x;
+      sum[i].y += v[i][s].y;
+      sum[i].z += v[i][s].z;
+      sum[i].w += v[i][s].w;
+    }
   }
 }
+
+// (sin a, cos a, sin b, cos b).  Not inlined: the epilogue needs it in two places, and its code is long.
+__device__ __noinline__ float4 sincos_pair(float a, float b) {
+  float4 r;
+  sincosf(a, &r.x, &r.y);
+  sincosf(b, &r.z, &r.w);
+  return r;
+}
+// Sines and cosines of a token's rotation for the four dims of each lane (dims 4 * lane + i, frequencies
+// 4 * (lane & 15) + i): lane j computes the angles of frequencies 2j and 2j + 1 (`freq2`), the lanes that need
+// them fetch them from there, so that a warp computes each of the head's 64 angles once.
+__device__ __forceinline__ void rotation_of(float pos, float2 freq2, float4* sn, float4* co) {
+  const float4 mine = sincos_pair(pos * freq2.x, pos * freq2.y);
+  const int src = 2 * (threadIdx.x & 15);
+  sn->x = __shfl_sync(0xffffffffu, mine.x, src);
+  co->x = __shfl_sync(0xffffffffu, mine.y, src);
+  sn->y = __shfl_sync(0xffffffffu, mine.z, src);
+  co->y = __shfl_sync(0xffffffffu, mine.w, src);
+  sn->z = __shfl_sync(0xffffffffu, mine.x, src + 1);
+  co->z = __shfl_sync(0xffffffffu, mine.y, src + 1);
+  sn->w = __shfl_sync(0xffffffffu, mine.z, src + 1);
+  co->w = __shfl_sync(0xffffffffu, mine.w, src + 1);
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 template <int BN, typename OutT, int kStages, int kEpilogue, bool kNormedX>
 __global__ void __launch_bounds__(192, 3)
 small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                     GemmParams p) {
-  static_assert((kEpilogue != kEpilogueQkv && kEpilogue != kEpilogueResidual) || GemmSmem<BN, kStages>::kOwnFits,
-                "the partial tile and the epilogue's scratch must fit in the stage ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * GemmSmem<BN, kStages>::kStage);
@@ -203,9 +239,15 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
   bool ok = true;
-  float qkv_wd = 1.f, qkv_freq = 0.f, qkv_sn = 0.f, qkv_co = 1.f;     // kEpilogueQkv: fetched ahead of the product
+  // In the tail a warp owns tokens and a lane four consecutive features of the tile (rows 4 * lane .. + 3).  Fetched
+  // ahead of the product, kEpilogueQkv: the norm weights and rotation frequencies of the lane's dims, position and
+  // cache slot of the warp's tokens (lane i holds those of the warp's i-th token), sine and cosine for its first.
+  float4 qkv_w = make_float4(1.f, 1.f, 1.f, 1.f);
+  float2 qkv_f = make_float2(0.f, 0.f);      // rotation frequencies 2 * lane and 2 * lane + 1
+  float4 qkv_sn = make_float4(0.f, 0.f, 0.f, 0.f), qkv_co = make_float4(1.f, 1.f, 1.f, 1.f);
+  int qkv_pos = 0;
   int64_t qkv_slot = -1;
-  float res_old = 0.f;                                                 // kEpilogueResidual: likewise
+  float4 res_old = make_float4(0.f, 0.f, 0.f, 0.f);     // kEpilogueResidual: the stream's old values, first token
 
   if (warp == 0) {
     // The weights do not depend on the kernel before this one: fill the ring's weight halves first, then wait
@@ -264,20 +306,6 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   } else {
     // epilogue: warp (2..5) reads the TMEM lanes of its quarter; lane = feature, column = token
     const int quarter = warp & 3;
-    if constexpr (kEpilogue == kEpilogueQkv) {
-      // while the product runs: what the first token of this CTA's share needs besides the product (its angle's
-      // sine and cosine, its cache slot, this dim's norm weight).  None of it comes from the previous kernel.
-      const GemmQkv& e = p.qkv;
-      const int row = quarter * 32 + lane;
-      const bool is_q = tile < e.num_heads, is_k = !is_q && tile < e.num_heads + e.num_kv_heads;
-      const float* w = is_q ? e.q_weight : (is_k ? e.k_weight : nullptr);
-      qkv_wd = w != nullptr ? w[row] : 1.f;
-      qkv_freq = ((is_q || is_k) && e.inv_freq != nullptr) ? e.inv_freq[row & 63] : 0.f;
-      if (split < p.tokens) {
-        sincosf((float)e.positions[split] * qkv_freq, &qkv_sn, &qkv_co);
-        if (!is_q && e.slots != nullptr) qkv_slot = e.slots[split];
-      }
-    }
     if constexpr (kNormedX) {
       // The token operand is the RMS norm of the residual stream, made here: x = hidden * inv_rms * weight,
       // rounded to bfloat16 and laid out as the TMA would (rows of 128 bytes, 16-byte chunk c of row r at
@@ -327,12 +355,29 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         if (lane == 0) mbar_arrive(&full[s]);
       }
     }
+    if constexpr (kEpilogue == kEpilogueQkv) {
+      // while the product runs (and after this warp's part in making the token operand, which the product waits
+      // for): what the tail needs besides the product.  None of it comes from the previous kernel.
+      const GemmQkv& e = p.qkv;
+      const bool is_q = tile < e.num_heads, is_k = !is_q && tile < e.num_heads + e.num_kv_heads;
+      const float* w = is_q ? e.q_weight : (is_k ? e.k_weight : nullptr);
+      if (w != nullptr) qkv_w = *reinterpret_cast<const float4*>(w + 4 * lane);
+      const bool rotate = (is_q || is_k) && e.inv_freq != nullptr;
+      if (rotate) qkv_f = *reinterpret_cast<const float2*>(e.inv_freq + 2 * lane);
+      const int mine = split + (quarter + 4 * lane) * p.splits;       // the warp's lane-th token
+      if (mine < p.tokens) {
+        qkv_pos = e.positions[mine];
+        if (!is_q && e.slots != nullptr) qkv_slot = e.slots[mine];
+      }
+      if (rotate && split + quarter * p.splits < p.tokens)      // the warp has a first token
+        rotation_of((float)__shfl_sync(0xffffffffu, qkv_pos, 0), qkv_f, &qkv_sn, &qkv_co);
+    }
     if constexpr (kEpilogue == kEpilogueResidual) {
-      // the residual stream's old value for the first token of this CTA's share, fetched while the product runs
+      // the residual stream's old values for the warp's first token, fetched while the product runs
       if constexpr (!kNormedX) pdl_wait();
-      const int feature = tile * kTileM + quarter * 32 + lane;
-      if (split < p.tokens && feature < p.features)
-        res_old = p.residual.hidden[(int64_t)split * p.features + feature];
+      const int token = split + quarter * p.splits, feature = tile * kTileM + 4 * lane;
+      if (token < p.tokens && (p.features & 3) == 0 && feature < p.features)
+        res_old = *reinterpret_cast<const float4*>(p.residual.hidden + (int64_t)token * p.features + feature);
     }
     // The tail runs once per CTA: its loops over token columns are not unrolled further than they must be (measured:
     // fetching the instructions of a fully unrolled copy of 64 columns took 4 us, executing them 0.5 us).
@@ -341,8 +386,6 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     float* reduce = reinterpret_cast<float*>(smem);     // [token][128 features]; the stages are drained by then
     float* part_out = p.parts ? p.parts + (int64_t)split * p.tokens * p.features : nullptr;
     OutT* out = reinterpret_cast<OutT*>(p.out);
-    const float first_sn = qkv_sn, first_co = qkv_co;
-    const int64_t first_slot = qkv_slot;
     if (!mbar_wait(acc_ready, 0)) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     {
@@ -375,182 +418,151 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // every CTA of the tile has its partial in shared memory: add them up across the cluster, in split order
       cluster_sync_all();
       const uint32_t tile_addr = smem_u32(smem);
-      // This CTA owns the tokens split, split + S, ...: at most BN / S of them.  Their sums over the splits are
-      // gathered in one round trip, whatever their number; what follows works on registers and on this CTA's
-      // own shared memory.
-      auto tail = [&](auto splits_tag, auto own_tag) {
+      // This CTA owns the tokens split, split + S, ...; warp w of the four takes the w-th, (w + 4)-th, ... of them,
+      // U at a time with U * S loads of 16 bytes under way, and a lane four consecutive features: a token's 128
+      // features are one warp's, so the norm over a head and the sum of squares are warp sums, the rotation's
+      // partner dim (+-64) sits 16 lanes away, and no warp waits for another.
+      auto tail = [&](auto splits_tag) {
         constexpr int S = decltype(splits_tag)::value;
-        constexpr int kOwn = decltype(own_tag)::value;       // places (tokens; gate and up rows count apart) per thread
-        float* own = reinterpret_cast<float*>(smem + GemmSmem<BN, kStages>::kReduce);      // [kOwn][128]
-        [[maybe_unused]] float* red = own + kOwn * kTileM;                                 // [kOwn][8]
-        uint32_t off[kOwn];
-        float sum[kOwn];
-        if constexpr (kEpilogue == kEpilogueGated) {
-          // rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64 outputs.  A thread takes
-          // output j of every other token of this CTA's share and adds up both of its rows.
-          constexpr int kTok = kOwn / 2;
-          const int j = row & 63, half = row >> 6;
-          const int out_features = p.features / 2;
-          const int gated_feature = tile * (kTileM / 2) + j;
-#pragma unroll
-          for (int i = 0; i < kTok; ++i) {
-            const int tok = split + half * S + i * 2 * S;
-            const bool there = tok < p.tokens && gated_feature < out_features;
-            off[2 * i] = there ? (uint32_t)(tok * kTileM + j) * 4u : kNoPlace;
-            off[2 * i + 1] = there ? off[2 * i] + (kTileM / 2) * 4u : kNoPlace;
-          }
-          gather_sums<kOwn, S>(tile_addr, off, sum);
-#pragma unroll
-          for (int i = 0; i < kTok; ++i) {
-            const int tok = split + half * S + i * 2 * S;
-            const float g = __bfloat162float(__float2bfloat16_rn(sum[2 * i]));
-            const float u = __bfloat162float(__float2bfloat16_rn(sum[2 * i + 1]));
-            if (off[2 * i] != kNoPlace)
-              out[(int64_t)tok * out_features + gated_feature] = from_float<OutT>(silu_mul_value<OutT>(g, u));
-          }
-        } else if constexpr (kEpilogue == kEpilogueQkv) {
-          // The tile is one head of 128 dims; a thread owns dim `row` of it.  Per token of this CTA's share: the
-          // sum rounded as the stored product would be, norm over the head, rotation with the partner dim
-          // (row ^ 64), store to q_out or to the token's cache slot.  The four epilogue warps meet at named
-          // barrier 1, twice for all tokens together.
-          const GemmQkv& e = p.qkv;
-          const int head = tile;
-          const bool is_q = head < e.num_heads, is_k = !is_q && head < e.num_heads + e.num_kv_heads;
-          const int local = is_q ? head : (is_k ? head - e.num_heads : head - e.num_heads - e.num_kv_heads);
-          const bool normed = (is_q ? e.q_weight : (is_k ? e.k_weight : nullptr)) != nullptr;
-          const bool rotate = (is_q || is_k) && e.inv_freq != nullptr;
-          // thread o < kOwn fetches the position and the slot of owned token o (the first one's are known already)
-          int my_pos = 0;
-          int64_t my_slot = -1;
-          {
-            const int tok = split + row * S;
-            if (row > 0 && row < kOwn && tok < p.tokens) {
-              my_pos = e.positions[tok];
-              if (!is_q && e.slots != nullptr) my_slot = e.slots[tok];
-            }
-          }
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o)
-            off[o] = split + o * S < p.tokens ? (uint32_t)((split + o * S) * kTileM + row) * 4u : kNoPlace;
-          gather_sums<kOwn, S>(tile_addr, off, sum);
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o) sum[o] = __bfloat162float(__float2bfloat16_rn(sum[o]));
-          if (normed) {
-#pragma unroll
-            for (int o = 0; o < kOwn; ++o) {
-              const float ss = warp_sum(sum[o] * sum[o]);
-              if (lane == 0) red[o * 8 + (warp & 3)] = ss;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-            for (int o = 0; o < kOwn; ++o) {
-              const float total = red[o * 8] + red[o * 8 + 1] + red[o * 8 + 2] + red[o * 8 + 3];
-              sum[o] = sum[o] * rsqrtf(total / (float)kTileM + e.eps) * qkv_wd;
-            }
-          }
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o) own[o * kTileM + row] = sum[o];
-          if (row > 0 && row < kOwn) {
-            reinterpret_cast<int*>(red)[row * 8 + 4] = my_pos;
-            *reinterpret_cast<int64_t*>(red + row * 8 + 6) = my_slot;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          // token by token from shared memory, so that one copy of the sine and cosine serves them all
+        constexpr int U = 8 / S;
+        [[maybe_unused]] const int feature = tile * kTileM + 4 * lane;      // the lane's first feature
+        [[maybe_unused]] const bool whole = (p.features & 3) == 0;          // output rows start on 16-byte boundaries
+        int round = 0;
 #pragma unroll 1
-          for (int o = 0; o < kOwn; ++o) {
-            const int tok = split + o * S;
+        for (int o = quarter; split + o * S < p.tokens; o += 4 * U, ++round) {
+          uint32_t off[U];
+          float4 sum[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int tok = split + (o + 4 * u) * S;
+            off[u] = tok < p.tokens ? (uint32_t)(tok * kTileM + 4 * lane) * 4u : kNoPlace;
+          }
+          gather_sums<U, S>(tile_addr, off, sum);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int tok = split + (o + 4 * u) * S;
             if (tok >= p.tokens) break;
-            float v = own[o * kTileM + row];
-            float sn = first_sn, co = first_co;
-            int64_t slot = first_slot;
-            if (o > 0) {       // the first token's were fetched while the product ran
-              if (rotate) sincosf((float)reinterpret_cast<const int*>(red)[o * 8 + 4] * qkv_freq, &sn, &co);
-              slot = *reinterpret_cast<const int64_t*>(red + o * 8 + 6);
-            }
-            if (rotate) {
-              const float partner = own[o * kTileM + (row ^ 64)];
-              v = row < 64 ? v * co - partner * sn : v * co + partner * sn;
-            }
-            __nv_bfloat16* dst = nullptr;
-            if (is_q) {
-              dst = (__nv_bfloat16*)e.q_out + ((int64_t)tok * e.num_heads + local) * kTileM;
-            } else if (e.slots != nullptr && e.k_cache != nullptr) {
-              if (slot >= e.num_pages * e.page_size) {
-                if (row == 0) set_status(p.status, kBadSlot);
-              } else if (slot >= 0) {
-                const int64_t page = slot / e.page_size, in_page = slot % e.page_size;
-                dst = (__nv_bfloat16*)(is_k ? e.k_cache : e.v_cache) +
-                      ((page * e.num_kv_heads + local) * e.page_size + in_page) * (int64_t)kTileM;
+            const float4 v = sum[u];
+            if constexpr (kEpilogue == kEpilogueGated) {
+              // rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64 outputs: lanes 0-15
+              // hold four gates each, lane + 16 the four ups that go with them
+              const float u0 = __shfl_xor_sync(0xffffffffu, v.x, 16), u1 = __shfl_xor_sync(0xffffffffu, v.y, 16);
+              const float u2 = __shfl_xor_sync(0xffffffffu, v.z, 16), u3 = __shfl_xor_sync(0xffffffffu, v.w, 16);
+              const int out_features = p.features / 2;
+              const int gated_feature = tile * (kTileM / 2) + 4 * lane;
+              if (lane < 16 && gated_feature < out_features) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(silu_mul_value<OutT>(bf16_round(v.x), bf16_round(u0)),
+                                                          silu_mul_value<OutT>(bf16_round(v.y), bf16_round(u1)));
+                __nv_bfloat162 hi = __floats2bfloat162_rn(silu_mul_value<OutT>(bf16_round(v.z), bf16_round(u2)),
+                                                          silu_mul_value<OutT>(bf16_round(v.w), bf16_round(u3)));
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)tok * out_features + gated_feature) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              }
+            } else if constexpr (kEpilogue == kEpilogueQkv) {
+              // The tile is one head of 128 dims.  The sums rounded as the stored product would be, norm over the
+              // head, rotation with the partner dim, store to q_out or to the token's cache slot.
+              const GemmQkv& e = p.qkv;
+              const int head = tile;
+              const bool is_q = head < e.num_heads, is_k = !is_q && head < e.num_heads + e.num_kv_heads;
+              const int local = is_q ? head : (is_k ? head - e.num_heads : head - e.num_heads - e.num_kv_heads);
+              const bool normed = (is_q ? e.q_weight : (is_k ? e.k_weight : nullptr)) != nullptr;
+              const bool rotate = (is_q || is_k) && e.inv_freq != nullptr;
+              float x[4] = {bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w)};
+              if (normed) {
+                const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+                const float inv = rsqrtf(ss / (float)kTileM + e.eps);
+                x[0] *= inv * qkv_w.x;
+                x[1] *= inv * qkv_w.y;
+                x[2] *= inv * qkv_w.z;
+                x[3] *= inv * qkv_w.w;
+              }
+              const int nth = round * U + u;      // this token is the warp's nth
+              if (rotate) {
+                float4 sn = qkv_sn, co = qkv_co;
+                if (nth > 0)      // the first token's were computed while the product ran
+                  rotation_of((float)__shfl_sync(0xffffffffu, qkv_pos, nth), qkv_f, &sn, &co);
+                const float sign = lane < 16 ? -1.f : 1.f;      // dims below 64: x cos - partner sin
+                const float p0 = __shfl_xor_sync(0xffffffffu, x[0], 16), p1 = __shfl_xor_sync(0xffffffffu, x[1], 16);
+                const float p2 = __shfl_xor_sync(0xffffffffu, x[2], 16), p3 = __shfl_xor_sync(0xffffffffu, x[3], 16);
+                x[0] = x[0] * co.x + sign * p0 * sn.x;
+                x[1] = x[1] * co.y + sign * p1 * sn.y;
+                x[2] = x[2] * co.z + sign * p2 * sn.z;
+                x[3] = x[3] * co.w + sign * p3 * sn.w;
+              }
+              __nv_bfloat16* dst = nullptr;
+              if (is_q) {
+                dst = (__nv_bfloat16*)e.q_out + ((int64_t)tok * e.num_heads + local) * kTileM;
+              } else if (e.slots != nullptr && e.k_cache != nullptr) {
+                const int64_t slot = __shfl_sync(0xffffffffu, qkv_slot, nth);
+                if (slot >= e.num_pages * e.page_size) {
+                  if (lane == 0) set_status(p.status, kBadSlot);
+                } else if (slot >= 0) {
+                  const int64_t page = slot / e.page_size, in_page = slot % e.page_size;
+                  dst = (__nv_bfloat16*)(is_k ? e.k_cache : e.v_cache) +
+                        ((page * e.num_kv_heads + local) * e.page_size + in_page) * (int64_t)kTileM;
+                }
+              }
+              if (dst != nullptr) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+                *reinterpret_cast<uint2*>(dst + 4 * lane) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              }
+            } else if constexpr (kEpilogue == kEpilogueResidual) {
+              // hidden += the tile (rounded as the stored product would be); the new values' squares, summed over
+              // the tile's features, are this tile's share of the token's mean square.
+              float* cell = p.residual.hidden + (int64_t)tok * p.features + feature;
+              float h[4] = {0.f, 0.f, 0.f, 0.f};
+              const float add[4] = {bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w)};
+              if (whole && feature < p.features) {
+                const float4 old = (round == 0 && u == 0) ? res_old : *reinterpret_cast<const float4*>(cell);
+                h[0] = old.x + add[0];
+                h[1] = old.y + add[1];
+                h[2] = old.z + add[2];
+                h[3] = old.w + add[3];
+                *reinterpret_cast<float4*>(cell) = make_float4(h[0], h[1], h[2], h[3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  if (feature + i < p.features) {
+                    h[i] = cell[i] + add[i];
+                    cell[i] = h[i];
+                  }
+              }
+              const float ss = warp_sum(h[0] * h[0] + h[1] * h[1] + h[2] * h[2] + h[3] * h[3]);
+              if (lane == 0) p.residual.ssq[(int64_t)tile * p.tokens + tok] = ss;
+            } else {
+              OutT* dst = out + (int64_t)tok * p.features + feature;
+              const float x[4] = {v.x, v.y, v.z, v.w};
+              if (whole && feature < p.features) {
+                if constexpr (sizeof(OutT) == 4) {
+                  *reinterpret_cast<float4*>(dst) = v;
+                } else {
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+                  *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  if (feature + i < p.features) dst[i] = from_float<OutT>(x[i]);
               }
             }
-            if (dst != nullptr) dst[row] = __float2bfloat16_rn(v);
-          }
-        } else if constexpr (kEpilogue == kEpilogueResidual) {
-          // hidden += the tile (rounded as the stored product would be); the new values' squares, summed over the
-          // tile's features, are this tile's share of each token's mean square.
-          float old[kOwn];
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o) {
-            const int tok = split + o * S;
-            const bool there = tok < p.tokens && feature < p.features;
-            off[o] = there ? (uint32_t)(tok * kTileM + row) * 4u : kNoPlace;
-            old[o] = 0.f;
-            if (there) old[o] = o == 0 ? res_old : p.residual.hidden[(int64_t)tok * p.features + feature];
-          }
-          gather_sums<kOwn, S>(tile_addr, off, sum);
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o) {
-            const int tok = split + o * S;
-            float h = 0.f;
-            if (off[o] != kNoPlace) {
-              h = old[o] + __bfloat162float(__float2bfloat16_rn(sum[o]));
-              p.residual.hidden[(int64_t)tok * p.features + feature] = h;
-            }
-            const float ss = warp_sum(h * h);
-            if (lane == 0) red[o * 8 + (warp & 3)] = ss;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (row < kOwn && split + row * S < p.tokens)
-            p.residual.ssq[(int64_t)tile * p.tokens + split + row * S] =
-                red[row * 8] + red[row * 8 + 1] + red[row * 8 + 2] + red[row * 8 + 3];
-        } else {
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o)
-            off[o] = (split + o * S < p.tokens && feature < p.features)
-                         ? (uint32_t)((split + o * S) * kTileM + row) * 4u : kNoPlace;
-          gather_sums<kOwn, S>(tile_addr, off, sum);
-#pragma unroll
-          for (int o = 0; o < kOwn; ++o)
-            if (off[o] != kNoPlace)
-              out[(int64_t)(split + o * S) * p.features + feature] = from_float<OutT>(sum[o]);
-        }
-      };
-      // the usual decode step has no more tokens than splits: one token per CTA, and code that knows it
-      auto tail_of = [&](auto splits_tag) {
-        constexpr int S = decltype(splits_tag)::value;
-        constexpr int kFew = kEpilogue == kEpilogueGated ? 2 : 1;
-        if constexpr (BN / S > kFew) {
-          if (p.tokens <= kFew * S) {
-            tail(splits_tag, std::integral_constant<int, kFew>{});
-            return;
           }
         }
-        tail(splits_tag, std::integral_constant<int, BN / S>{});
       };
       switch (p.splits) {
-        case 1: tail_of(std::integral_constant<int, 1>{}); break;
-        case 2: tail_of(std::integral_constant<int, 2>{}); break;
-        case 4: tail_of(std::integral_constant<int, 4>{}); break;
-        default: tail_of(std::integral_constant<int, 8>{}); break;
+        case 1: tail(std::integral_constant<int, 1>{}); break;
+        case 2: tail(std::integral_constant<int, 2>{}); break;
+        case 4: tail(std::integral_constant<int, 4>{}); break;
+        default: tail(std::integral_constant<int, 8>{}); break;
       }
-      cluster_sync_all();      // nobody leaves while a peer may still read its shared memory
+      cluster_meet_to_leave();      // nobody leaves while a peer may still read its shared memory
     }
   }
   if (warp < 2) {
     if (!ok) set_status(p.status, kWaitTimeout);
     if (p.out != nullptr) {
       cluster_sync_all();      // with warps 2-5: the partials are in place, then everybody is done reading
-      cluster_sync_all();
+      cluster_meet_to_leave();
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

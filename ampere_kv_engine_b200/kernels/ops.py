@@ -313,9 +313,10 @@ def _operand(x, weight: torch.Tensor):
     return None, {"nx_hidden": h, "nx_ssq": x.ssq, "nx_weight": x.weight, "nx_eps": x.eps}, True
 
 
-#: products of at most this many bfloat16 tokens go through the package's own tcgen05 kernel (the kernel takes
-#: up to 64; measured on B200 the library is faster from 33 tokens on)
-SMALL_M_LIMIT = 32
+#: products of at most this many bfloat16 tokens go through the package's own tcgen05 kernel: all it takes.
+#: Measured per decode step on B200 against the library product with the row-wise kernels around it: 5.08 against
+#: 5.21 ms at 40 tokens, 5.21 against 5.36 ms at 56, 5.17 against 5.37 ms at 64.
+SMALL_M_LIMIT = 64
 use_small_m_gemm = True
 #: up to this many tokens a decode branch adds to the residual stream inside its last product and the next product
 #: applies the norm to its own token operand.  Every CTA of that product re-reads the float32 stream for its K
