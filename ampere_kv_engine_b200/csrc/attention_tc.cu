@@ -313,16 +313,19 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank
 }
 
 // Merge of one output row across the key splits of a cluster (at most 8 CTAs): row layout in every CTA's shared
-// memory is (acc[D], max in log2 units, sum).  All loads of a step are issued before the first is used (one round
-// trip through distributed shared memory per step, not one per split); the sums run in split order.
+// memory is (acc[D], max in log2 units, sum).  A thread's first dim is fetched together with the maxima and the
+// sums, all loads issued before the first is used: one round trip through distributed shared memory for the row
+// when the CTA has a thread per dim, not one for the weights and another for the values.  The sums run in split
+// order.
 template <int D>
 __device__ __forceinline__ void merge_row_over_splits(uint32_t base, int splits, int tid, int nthreads,
                                                       __nv_bfloat16* out) {
-  float mv[8], lv[8];
+  float mv[8], lv[8], v[8];
 #pragma unroll
   for (int s = 0; s < 8; ++s) {
     mv[s] = s < splits ? ld_peer_smem(base + D * 4u, (uint32_t)s) : -CUDART_INF_F;
     lv[s] = s < splits ? ld_peer_smem(base + (D + 1) * 4u, (uint32_t)s) : 0.f;
+    v[s] = (s < splits && tid < D) ? ld_peer_smem(base + tid * 4u, (uint32_t)s) : 0.f;
   }
   float mx = -CUDART_INF_F;
 #pragma unroll
@@ -335,9 +338,10 @@ __device__ __forceinline__ void merge_row_over_splits(uint32_t base, int splits,
     den += w[s] * lv[s];
   }
   for (int d = tid; d < D; d += nthreads) {
-    float v[8];
+    if (d != tid) {
 #pragma unroll
-    for (int s = 0; s < 8; ++s) v[s] = s < splits ? ld_peer_smem(base + d * 4u, (uint32_t)s) : 0.f;
+      for (int s = 0; s < 8; ++s) v[s] = s < splits ? ld_peer_smem(base + d * 4u, (uint32_t)s) : 0.f;
+    }
     float num = 0.f;
 #pragma unroll
     for (int s = 0; s < 8; ++s) num += w[s] * v[s];

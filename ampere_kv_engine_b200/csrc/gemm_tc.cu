@@ -311,7 +311,28 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // rounded to bfloat16 and laid out as the TMA would (rows of 128 bytes, 16-byte chunk c of row r at
       // c ^ (r & 7)).  Warp q makes the K blocks kb = q, q + 4, ...: up to four blocks are under way at a time.
       const GemmNormedX& nx = p.normed;
+      // A stage must always be written by the same warp, so that the warp sees each of the stage's "empty" phases
+      // in turn (a parity wait two phases late answers wrongly): with three stages three warps work.
+      constexpr int kXWarps = kStages < 4 ? kStages : 4;
+      // The product cannot start before its first token tiles exist, and they wait for two things from memory one
+      // after the other: the sums of squares (for the scale), then the rows.  With few tokens (two 16-byte pieces
+      // of a tile per lane, both of the same 8 K elements) a warp fetches the rows of its first K block together
+      // with the sums of squares, and the norm weights, which are the model's, before it waits for the previous
+      // kernel at all.  (Fetching the rows of its second block as well was measured slower: 3.41 against 3.29 ms
+      // a step at batch 8.)
+      const bool pre = p.tokens * 8 <= 64 && quarter < kXWarps && quarter < num_kb;
+      float pre_h[2][8], pre_w[8];
+      auto piece_k0 = [&](int kb, int task) { return (kb_begin + kb) * kTileK + (task & 7) * 8; };
+      if (pre && piece_k0(quarter, lane) < p.k) load8<float>(nx.weight + piece_k0(quarter, lane), pre_w);
       pdl_wait();      // hidden and its sums of squares come from the kernels before this one
+      if (pre) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int task = lane + 32 * j;
+          if (task < p.tokens * 8 && piece_k0(quarter, task) < p.k)
+            load8<float>(nx.hidden + (int64_t)(task >> 3) * p.k + piece_k0(quarter, task), pre_h[j]);
+        }
+      }
       // a warp per token, a lane per tile: the partial sums of a token arrive in one round trip (one thread adding
       // a token's 32 tiles up in turn waited for each load)
       for (int t = quarter; t < p.tokens; t += 4) {
@@ -321,9 +342,22 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         if (lane == 0) inv_rms[t] = rsqrtf(ss / (float)p.k + nx.eps);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      // A stage must always be written by the same warp, so that the warp sees each of the stage's "empty" phases
-      // in turn (a parity wait two phases late answers wrongly): with three stages three warps work.
-      constexpr int kXWarps = kStages < 4 ? kStages : 4;
+      // x = hidden * inv_rms * weight of one 16-byte piece (token r, 8 K elements), rounded, to its swizzled place
+      auto put = [&](uint8_t* x_tile, int task, const float (&h)[8], const float (&w)[8], bool inside) {
+        const int r = task >> 3, c = task & 7;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);       // past the end of K: zeros (the weights' are zeros too)
+        if (inside) {
+          const float inv = inv_rms[r];
+          uint32_t u[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(h[2 * e] * inv * w[2 * e], h[2 * e + 1] * inv * w[2 * e + 1]);
+            u[e] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          packed = make_uint4(u[0], u[1], u[2], u[3]);
+        }
+        *reinterpret_cast<uint4*>(x_tile + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
+      };
       for (int kb = quarter; quarter < kXWarps && kb < num_kb && ok; kb += kXWarps) {
         const int s = kb % kStages;
         if (kb >= kStages && !mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
@@ -331,24 +365,22 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           break;
         }
         uint8_t* x_tile = smem + s * GemmSmem<BN, kStages>::kStage + GemmSmem<BN, kStages>::kA;
-        for (int task = lane; task < p.tokens * 8; task += 32) {
-          const int r = task >> 3, c = task & 7;
-          const int k0 = (kb_begin + kb) * kTileK + c * 8;
-          uint4 packed = make_uint4(0u, 0u, 0u, 0u);       // past the end of K: zeros (the weights' are zeros too)
-          if (k0 < p.k) {
-            float h[8], w[8];
-            load8<float>(nx.hidden + (int64_t)r * p.k + k0, h);
-            load8<float>(nx.weight + k0, w);
-            const float inv = inv_rms[r];
-            uint32_t u[4];
+        if (pre && kb == quarter) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 v = __floats2bfloat162_rn(h[2 * e] * inv * w[2 * e], h[2 * e + 1] * inv * w[2 * e + 1]);
-              u[e] = *reinterpret_cast<uint32_t*>(&v);
-            }
-            packed = make_uint4(u[0], u[1], u[2], u[3]);
+          for (int j = 0; j < 2; ++j) {
+            const int task = lane + 32 * j;
+            if (task < p.tokens * 8) put(x_tile, task, pre_h[j], pre_w, piece_k0(kb, task) < p.k);
           }
-          *reinterpret_cast<uint4*>(x_tile + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
+        } else {
+          for (int task = lane; task < p.tokens * 8; task += 32) {
+            const int k0 = piece_k0(kb, task);
+            float h[8], w[8];
+            if (k0 < p.k) {
+              load8<float>(nx.hidden + (int64_t)(task >> 3) * p.k + k0, h);
+              load8<float>(nx.weight + k0, w);
+            }
+            put(x_tile, task, h, w, k0 < p.k);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads through the async proxy
         __syncwarp();
