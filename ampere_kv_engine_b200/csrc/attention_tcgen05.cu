@@ -18,6 +18,12 @@
 // mathematics is the reference's (ampere_kv/kv_cache.py:76-94): score = q.k * scale, key j visible to the query at
 // position t iff j <= t (and j > t - window), q-head h reads kv-head h / G.
 //
+//
+// That is the narrow form, for launches of more CTAs than SMs (two CTAs share an SM and fill each other's waits).
+// Launches that fit in one wave (short prompts, portions of long ones) take the wide form further down: one CTA
+// per SM with all of its tensor memory, 128-key blocks, two threads per query row and an issuing thread each for
+// the scores and for P V.
+//
 // Every wait is bounded; a wait that runs out sets kWaitTimeout in the status word and the CTA frees its TMEM and
 // leaves without writing results.
 #include "common.cuh"
@@ -140,6 +146,14 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -149,6 +163,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -501,6 +523,345 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   }
 }
 
+// ------------------------------------------------------------------------------------------------ the wide form
+// The same mathematics with the work shaped by three measurements: one thread issues a tcgen05.mma about every 100
+// cycles whatever its size, so the MMAs should be as wide as the tensor core allows and the scores and P V should
+// have an issuing thread each; and a softmax thread that owns a whole row keeps the tensor core waiting.  One CTA
+// per SM with all of its tensor memory: blocks of 128 keys (S = Q K^T is eight MMAs of 128 columns per block
+// instead of sixteen of 64), two score buffers of 128 columns, eight softmax warps (warps w and w + 4 share the
+// TMEM lanes 32 (w % 4) .. + 31 and take keys 0-63 and 64-127 of each block: per block a thread still handles 64
+// scores, but two blocks' worth of keys; the halves' maxima and sums meet through shared memory at a named
+// barrier of 64 threads), warp 8 copies (K of a stage released as soon as its scores are computed, V after P V),
+// warp 9 issues the scores, warp 10 issues P V.
+constexpr int kWideKeys = 128;
+constexpr int kWideSoftmax = 256;
+constexpr int kWideThreads = kWideSoftmax + 96;      // + the copy warp and the two issuing warps
+constexpr int kWideStages = 2;
+struct FaWideSmem {
+  static constexpr int kQ = 2 * kRows * 128;
+  static constexpr int kK = 2 * kWideKeys * 128;
+  static constexpr int kStage = 2 * kK;
+  static constexpr int kBars = (1 + 4 * kWideStages + 2 + 2 + 2) * 8;
+  static constexpr int kExchange = 2 * 2 * kRows * 4;      // [block parity][half][row]: maxima, at the end sums
+  static constexpr int kBytes = kQ + kWideStages * kStage + kBars + 16 + kExchange + 1024;
+};
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("barrier.cta.sync %0, 64;" ::"r"(id) : "memory"); }
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+attention_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                              const __grid_constant__ CUtensorMap v_map, FaParams fp) {
+  using FaSmem = FaWideSmem;
+  constexpr int kStagesKV = kWideStages;
+  const PagedAttentionParams& p = fp.p;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* kv_smem = smem + FaSmem::kQ;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(kv_smem + kStagesKV * FaSmem::kStage);
+  uint64_t* k_full = q_full + 1;                 // [stages]
+  uint64_t* v_full = k_full + kStagesKV;         // [stages]
+  uint64_t* k_empty = v_full + kStagesKV;        // [stages] the scores of the stage's block are computed: K may go
+  uint64_t* kv_empty = k_empty + kStagesKV;      // [stages] P V of the stage's block is done: V may go
+  uint64_t* s_ready = kv_empty + kStagesKV;      // [2] scores of a block are in TMEM buffer (block & 1)
+  uint64_t* p_ready = s_ready + 2;               // [2] P of a block is in tensor memory: 256 arrivals
+  uint64_t* pv_done = p_ready + 2;               // [2] O holds the sum through block j: barrier (j & 1), phase (j >> 1)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 2);
+  float* exchange = reinterpret_cast<float*>(tmem_holder + 4);      // [2][2][128]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.num_heads / p.num_kv_heads, NH = p.num_heads, P = p.page_size;
+  const int kvh = blockIdx.y;
+  constexpr uint32_t kTmemCols = 512;            // S: columns 0-127 and 128-255, O: columns 256-383
+  constexpr int kCopyWarp = 8, kScoreWarp = 9, kPvWarp = 10;
+
+  pdl_launch_dependents();
+  // CTAs start in index order and a sequence's later tiles see more keys: walk the tiles backwards, longest first
+  const int slot = blockIdx.x / fp.subtiles, sub = blockIdx.x - slot * fp.subtiles;
+  const int batch_tile = (int)(gridDim.x / fp.subtiles) - 1 - slot;
+  const int seq = p.tile_seq[batch_tile];
+  const int q0 = p.tile_q0[batch_tile] + fp.tq * sub;
+  const int nq = min(fp.tq, p.tile_nq[batch_tile] - fp.tq * sub);
+  if (nq <= 0) return;
+  const int ctx = p.ctx_lens[seq];
+  const int seq_q0 = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - seq_q0;
+  const int tile_pos = ctx - q_len + (q0 - seq_q0);
+  int lo = p.window > 0 ? max(0, tile_pos - p.window + 1) : 0;
+  lo = lo / fp.box_rows * fp.box_rows;
+  const int hi = tile_pos + nq;
+  const int num_blocks = (hi - lo + kWideKeys - 1) / kWideKeys;
+
+  if (tid == 0) {
+    bar_init(q_full, 1);
+    for (int s = 0; s < kStagesKV; ++s) {
+      bar_init(&k_full[s], 1);
+      bar_init(&v_full[s], 1);
+      bar_init(&k_empty[s], 1);
+      bar_init(&kv_empty[s], 1);
+    }
+    bar_init(&s_ready[0], 1);
+    bar_init(&s_ready[1], 1);
+    bar_init(&p_ready[0], kWideSoftmax);
+    bar_init(&p_ready[1], kWideSoftmax);
+    bar_init(&pv_done[0], 1);
+    bar_init(&pv_done[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kScoreWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_holder)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_holder;
+  pdl_wait();      // q and this step's K/V pages come from the previous kernels
+  bool ok = true;
+
+  if (warp == kCopyWarp) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      bar_expect_tx(q_full, 2u * (uint32_t)(fp.tq * G) * 128u);
+      tma_3d(q_smem, &q_map, 0, kvh * G, q0, q_full);
+      tma_3d(q_smem + kRows * 128, &q_map, 64, kvh * G, q0, q_full);
+    }
+    const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
+    // one copy per lane: lane = 4 * box + kind, kind = K low half, K high half, V low half, V high half
+    const int boxes = kWideKeys / fp.box_rows;
+    const int x = lane >> 2, kind = lane & 3;
+    auto row_of = [&](int blk) -> int {       // first cache row of this lane's box in block blk, -1: no box
+      const int key = lo + blk * kWideKeys + x * fp.box_rows;
+      if (blk >= num_blocks || x >= boxes || key >= hi) return -1;
+      const int logical = key / P;
+      int page = logical < p.table_width ? table[logical] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        set_status(p.status, kBadPage);
+        page = 0;     // keep the byte count honest; the result is flagged
+      }
+      return (page * p.num_kv_heads + kvh) * P + key % P;
+    };
+    auto fetch = [&](int blk, int y, bool keys) -> bool {      // this lane's copies of K or V of block blk
+      const int s = blk % kStagesKV;
+      if (blk >= kStagesKV) {
+        const bool freed = bar_wait(keys ? &k_empty[s] : &kv_empty[s], ((blk / kStagesKV) - 1) & 1);
+        if (!__all_sync(0xffffffffu, freed)) return false;       // the warp decides together: it votes below
+      }
+      const bool mine = y >= 0 && (kind < 2) == keys;
+      const uint32_t valid_boxes = __popc(__ballot_sync(0xffffffffu, y >= 0 && kind == 0));
+      uint64_t* full = keys ? &k_full[s] : &v_full[s];
+      if (lane == 0) bar_expect_tx(full, valid_boxes * (uint32_t)fp.box_rows * 256u);
+      __syncwarp();
+      if (mine) {
+        uint8_t* dst = kv_smem + s * FaSmem::kStage + (keys ? 0 : FaSmem::kK);
+        const uint32_t off = (uint32_t)(kind & 1) * (kWideKeys * 128) + (uint32_t)x * fp.box_rows * 128;
+        tma_2d(dst + off, keys ? &k_map : &v_map, (kind & 1) * 64, y, full);
+      }
+      return true;
+    };
+    int y_cur = row_of(0), y_next = row_of(1);
+    if (num_blocks > 0 && !fetch(0, y_cur, true)) ok = false;
+    for (int b = 0; b < num_blocks && ok; ++b) {
+      const int y_after = row_of(b + 2);                       // looked up two blocks early
+      if (b + 1 < num_blocks && !fetch(b + 1, y_next, true)) { ok = false; break; }
+      if (!fetch(b, y_cur, false)) { ok = false; break; }
+      y_cur = y_next;
+      y_next = y_after;
+    }
+  } else if (warp == kScoreWarp) {
+    // ---------------------------------------------------------------- MMA issuer: scores
+    if (lane == 0) {
+      constexpr uint32_t id_s = idesc(kWideKeys, false);
+      const uint32_t q_addr = s_addr(q_smem);
+      if (!bar_wait(q_full, 0)) ok = false;
+      for (int b = 0; b < num_blocks && ok; ++b) {
+        const int s = b % kStagesKV;
+        // the scores of block b go into buffer b & 1, where P of block b - 2 lay: P V of that block must be done
+        if (b >= 2 && !bar_wait(&pv_done[b & 1], ((b - 2) >> 1) & 1)) { ok = false; break; }
+        if (!bar_wait(&k_full[s], (b / kStagesKV) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k_addr = s_addr(kv_smem + s * FaSmem::kStage);
+#pragma unroll
+        for (int t = 0; t < kD / 16; ++t) {
+          const uint32_t off = (t >> 2) * (kRows * 128) + (t & 3) * 32;          // half, then 32 bytes per k-step
+          const uint32_t koff = (t >> 2) * (kWideKeys * 128) + (t & 3) * 32;
+          umma(tmem + (b & 1) * kWideKeys, desc_k_major(q_addr + off), desc_k_major(k_addr + koff), id_s, t > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_ready[b & 1]);
+        umma_commit(&k_empty[s]);
+      }
+    }
+  } else if (warp == kPvWarp) {
+    // ---------------------------------------------------------------- MMA issuer: O += P V
+    if (lane == 0) {
+      constexpr uint32_t id_o = idesc(kD, true);
+      for (int b = 0; b < num_blocks && ok; ++b) {
+        const int s = b % kStagesKV;
+        // once P is in tensor memory (and any rescaling of O is done) and V has landed
+        if (!bar_wait(&p_ready[b & 1], (b >> 1) & 1)) { ok = false; break; }
+        if (!bar_wait(&v_full[s], (b / kStagesKV) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_addr = s_addr(kv_smem + s * FaSmem::kStage) + FaSmem::kK;
+        const uint32_t p_tmem = tmem + (b & 1) * kWideKeys;      // P lies over the first half of the block's scores
+#pragma unroll
+        for (int t = 0; t < kWideKeys / 16; ++t) {
+          // A = P from tensor memory: 16 keys = 8 columns; B = V: 16 keys = 16 rows of 128 bytes
+          umma_a_tmem(tmem + 256, p_tmem + t * 8, desc_mn_major(v_addr + t * 16 * 128, kWideKeys * 128), id_o,
+                      (b > 0 || t > 0) ? 1u : 0u);
+        }
+        umma_commit(&pv_done[b & 1]);
+        umma_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax: two threads per query row
+    const int half = warp >> 2;                        // which 64 of a block's 128 keys
+    const int row = (warp & 3) * 32 + lane;            // TMEM lane
+    const int pair_bar = 1 + (warp & 3);               // the named barrier of this warp and its partner
+    const int token_local = row / G, head_local = row - token_local * G;
+    const bool live = token_local < nq;
+    const int pos = tile_pos + token_local;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const float scale_log2 = p.scale * kLog2e;
+    float m_ref = -CUDART_INF_F, l = 0.f;              // l: this half's share of the row sum
+
+    for (int b = 0; b < num_blocks; ++b) {
+      const int s = b % kStagesKV;
+      const int key0 = lo + b * kWideKeys + half * 64;      // this thread's first key of the block
+      const int nvalid_block = min(kWideKeys, hi - (lo + b * kWideKeys));
+      const int nvalid = max(0, min(64, nvalid_block - half * 64));
+      if (ok && !bar_wait(&s_ready[b & 1], (b >> 1) & 1)) ok = false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t raw[2][32];
+      if (ok) {
+        tmem_ld32_nowait(lane_base + (b & 1) * kWideKeys + half * 64, raw[0]);
+        tmem_ld32_nowait(lane_base + (b & 1) * kWideKeys + half * 64 + 32, raw[1]);
+        tmem_wait_ld();
+      }
+      const bool plain = ok && nvalid == 64 && key0 + 63 <= tile_pos &&
+                         (p.window <= 0 || key0 > tile_pos + nq - 1 - p.window);
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      if (plain && live) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int key = key0 + j;
+          const bool visible = ok && live && j < nvalid && key <= pos && (p.window <= 0 || key > pos - p.window);
+          if (!visible) raw[j >> 5][j & 31] = 0xff800000u;     // -inf
+          mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
+        }
+      }
+      // the row's maximum over the block: this half's and the partner's, through shared memory.  Both have their
+      // scores in registers once they meet, so either may then write P over the other's score columns.
+      float* xmax = exchange + (b & 1) * 2 * kRows;
+      const float hmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;     // the scale is positive
+      xmax[half * kRows + row] = hmax;
+      pair_sync(pair_bar);
+      const float bmax = fmaxf(hmax, xmax[(half ^ 1) * kRows + row]);
+      // raise the reference maximum only when it pays; then O (in TMEM) and l are rescaled.  Both halves of a row
+      // see the same bmax and m_ref, so they decide alike; each rescales its 64 of the row's 128 columns of O.
+      const bool raise = bmax > m_ref + kRescaleThreshold || (m_ref == -CUDART_INF_F && bmax > -CUDART_INF_F);
+      if (__any_sync(0xffffffffu, raise)) {
+        const float alpha = (raise && m_ref != -CUDART_INF_F) ? ex2(m_ref - bmax) : 1.f;
+        if (b > 0) {
+          // O must hold all earlier blocks and no MMA may be adding to it: P V of block b - 1 is done
+          if (ok && !bar_wait(&pv_done[(b - 1) & 1], ((b - 1) >> 1) & 1)) ok = false;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {      // 16 columns at a time: the block's scores are alive beside them
+              uint32_t o[16];
+              tmem_ld16_nowait(lane_base + 256 + half * 64 + c * 16, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st16(lane_base + 256 + half * 64 + c * 16, o);
+            }
+            tmem_wait_st();
+          }
+        }
+        if (raise) {
+          l *= alpha;
+          m_ref = bmax;
+        }
+      }
+      // A row that has seen no key yet subtracts 0, so that 2^(-inf - 0) = 0 and not 2^(-inf + inf).
+      const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+      // P as bfloat16 pairs, one 32-bit column per pair: this half's 64 keys are columns 32 half .. + 31 of the
+      // block's score buffer (P of the whole block lies over the first 64 score columns)
+      uint32_t packed[32];
+      float part[4] = {0.f, 0.f, 0.f, 0.f};     // four chains for the row sum as well
+#pragma unroll
+      for (int j = 0; j < 64; j += 2) {
+        const float pa = ex2(fmaf(__uint_as_float(raw[j >> 5][j & 31]), scale_log2, -m_sub));
+        const float pb = ex2(fmaf(__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31]), scale_log2, -m_sub));
+        part[(j >> 1) & 3] += pa + pb;
+        __nv_bfloat162 h = __floats2bfloat162_rn(pa, pb);
+        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      if (ok) {
+        tmem_st32(lane_base + (b & 1) * kWideKeys + half * 32, packed);
+        tmem_wait_st();
+      }
+      l += (part[0] + part[1]) + (part[2] + part[3]);
+      if (nvalid_block < kWideKeys) {
+        // V rows of keys past the end may hold anything (a page's tail, or nothing was loaded): zero them, or
+        // 0 * NaN would poison the product.  V has to have landed first.
+        if (ok && !bar_wait(&v_full[s], (b / kStagesKV) & 1)) ok = false;
+        uint8_t* v_area = kv_smem + s * FaSmem::kStage + FaSmem::kK;
+        for (int i = tid; i < (kWideKeys - nvalid_block) * 16; i += kWideSoftmax) {
+          const int r = nvalid_block + (i >> 4), c = i & 15;
+          *reinterpret_cast<uint4*>(v_area + (c >> 3) * (kWideKeys * 128) + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        // generic-proxy writes must be visible to the tensor core's async-proxy reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      bar_arrive(&p_ready[b & 1]);
+    }
+    // the row sum: this half's share and the partner's, first half first
+    float* xsum = exchange + (num_blocks & 1) * 2 * kRows;
+    xsum[half * kRows + row] = l;
+    pair_sync(pair_bar);
+    l = xsum[row] + xsum[kRows + row];
+    // O / l: the products run in order, so the last one done means all are
+    if (num_blocks > 0 && ok && !bar_wait(&pv_done[(num_blocks - 1) & 1], ((num_blocks - 1) >> 1) & 1)) ok = false;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)(q0 + token_local) * NH + kvh * G + head_local) * kD +
+                         half * 64;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t o[32];
+      if (ok) {
+        tmem_ld32_nowait(lane_base + 256 + half * 64 + c * 32, o);
+        tmem_wait_ld();
+      }
+      if (ok && live) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[v * 8 + 2 * e]) * inv,
+                                                      __uint_as_float(o[v * 8 + 2 * e + 1]) * inv);
+            packed[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(out + c * 32 + v * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0) set_status(p.status, kWaitTimeout);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kScoreWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -616,16 +977,44 @@ int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream)
     return (int)cudaErrorInvalidValue;
   FaParams fp{p, tq, subtiles, box_rows};
   const dim3 grid((unsigned)(p.num_tiles * subtiles), (unsigned)p.num_kv_heads, 1u);
-  // more CTAs than SMs: two per SM, two K/V stages each; fewer: one per SM with four stages.  Measured:
-  // a 2,048-token prompt (512 CTAs) 86 us with two per SM against 101 us with one; a 512-token portion after
-  // 7,680 keys (128 CTAs) 160 us with the deep ring against 191 us with the shallow one.
+  // the narrow form's ring (AKV_PROMPT_STAGES=2 | 4 forces it): two stages and two CTAs per SM when there are more
+  // CTAs than SMs, else four stages and one CTA per SM
   static const int forced = [] {
     const char* v = getenv("AKV_PROMPT_STAGES");
     const int n = v ? atoi(v) : 0;
     return (n == 2 || n == 4) ? n : 0;
   }();
+  // Two forms.  More CTAs than SMs: the narrow form, two CTAs per SM with two K/V stages each, whose CTAs fill
+  // each other's waits.  No more CTAs than SMs (a short prompt, a portion of a long one): the wide form, one CTA
+  // per SM with 128-key blocks, two threads per row and an issuing thread each for the scores and for P V.
+  // Measured: a 2,048-token prompt (512 CTAs) 81 us narrow against 84 us wide, an 8,192-token prompt 826 against
+  // 643 TFLOP/s; a 512-token portion after 7,680 keys (128 CTAs) 126 us wide against 148 us for the narrow form
+  // with a four-stage ring, a 256-token prompt 22 against 26 us.  AKV_PROMPT_FORM=1 | 2 forces wide | narrow.
+  static const int form = [] {
+    const char* v = getenv("AKV_PROMPT_FORM");
+    const int n = v ? atoi(v) : 0;
+    return (n == 1 || n == 2) ? n : 0;
+  }();
   const int sms = sm_count();
-  const bool shallow = forced ? forced == 2 : (int64_t)grid.x * grid.y > sms;
+  const bool few = (int64_t)grid.x * grid.y <= sms;
+  const bool wide_form = p.kernel == 4 || (p.kernel != 3 && (form == 1 || (form == 0 && few)));
+  if (wide_form) {
+    const int wide_rows = p.page_size < 64 ? p.page_size : 64;      // a box holds at most 64 keys (8 KB per half)
+    CUtensorMap kw, vw;
+    if (!cache_map(p.k_cache, rows, wide_rows, &kw) || !cache_map(p.v_cache, rows, wide_rows, &vw))
+      return (int)cudaErrorInvalidValue;
+    FaParams wide{p, tq, subtiles, wide_rows};
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             FaWideSmem::kBytes);
+      if (err != cudaSuccess) return (int)err;
+      configured = true;
+    }
+    return (int)launch_chain(attention_tcgen05_wide_kernel, grid, dim3(kWideThreads), FaWideSmem::kBytes, stream,
+                             dim3(1, 1, 1), q_map, kw, vw, wide);
+  }
+  const bool shallow = forced ? forced == 2 : !few;
   if (shallow) return launch_stages<2>(q_map, k_map, v_map, fp, grid, stream);
   return launch_stages<4>(q_map, k_map, v_map, fp, grid, stream);
 }

@@ -171,7 +171,8 @@ struct PagedAttentionParams {
   int num_heads, num_kv_heads, head_dim, page_size;
   int64_t num_pages;
   int window;                  // 0 = all keys
-  int kernel;                  // 0 = best kernel that takes the sizes, 1 = the general kernel, 2 = no tcgen05 prompt kernel
+  int kernel;                  // 0 = best kernel that takes the sizes, 1 = the general kernel, 2 = no tcgen05 prompt
+                               // kernel, 3 / 4 = the tcgen05 prompt kernel's narrow / wide form whatever the grid
   float scale;
   int dtype;
   int* status;

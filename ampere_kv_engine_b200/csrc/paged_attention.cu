@@ -273,12 +273,12 @@ int launch_paged_attention(const PagedAttentionParams& p, cudaStream_t stream) {
   if (p.num_tiles == 0 || p.num_tokens == 0) return 0;
   if (p.head_dim % 16 || p.head_dim > 256 || p.num_heads % p.num_kv_heads || p.num_splits < 1)
     return (int)cudaErrorInvalidValue;
-  if (p.kernel == 0 && p.q_tile > 1 && attention_tcgen05_supported(p)) {
+  if ((p.kernel == 0 || p.kernel == 3 || p.kernel == 4) && p.q_tile > 1 && attention_tcgen05_supported(p)) {
     PagedAttentionParams q = p;
     q.num_splits = 1;
     return launch_attention_tcgen05(q, stream);
   }
-  if ((p.kernel == 0 || p.kernel == 2) && attention_tc_supported(p)) {
+  if (p.kernel != 1 && attention_tc_supported(p)) {
     PagedAttentionParams q = p;
     if (q.q_tile > 1) q.num_splits = 1;          // the prompt kernel walks all keys of a tile itself
     const int err = launch_attention_tc(q, stream);

@@ -236,7 +236,8 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
     """Causal attention of the batch's new tokens over the paged cache.  ``kernel``: ``"auto"`` takes the
     tensor-core kernels where they fit (bfloat16, head size 64 or 128; prompt portions at head size 128 and groups
     of up to 16 q-heads on tcgen05) and the general kernel elsewhere; ``"general"`` forces the latter, ``"mma"``
-    keeps prompt portions on the mma.sync kernel.  Only the rows of the given tiles are written; with ``out`` they
+    keeps prompt portions on the mma.sync kernel, ``"tcgen05-narrow"`` / ``"tcgen05-wide"`` pick the form of the
+    tcgen05 prompt kernel that the grid's size otherwise decides.  Only the rows of the given tiles are written; with ``out`` they
     go into that tensor (a batch may be covered by two calls with different tile sizes)."""
     if out is None:
         out = torch.empty_like(q)
@@ -246,7 +247,7 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
                                device=q.device)
     ext().paged_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
                           partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(window or 0),
-                          float(scale), status, {"auto": 0, "general": 1, "mma": 2}[kernel])
+                          float(scale), status, {"auto": 0, "general": 1, "mma": 2, "tcgen05-narrow": 3, "tcgen05-wide": 4}[kernel])
     _launched(2 if num_splits > 1 else 1)
     return out
 

@@ -404,8 +404,9 @@ def test_tcgen05_prompt_attention(ops, nh, nkv, page, q_tile, window):
     case = PagedCase(dtype, nh, nkv, 128, page, q_lens=[300, 77, 33, 1, 128], ctx_lens=[300, 500, 33, 40, 128],
                      seed=page + nh, q_tile=q_tile)
     want = case.reference(window)
-    torch.testing.assert_close(case.run(ops, window, 1, kernel="auto"), want, **tol(dtype))
-    torch.testing.assert_close(case.run(ops, window, 1, kernel="mma"), want, **tol(dtype))
+    # both forms of the kernel (the grid's size picks one otherwise), and the mma.sync kernel
+    for kernel in ("tcgen05-narrow", "tcgen05-wide", "auto", "mma"):
+        torch.testing.assert_close(case.run(ops, window, 1, kernel=kernel), want, **tol(dtype))
 
 
 @pytest.mark.parametrize("q_tile", [32, 64])
@@ -427,10 +428,11 @@ def test_tcgen05_prompt_attention_repeats_and_rescales(ops, q_tile):
                 case.q_seq[2][:, h] = (case.q_seq[2][:, h].float() + 25.0 * direction).to(dtype)
     case.rewrite_cache()
     want = case.reference(0)
-    first = case.run(ops, 0, 1, kernel="auto")
-    torch.testing.assert_close(first, want, **tol(dtype))
-    for _ in range(8):
-        assert torch.equal(case.run(ops, 0, 1, kernel="auto"), first)
+    for form in ("tcgen05-narrow", "tcgen05-wide"):
+        first = case.run(ops, 0, 1, kernel=form)
+        torch.testing.assert_close(first, want, **tol(dtype))
+        for _ in range(8):
+            assert torch.equal(case.run(ops, 0, 1, kernel=form), first)
     torch.testing.assert_close(case.run(ops, 0, 1, kernel="mma"), want, **tol(dtype))
 
 
@@ -470,7 +472,7 @@ def test_attention_over_thousands_of_keys(ops, window, q_tile):
             case.q_seq[0][:, h] = (case.q_seq[0][:, h].float() + 20.0 * direction).to(dtype)
     case.rewrite_cache()
     want = _last_rows_reference(case, window)
-    for kernel in ("auto", "mma"):
+    for kernel in ("tcgen05-narrow", "tcgen05-wide", "auto", "mma"):
         torch.testing.assert_close(case.run(ops, window, 1, kernel=kernel), want, **tol(dtype))
     decode = PagedCase(dtype, 8, 2, 128, 16, q_lens=[1, 1, 1, 1], ctx_lens=[6000, 4100, 1, 2500], seed=42)
     want = _last_rows_reference(decode, window)
