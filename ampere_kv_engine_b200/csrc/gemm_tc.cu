@@ -372,14 +372,26 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             if (task < p.tokens * 8) put(x_tile, task, pre_h[j], pre_w, piece_k0(kb, task) < p.k);
           }
         } else {
-          for (int task = lane; task < p.tokens * 8; task += 32) {
-            const int k0 = piece_k0(kb, task);
-            float h[8], w[8];
-            if (k0 < p.k) {
-              load8<float>(nx.hidden + (int64_t)(task >> 3) * p.k + k0, h);
-              load8<float>(nx.weight + k0, w);
+          // a lane's pieces of a tile are all of the same 8 K elements (32 is a multiple of 8): one fetch of the
+          // norm weights, and the rows of four pieces under way at a time (one piece at a time paid a round trip
+          // to the L2 per piece: with 16 tokens four in a row per tile)
+          const int k0 = piece_k0(kb, lane);
+          const bool inside = k0 < p.k;
+          float w[8];
+          if (inside) load8<float>(nx.weight + k0, w);
+#pragma unroll 1
+          for (int base = lane; base < p.tokens * 8; base += 4 * 32) {
+            float h[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int task = base + 32 * j;
+              if (inside && task < p.tokens * 8) load8<float>(nx.hidden + (int64_t)(task >> 3) * p.k + k0, h[j]);
             }
-            put(x_tile, task, h, w, k0 < p.k);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int task = base + 32 * j;
+              if (task < p.tokens * 8) put(x_tile, task, h[j], w, inside);
+            }
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads through the async proxy

@@ -321,9 +321,10 @@ SMALL_M_LIMIT = 64
 use_small_m_gemm = True
 #: up to this many tokens a decode branch adds to the residual stream inside its last product and the next product
 #: applies the norm to its own token operand.  Every CTA of that product re-reads the float32 stream for its K
-#: range, which grows with the tokens: measured per decode step on B200, the pair saves 94 us at 8 tokens and costs
-#: 50 us at 12, 210 us at 16 and 1.3 ms at 32.
-LAZY_NORM_LIMIT = 8
+#: range, which grows with the tokens: measured per decode step on B200 against the norm as a kernel of its own,
+#: 3.64 against 3.67 ms at 12 tokens, 3.71 against 3.76 ms at 16, but 4.98 against 4.25 ms at 32 and 7.0 against
+#: 5.2 ms at 64.
+LAZY_NORM_LIMIT = 16
 #: hand split-K partial sums to the consuming kernel instead of adding them up inside the product kernel
 prefer_partials = False
 
