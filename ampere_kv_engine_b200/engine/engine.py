@@ -116,20 +116,17 @@ class Engine:
             logits = self.runner.step(entries)
         if logits is None:
             return None
-        tokens = self.sampler.sample(logits, [r.sampling for r in wanted], steps)
-        count = tokens.shape[0]
-        self.runner.sampled[:count].copy_(tokens)
+        # the choice lands where the next step's entries with a ``source`` look for it, right behind the kernels'
+        # status word: one read-back brings both
+        count = self.sampler.sample(logits, [r.sampling for r in wanted], steps, out=self.runner.sampled).shape[0]
         slot = self._readback[self._readback_turn]
         self._readback_turn = (self._readback_turn + 1) % len(self._readback)
-        # one read-back: the tokens and the kernels' status word
         if self.device.type == "cuda":
-            slot[:count].copy_(tokens, non_blocking=True)
-            slot[count:count + 1].copy_(self.runner.status, non_blocking=True)
+            slot[:count + 1].copy_(self.runner.outcome[:count + 1], non_blocking=True)
             done = torch.cuda.Event()
             done.record()
         else:
-            slot[:count].copy_(tokens)
-            slot[count:count + 1].copy_(self.runner.status)
+            slot[:count + 1].copy_(self.runner.outcome[:count + 1])
             done = None
         return slot, count, done
 
@@ -141,10 +138,10 @@ class Engine:
         slot, count, done = handle
         if done is not None:
             done.synchronize()
-        host = slot[:count + 1].tolist()
-        if host[-1]:
+        host = slot[:count + 1].tolist()      # the status word, then the tokens
+        if host[0]:
             self.runner.raise_on_status()
-        return host[:-1]
+        return host[1:]
 
     def new_scheduler(self, **overrides) -> Scheduler:
         options = dict(max_batch_tokens=self.max_batch_tokens, max_seqs=self.max_seqs,

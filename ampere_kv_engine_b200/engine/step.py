@@ -77,9 +77,11 @@ class ModelRunner:
                                     max_seqs=max_seqs, dtype=kv_dtype, device=self.device)
         self.views = self.manager.layer_views()
         self.q_tile = model.q_tile() if hasattr(model, "q_tile") else ops.ATTENTION_Q_TILE
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        #: the tokens the last step chose, kept on the device: an entry with a ``source`` reads its token here
-        self.sampled = torch.zeros(max(1, max_seqs), dtype=torch.int32, device=self.device)
+        # the kernels' status word and, behind it, the tokens the last step chose (kept on the device: an entry with
+        # a ``source`` reads its token here): one buffer, so that one copy brings both to the host
+        self.outcome = torch.zeros(1 + max(1, max_seqs), dtype=torch.int32, device=self.device)
+        self.status = self.outcome[:1]
+        self.sampled = self.outcome[1:]
         self.steps_run = 0
         self.last_h2d_bytes = 0
         #: decode-only steps are replayed as CUDA graphs (one per batch-size and table-width bucket)

@@ -255,11 +255,19 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
 _SAMPLE_TICKETS: dict = {}      # per device: zeroed row counters of the sampling kernel (it leaves them zero)
 
 
-def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+           out: torch.Tensor | None = None) -> torch.Tensor:
     """int32 token per row: the arg-max where ``temperature`` is 0, else the inverse-CDF draw of
-    ``softmax(logits / temperature)`` at ``uniform``."""
+    ``softmax(logits / temperature)`` at ``uniform``.  With ``out`` (int32, contiguous, at least a row each) the
+    tokens are written there."""
     rows = logits.shape[0]
-    tokens = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        tokens = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    else:
+        if out.dtype != torch.int32 or out.device != logits.device or out.dim() != 1 or out.shape[0] < rows \
+                or not out.is_contiguous():
+            raise ValueError("sample: out must be a contiguous int32 vector on the logits' device with a row each")
+        tokens = out[:rows]
     tickets = _SAMPLE_TICKETS.get(logits.device)
     if tickets is None or tickets.numel() < rows:
         tickets = torch.zeros((max(rows, 512),), dtype=torch.int32, device=logits.device)

@@ -45,17 +45,35 @@ class SamplingParams:
 
 
 class Sampler:
+    #: pinned staging buffers in turn: a copy may still be under way when the next step is prepared
+    RING = 4
+
     def __init__(self, device):
         self.device = torch.device(device)
+        self._staging: list[torch.Tensor] = []
+        self._turn = 0
 
-    def sample(self, logits: torch.Tensor, params: list[SamplingParams], steps: list[int]) -> torch.Tensor:
-        """int32 token per row of ``logits`` (on the device; no sync)."""
+    def _stage(self, rows: int) -> torch.Tensor:
+        """A pinned [2, rows] float32 buffer (temperatures, uniforms) that no copy of the last RING - 1 steps reads."""
+        if not self._staging or self._staging[0].shape[1] < rows:
+            size = max(64, 2 * rows)
+            self._staging = [torch.empty((2, size), dtype=torch.float32).pin_memory() for _ in range(self.RING)]
+        self._turn = (self._turn + 1) % self.RING
+        return self._staging[self._turn][:, :rows]
+
+    def sample(self, logits: torch.Tensor, params: list[SamplingParams], steps: list[int],
+               out: torch.Tensor | None = None) -> torch.Tensor:
+        """int32 token per row of ``logits`` (on the device; no sync), written into ``out`` when that is given."""
         if logits.shape[0] != len(params):
             raise ValueError("one SamplingParams per logits row")
-        host = torch.tensor([[p.temperature for p in params],
-                             [uniform_for(p.seed, p.stream, s) if p.temperature > 0 else 0.0
-                              for p, s in zip(params, steps)]], dtype=torch.float32)
+        values = torch.tensor([[p.temperature for p in params],
+                               [uniform_for(p.seed, p.stream, s) if p.temperature > 0 else 0.0
+                                for p, s in zip(params, steps)]], dtype=torch.float32)
         if self.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        return ops.sample(logits.contiguous(), dev[0], dev[1])
+            host = self._stage(len(params))
+            host.copy_(values)
+            dev = torch.empty((2, len(params)), dtype=torch.float32, device=self.device)
+            dev.copy_(host, non_blocking=True)
+        else:
+            dev = values
+        return ops.sample(logits.contiguous(), dev[0], dev[1], out=out)
