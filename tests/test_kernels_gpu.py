@@ -393,7 +393,8 @@ def test_tensor_core_and_general_kernels_agree(ops, nh, nkv, d, page, window):
                                                  # groups that do not divide 128 (dead rows at a tile's end), one
                                                  # q-head per kv head, sixteen
                                                  (40, 8, 16, 25), (40, 8, 16, 32), (6, 2, 16, 42), (4, 4, 16, 32),
-                                                 (16, 1, 16, 32), (12, 2, 32, 21), (14, 2, 16, 64)])
+                                                 (16, 1, 16, 32), (12, 2, 32, 21), (14, 2, 16, 64), (8, 2, 64, 32),
+                                                 (8, 2, 128, 32)])
 @pytest.mark.parametrize("window", [0, 100, 37])
 def test_tcgen05_prompt_attention(ops, nh, nkv, page, q_tile, window):
     """Prompt portions at head size 128 with groups of 1 to 16 q-heads run on the tcgen05 kernel: whole
