@@ -312,6 +312,22 @@ __global__ void __launch_bounds__(128) qk_norm_rope_write_vec_kernel(QkRopeWrite
   const int total_heads = p.num_heads + 2 * p.num_kv_heads;
   const int64_t token = blockIdx.x;
   const bool rotary = p.inv_freq != nullptr;
+  // A block lives for a few microseconds, most of them waiting: for the token's position, then its angles, then
+  // its row.  The row does not depend on the angles: the loads of the first passes over the heads (all of them
+  // for up to 64 heads) are issued first and travel while the angle table is made.
+  constexpr int kAhead = 4;
+  const int sub = lane % LPH, d0 = sub * 8;
+  const __nv_bfloat16* row = (const __nv_bfloat16*)p.qkv + token * (int64_t)total_heads * D;
+  uint4 ahead_lo[kAhead], ahead_hi[kAhead];
+#pragma unroll
+  for (int i = 0; i < kAhead; ++i) {
+    const int head = (i * 4 + warp) * kHeadsPerWarp + lane / LPH;
+    ahead_lo[i] = ahead_hi[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (head < total_heads) {
+      ahead_lo[i] = *reinterpret_cast<const uint4*>(row + head * D + d0);
+      ahead_hi[i] = *reinterpret_cast<const uint4*>(row + head * D + half + d0);
+    }
+  }
   if (rotary && threadIdx.x < half) {
     float sn, co;
     sincosf((float)p.positions[token] * p.inv_freq[threadIdx.x], &sn, &co);
@@ -330,13 +346,31 @@ __global__ void __launch_bounds__(128) qk_norm_rope_write_vec_kernel(QkRopeWrite
     }
   }
   __syncthreads();
-  const int sub = lane % LPH, d0 = sub * 8;
-  const __nv_bfloat16* row = (const __nv_bfloat16*)p.qkv + token * (int64_t)total_heads * D;
-  for (int base = 0; base < total_heads; base += 4 * kHeadsPerWarp) {
+  auto unpack = [](const uint4& raw, float (&out)[8]) {
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(pairs[e]);
+      out[2 * e] = f.x;
+      out[2 * e + 1] = f.y;
+    }
+  };
+  int pass = 0;
+  for (int base = 0; base < total_heads; base += 4 * kHeadsPerWarp, ++pass) {
     const int head = base + warp * kHeadsPerWarp + lane / LPH;
     const bool active = head < total_heads;
     float lo[8], hi[8];
-    if (active) {
+    if (pass < kAhead) {      // fetched above (zeros for a head that does not exist)
+      uint4 raw_lo = ahead_lo[0], raw_hi = ahead_hi[0];
+#pragma unroll
+      for (int i = 1; i < kAhead; ++i)
+        if (pass == i) {
+          raw_lo = ahead_lo[i];
+          raw_hi = ahead_hi[i];
+        }
+      unpack(raw_lo, lo);
+      unpack(raw_hi, hi);
+    } else if (active) {
       load8<__nv_bfloat16>(row + head * D + d0, lo);
       load8<__nv_bfloat16>(row + head * D + half + d0, hi);
     } else {
