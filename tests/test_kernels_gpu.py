@@ -594,11 +594,13 @@ def test_sample_distribution(ops):
 
 
 @pytest.mark.parametrize("tokens", [1, 8, 17, 64])
-@pytest.mark.parametrize("features,k", [(128, 64), (200, 200), (6144, 4096), (4096, 12288), (1000, 4096)])
+@pytest.mark.parametrize("features,k", [(128, 64), (200, 200), (6144, 4096), (4096, 12288), (1000, 4096),
+                                        (1001, 1024), (3, 200)])
 def test_small_m_gemm_on_tcgen05(ops, tokens, features, k):
     """The weight-streaming tcgen05 kernel: partial sums of every split add up to x @ w^T (float32 reference on the
     same bfloat16 values), for token counts that pad to 16/32/64, feature counts that are no multiple of the
-    128-row tile and K that is no multiple of the 64-element stage."""
+    128-row tile (nor of the four features a lane stores at once) and K that is no multiple of the 64-element
+    stage."""
     g = torch.Generator().manual_seed(tokens * 1000 + features)
     x = torch.randn(tokens, k, generator=g).to(torch.bfloat16)
     w = (torch.randn(features, k, generator=g) * k ** -0.5).to(torch.bfloat16)
